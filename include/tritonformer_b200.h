@@ -1,0 +1,171 @@
+/*
+ * tritonformer_b200 -- C ABI of the sm_100a kernel library behind the
+ * tritonformer autograd Functions.
+ *
+ * Every entry point
+ *   - takes plain device pointers, 64-bit sizes/strides (in ELEMENTS), a dtype
+ *     code, and the CUDA stream (as void*) to launch on;
+ *   - is asynchronous and stream ordered, never synchronises the host, never
+ *     allocates or frees device memory (scratch buffers are passed in), never
+ *     writes to an input;
+ *   - returns 0 on success or a negative tfb_status; the text of the last
+ *     failure on the calling thread is available from tfb_last_error().
+ *
+ * The comment above each declaration names the piece of the reference
+ * (fattorib/tritonformer, paths relative to that project) it stands in for.
+ */
+#ifndef TRITONFORMER_B200_H
+#define TRITONFORMER_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* dtype codes */
+#define TFB_F16 0
+#define TFB_BF16 1
+#define TFB_F32 2
+
+/* status codes */
+#define TFB_OK 0
+#define TFB_ERR_ARG (-1)      /* bad shape / stride / alignment / dtype      */
+#define TFB_ERR_UNSUPPORTED (-2)
+#define TFB_ERR_LAUNCH (-3)   /* CUDA reported an error at launch            */
+#define TFB_ERR_DRIVER (-4)   /* tensor-map encoding / driver entry missing  */
+
+/* Library ABI version (bumped when a signature changes). */
+int tfb_version(void);
+/* Text of the last error raised on the calling thread ("" if none). */
+const char* tfb_last_error(void);
+/* Number of kernels this library has launched in the calling process. */
+int64_t tfb_launch_count(void);
+/* Device-side status of the tcgen05 kernels: 0, or the code of the first bounded wait that
+ * expired (the kernels then return without doing work until the status is cleared).
+ * Synchronises the device; meant for tests and post-mortems.  reset != 0 clears it.      */
+int tfb_device_status(int reset);
+/* Test switches.  key 0: value 1 sends every GEMM to the generic-stride kernel.
+ *                key 1: value 1 sends every attention call to the mma.sync kernels.      */
+void tfb_debug_set(int key, int value);
+
+/* ------------------------------------------------------------------ LayerNorm
+ * Replaces layernorm_fwd + layernorm_fwd_kernel (tritonformer/kernels/layernorm.py:9-87).
+ * y = alpha * (x - mean) * rstd + beta over the last dim; additionally stores the
+ * per-row mean and rstd (fp32) so the backward does not recompute them.
+ * x, y: (rows, d) with row strides x_ld / y_ld, unit inner stride.           */
+int tfb_layernorm_fwd(const void* x, const void* alpha, const void* beta, void* y,
+                      float* mean, float* rstd, int64_t rows, int64_t d,
+                      int64_t x_ld, int64_t y_ld, float eps, int dtype, void* stream);
+
+/* Number of fp32 partial rows the backward needs: scratch = n * 2 * d floats. */
+int64_t tfb_layernorm_bwd_partials(int64_t rows, int64_t d);
+
+/* Replaces dx_layernorm + layernorm_da_db + _unbroadcast
+ * (tritonformer/kernels/layernorm.py:91-259, kernels/reductions.py:25-63): one pass
+ * over (dy, x) writes dx and fp32 partial column sums; a second small kernel folds the
+ * partials into dalpha / dbeta (dtype `dtype`, shape (d,)).                    */
+int tfb_layernorm_bwd(const void* dy, const void* x, const void* alpha,
+                      const float* mean, const float* rstd, void* dx,
+                      void* dalpha, void* dbeta, float* partials, int64_t n_partials,
+                      int64_t rows, int64_t d, int64_t dy_ld, int64_t x_ld, int64_t dx_ld,
+                      int dtype, void* stream);
+
+/* -------------------------------------------------------------------- Softmax
+ * Replaces softmax_fwd / softmax_bwd (tritonformer/kernels/softmax.py:7-111).
+ * Row softmax over the last dim; the backward writes a fresh tensor (the reference
+ * overwrites grad_out).  dtype may be F16, BF16 or F32.                        */
+int tfb_softmax_fwd(const void* x, void* y, int64_t rows, int64_t cols,
+                    int64_t x_ld, int64_t y_ld, int dtype, void* stream);
+int tfb_softmax_bwd(const void* dy, const void* y, void* dx, int64_t rows, int64_t cols,
+                    int64_t dy_ld, int64_t y_ld, int64_t dx_ld, int dtype, void* stream);
+
+/* -------------------------------------------------------------- Cross-entropy
+ * Replaces cross_entropy_fwd / cross_entropy_bwd (tritonformer/kernels/crossentropy.py:7-127)
+ * and the multiply that follows in tritonformer/crossentropy.py:24.
+ * fwd: loss[i] = logsumexp(logits[i,:]) - logits[i,label[i]] (dtype `dtype`), lse[i] fp32;
+ *      loss_f32 (may be NULL) receives the same per-row loss unrounded.
+ * bwd: dlogits[i,j] = (exp(logits[i,j]-lse[i]) - [j==label[i]]) * grad[i].
+ * `grad` has element stride grad_stride (0 broadcasts one value).
+ * A label outside [0, vocab) makes its row contribute zero loss and zero gradient.   */
+int tfb_cross_entropy_fwd(const void* logits, const int64_t* labels, void* loss, float* loss_f32,
+                          float* lse, int64_t rows, int64_t vocab, int64_t logits_ld, int dtype,
+                          void* stream);
+int tfb_cross_entropy_bwd(const void* logits, const int64_t* labels, const float* lse,
+                          const void* grad, int64_t grad_stride, void* dlogits,
+                          int64_t rows, int64_t vocab, int64_t logits_ld, int64_t dlogits_ld,
+                          int dtype, void* stream);
+
+/* ---------------------------------------------------------- ReLU grad / bias grad
+ * Replaces mask_grad (tritonformer/kernels/activation.py:7-44) without mutating the
+ * incoming gradient: dz = act > 0 ? dy : 0 for n contiguous elements.          */
+int tfb_relu_bwd(const void* dy, const void* act, void* dz, int64_t n, int dtype, void* stream);
+
+/* fp32 partial rows needed by tfb_colsum: scratch = n * cols floats.           */
+int64_t tfb_colsum_partials(int64_t rows, int64_t cols);
+/* Replaces unbroadcast_leading + _unbroadcast (tritonformer/kernels/reductions.py:25-122):
+ * out[j] = sum_i x[i,j], accumulated in fp32.                                  */
+int tfb_colsum(const void* x, void* out, float* partials, int64_t n_partials,
+               int64_t rows, int64_t cols, int64_t x_ld, int dtype, void* stream);
+
+/* ------------------------------------------------------------------------ GEMM
+ * Replaces mm / gemm / bmm + torch.sum (tritonformer/kernels/gemm.py:81-616,
+ * tritonformer/linear.py:15-102).
+ *   C[m,n] = act( sum_k A(m,k) * B(k,n) + bias[n] ) (+ C[m,n] if accumulate)
+ * A(m,k) lives at a[m*a_sm + k*a_sk], B(k,n) at b[k*b_sk + n*b_sn] (element strides,
+ * one of each pair must be 1); C is row-major with leading dimension ldc.
+ * fp16/bf16 operands, fp32 accumulation over the whole contraction, one rounding.
+ * The weight gradient is this same call with the contraction over all B*T rows.
+ * bias may be NULL; relu != 0 applies max(.,0) after the bias.
+ * Shapes whose operand rows are 16-byte aligned run on the tcgen05/TMA kernel; the
+ * rest run on a generic-stride tensor-core kernel.  `path` (may be NULL) receives
+ * 1 for the tcgen05 kernel, 0 for the generic one.                              */
+int tfb_gemm(const void* a, const void* b, void* c, const void* bias,
+             int64_t M, int64_t N, int64_t K,
+             int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int64_t ldc,
+             int relu, int accumulate, int dtype, void* stream, int* path);
+
+/* ------------------------------------------------------------------- Attention
+ * Replaces flash_wrapper_fwd / flash_wrapper_fwd_attn_bias
+ * (tritonformer/kernels/attention.py:9-217, kernels/biased_attention.py:9-245).
+ * q,k,v,o: (B,H,T,hd) with element strides {b,h,t} each and unit stride on hd.
+ * Causal. Optional additive bias, one of:
+ *   slopes != NULL : ALiBi, bias(i,j) = -slope[h]*(i-j), slopes fp32 (H,).  If
+ *                    alibi_round != 0 the product is rounded the way the reference table is
+ *                    built (element dtype product of rounded distance and rounded slope,
+ *                    transformer.py:55-75).
+ *   bias != NULL   : dense (H,T,T) table of dtype `dtype`, element strides bias_sh, bias_si,
+ *                    unit stride on j (entries above the diagonal are ignored).
+ * lse: (B,H,T) fp32 contiguous = natural-log-sum-exp of the scaled, biased scores.  */
+int tfb_attention_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
+                      int64_t B, int64_t H, int64_t T, int64_t hd,
+                      const int64_t* q_strides, const int64_t* k_strides,
+                      const int64_t* v_strides, const int64_t* o_strides,
+                      const float* slopes, int alibi_round,
+                      const void* bias, int64_t bias_sh, int64_t bias_si,
+                      int dtype, void* stream, int* path);
+
+/* Bytes of scratch tfb_attention_bwd needs (fp32 delta (B,H,T) plus, on the tcgen05
+ * path, an fp32 dQ accumulator (B,H,T,hd)).                                     */
+int64_t tfb_attention_bwd_scratch_bytes(int64_t B, int64_t H, int64_t T, int64_t hd);
+
+/* Replaces flash_wrapper_bwd / flash_wrapper_bwd_attn_bias
+ * (tritonformer/kernels/attention.py:221-607, kernels/biased_attention.py:249-660).
+ * Every tensor carries its own {b,h,t} strides.                                 */
+int tfb_attention_bwd(const void* q, const void* k, const void* v, const void* o,
+                      const void* d_o, const float* lse,
+                      void* dq, void* dk, void* dv,
+                      int64_t B, int64_t H, int64_t T, int64_t hd,
+                      const int64_t* q_strides, const int64_t* k_strides,
+                      const int64_t* v_strides, const int64_t* o_strides,
+                      const int64_t* do_strides, const int64_t* dq_strides,
+                      const int64_t* dk_strides, const int64_t* dv_strides,
+                      const float* slopes, int alibi_round,
+                      const void* bias, int64_t bias_sh, int64_t bias_si,
+                      void* scratch, int64_t scratch_bytes,
+                      int dtype, void* stream, int* path);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRITONFORMER_B200_H */

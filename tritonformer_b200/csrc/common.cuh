@@ -1,0 +1,115 @@
+// Shared host/device helpers for the tritonformer_b200 kernel library (sm_100a only).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+#include <atomic>
+
+#include "../../include/tritonformer_b200.h"
+
+namespace tfb {
+
+// ---- host-side error plumbing -------------------------------------------------------
+extern thread_local char g_err[512];
+extern std::atomic<int64_t> g_launches;
+
+inline int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+// Call after a <<<>>> launch: counts it and converts a launch error into a status.
+inline int launched(const char* what) {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(TFB_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+  return TFB_OK;
+}
+
+#define TFB_REQUIRE(cond, ...)                         \
+  do {                                                 \
+    if (!(cond)) return ::tfb::fail(TFB_ERR_ARG, __VA_ARGS__); \
+  } while (0)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// ---- device-side numeric helpers ------------------------------------------------------
+template <typename T> struct Num;
+template <> struct Num<__half> {
+  using T2 = __half2;
+  static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
+  static __device__ __forceinline__ float2 to_f2(__half2 v) { return __half22float2(v); }
+  static __device__ __forceinline__ __half2 from_f2(float a, float b) { return __floats2half2_rn(a, b); }
+};
+template <> struct Num<__nv_bfloat16> {
+  using T2 = __nv_bfloat162;
+  static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
+  static __device__ __forceinline__ float2 to_f2(__nv_bfloat162 v) { return __bfloat1622float2(v); }
+  static __device__ __forceinline__ __nv_bfloat162 from_f2(float a, float b) { return __floats2bfloat162_rn(a, b); }
+};
+template <> struct Num<float> {
+  static __device__ __forceinline__ float to_f(float v) { return v; }
+  static __device__ __forceinline__ float from_f(float v) { return v; }
+};
+
+// 16-byte vector of 8 sixteen-bit values, unpacked to / packed from fp32.
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]) {
+  using T2 = typename Num<T>::T2;
+  const T2* p = reinterpret_cast<const T2*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = Num<T>::to_f2(p[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+template <typename T>
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  using T2 = typename Num<T>::T2;
+  uint4 raw;
+  T2* p = reinterpret_cast<T2*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p[i] = Num<T>::from_f2(f[2 * i], f[2 * i + 1]);
+  return raw;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Streaming (evict-first) 16-byte global accesses for data touched once.
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.cs.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+  return r;
+}
+__device__ __forceinline__ void st_stream16(void* p, const uint4& v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+// Dispatch a 16-bit dtype code to a template instantiation.
+#define TFB_DISPATCH_16(dtype, T, ...)                                   \
+  if ((dtype) == TFB_F16) { using T = __half; __VA_ARGS__ }              \
+  else if ((dtype) == TFB_BF16) { using T = __nv_bfloat16; __VA_ARGS__ } \
+  else return ::tfb::fail(TFB_ERR_ARG, "dtype %d: expected fp16 or bf16", (int)(dtype));
+
+}  // namespace tfb

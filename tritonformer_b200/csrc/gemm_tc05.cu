@@ -1,0 +1,358 @@
+// tcgen05 / TMEM GEMM for sm_100a.
+//
+//   C[M,N] = act(A·B + bias) (+ C), fp16/bf16 operands, fp32 accumulation in tensor memory.
+//
+// Persistent CTAs (one per SM) walk 128 x BN output tiles.  Per CTA:
+//   warp 0  : TMA producer  - 128-byte-swizzled operand tiles into a STAGES-deep smem ring
+//   warp 1  : MMA issuer    - one elected lane issues tcgen05.mma (M=128, N=BN, K=16) into one
+//                             of two TMEM accumulator buffers, commits ring slots back
+//   warps 2-5: epilogue     - tcgen05.ld the finished accumulator (each warp its 32 lanes),
+//                             bias / ReLU / accumulate, round once, 16-byte global stores;
+//                             overlaps the next tile's main loop through the second buffer
+// Either operand may be K-major (contraction index contiguous) or MN-major, so the forward
+// product X·W, the input gradient dY·Wᵀ and the weight gradient Xᵀ·dY (contraction over every
+// token of the batch, i.e. the batch reduction fused into the product) are the same kernel.
+#include "tc05.cuh"
+#include <type_traits>
+
+namespace tfb {
+
+constexpr int TB_M = 128;
+constexpr int TB_K = 64;  // 64 sixteen-bit elements = one 128-byte swizzle row
+constexpr int TB_THREADS = 192;
+
+template <int BN> struct GemmCfg {
+  static constexpr int A_BYTES = TB_M * TB_K * 2;
+  static constexpr int B_BYTES = BN * TB_K * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+  static constexpr int TMEM_COLS = 2 * BN;
+};
+
+struct GemmParams {
+  void* C;
+  const void* bias;
+  int M, N, K;
+  int64_t ldc;
+  int relu, accumulate;
+  int tiles_m, tiles_n;
+};
+
+template <typename T, int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(TB_THREADS, 1) gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA,
+                                                                  const __grid_constant__ CUtensorMap tmB,
+                                                                  const GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: the swizzle pattern is a function of the shared-memory address
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full = bars;                    // [STAGES] TMA -> MMA
+  uint64_t* empty = bars + STAGES;          // [STAGES] MMA -> TMA
+  uint64_t* acc_full = bars + 2 * STAGES;   // [2] MMA -> epilogue
+  uint64_t* acc_empty = acc_full + 2;       // [2] epilogue -> MMA
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 4);  // one arrival per epilogue warp
+    }
+    // an earlier kernel that gave up leaves the status set: then this one does nothing
+    *abort_flag = (*(volatile int*)&g_dev_status != 0) ? 1 : 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tmem_alloc(tmem_holder, Cfg::TMEM_COLS);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  const int num_tiles = *abort_flag ? 0 : p.tiles_m * p.tiles_n;
+  const int kblocks = (p.K + TB_K - 1) / TB_K;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % p.tiles_m) * TB_M;
+        const int n0 = (tile / p.tiles_m) * BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, 0x100 | stage, abort_flag)) { ok = false; break; }
+          uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
+          uint8_t* sb = sa + Cfg::A_BYTES;
+          mbar_expect_tx(&full[stage], Cfg::STAGE_BYTES);
+          const int k0 = kb * TB_K;
+          if (A_MN) {
+#pragma unroll
+            for (int i = 0; i < TB_M / 64; ++i) tma_load_2d(sa + i * 8192, &tmA, m0 + i * 64, k0, &full[stage]);
+          } else {
+            tma_load_2d(sa, &tmA, k0, m0, &full[stage]);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i) tma_load_2d(sb + i * 8192, &tmB, n0 + i * 64, k0, &full[stage]);
+          } else {
+            tma_load_2d(sb, &tmB, k0, n0, &full[stage]);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc_f16(TB_M, BN, sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1 : 0,
+                                                A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int buf = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(&acc_empty[buf], acc_phase ^ 1, 0x300 | buf, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&full[stage], phase, 0x200 | stage, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+          const uint32_t sb = sa + Cfg::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < TB_K / 16; ++k) {
+            // K-major: 16 elements = 32 bytes along the swizzled row; MN-major: 16 k-rows of 128 B
+            const uint64_t ad = A_MN ? smem_desc_sw128(sa + k * 2048, 8192, 1024)
+                                     : smem_desc_sw128(sa + k * 32, 16, 1024);
+            const uint64_t bd = B_MN ? smem_desc_sw128(sb + k * 2048, 8192, 1024)
+                                     : smem_desc_sw128(sb + k * 32, 16, 1024);
+            tc_mma_ss(d_tmem, ad, bd, idesc, (kb | k) ? 1u : 0u);
+          }
+          tc_commit(&empty[stage]);  // slot reusable once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        tc_commit(&acc_full[buf]);  // accumulator complete
+        buf ^= 1;
+        if (buf == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------------- epilogue
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    T* C = reinterpret_cast<T*>(p.C);
+    const T* bias = reinterpret_cast<const T*>(p.bias);
+    int buf = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int m0 = (tile % p.tiles_m) * TB_M;
+      const int n0 = (tile / p.tiles_m) * BN;
+      if (!mbar_wait(&acc_full[buf], acc_phase, 0x400 | buf, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c * 32, r);
+        tc_wait_ld();
+        const int col0 = n0 + c * 32;
+        if (row < p.M && col0 < p.N) {
+          T* dst = C + (int64_t)row * p.ldc + col0;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int col = col0 + v * 8;
+            if (col >= p.N) break;
+            float f[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
+            if (col + 8 <= p.N) {
+              if (bias) {
+                float b[8];
+                unpack8<T>(__ldg(reinterpret_cast<const uint4*>(bias + col)), b);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] += b[j];
+              }
+              if (p.relu) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = fmaxf(f[j], 0.f);
+              }
+              if (p.accumulate) {
+                float o[8];
+                unpack8<T>(*reinterpret_cast<const uint4*>(dst + v * 8), o);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] += o[j];
+              }
+              *reinterpret_cast<uint4*>(dst + v * 8) = pack8<T>(f);
+            } else {
+              for (int j = 0; j < 8 && col + j < p.N; ++j) {
+                float x = f[j];
+                if (bias) x += Num<T>::to_f(bias[col + j]);
+                if (p.relu) x = fmaxf(x, 0.f);
+                if (p.accumulate) x += Num<T>::to_f(dst[v * 8 + j]);
+                dst[v * 8 + j] = Num<T>::from_f(x);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      buf ^= 1;
+      if (buf == 0) acc_phase ^= 1;
+    }
+  }
+
+  // Unwind: every role has left its loop (normally or through a bounded wait).
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // give copies that may still be in flight time to land before the CTA's smem goes away
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                             const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                             CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeFn get_encoder() {
+  static EncodeFn fn = []() -> EncodeFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) return nullptr;
+    if (q != cudaDriverEntryPointSuccess) return nullptr;
+    return reinterpret_cast<EncodeFn>(p);
+  }();
+  return fn;
+}
+
+int encode_tmap_sw128(CUtensorMap* out, const void* base, int dtype, int rank, const uint64_t* dims,
+                      const uint64_t* strides_bytes, const uint32_t* box) {
+  EncodeFn enc = get_encoder();
+  if (!enc) return fail(TFB_ERR_DRIVER, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t gdim[5], gstr[5];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bx[i] = box[i];
+    es[i] = 1;
+    if (i + 1 < rank) gstr[i] = strides_bytes[i];
+  }
+  const CUtensorMapDataType dt = dtype == TFB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = enc(out, dt, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, bx, es,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(TFB_ERR_DRIVER, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return TFB_OK;
+}
+
+int gemm_tc05_status(int reset) { return read_dev_status(reset); }
+
+static int sm_count() {
+  static int n = []() {
+    int dev = 0, v = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    return v > 0 ? v : 148;
+  }();
+  return n;
+}
+
+template <typename T, int BN, bool A_MN, bool B_MN>
+static int launch_tc05(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t st) {
+  using Cfg = GemmCfg<BN>;
+  auto kern = gemm_tc05_kernel<T, BN, A_MN, B_MN>;
+  static bool attr_set = false;  // benign race: the call is idempotent
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return fail(TFB_ERR_LAUNCH, "gemm_tc05: smem attribute: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kern<<<grid, TB_THREADS, Cfg::SMEM_BYTES, st>>>(tmA, tmB, p);
+  return launched("gemm_tc05");
+}
+
+template <typename T, int BN>
+static int dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& tmA, const CUtensorMap& tmB,
+                          const GemmParams& p, cudaStream_t st) {
+  if (a_mn && b_mn) return launch_tc05<T, BN, true, true>(tmA, tmB, p, st);
+  if (a_mn) return launch_tc05<T, BN, true, false>(tmA, tmB, p, st);
+  if (b_mn) return launch_tc05<T, BN, false, true>(tmA, tmB, p, st);
+  return launch_tc05<T, BN, false, false>(tmA, tmB, p, st);
+}
+
+// Whether (ptr, strides) can be described by a TMA tensor map of 16-bit elements.
+static bool tma_ok(const void* ptr, int64_t s_outer) { return aligned16(ptr) && s_outer % 8 == 0 && s_outer > 0; }
+
+bool gemm_tc05_eligible(const void* a, const void* b, const void* c, const void* bias, int64_t M, int64_t N,
+                        int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int64_t ldc) {
+  if (M < 1 || N < 1 || K < 1) return false;
+  if (M >= (1LL << 31) || N >= (1LL << 31) || K >= (1LL << 31)) return false;
+  const bool a_ok = (a_sk == 1) ? tma_ok(a, a_sm) : (a_sm == 1 && tma_ok(a, a_sk));
+  const bool b_ok = (b_sk == 1) ? tma_ok(b, b_sn) : (b_sn == 1 && tma_ok(b, b_sk));
+  // A tensor of extent 1 along its strided dim still needs a legal stride; callers pass real strides.
+  return a_ok && b_ok && aligned16(c) && ldc % 8 == 0 && (bias == nullptr || aligned16(bias));
+}
+
+int gemm_tc05(const void* a, const void* b, void* c, const void* bias, int64_t M, int64_t N, int64_t K,
+              int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int64_t ldc, int relu, int accumulate,
+              int dtype, cudaStream_t st) {
+  const bool a_mn = (a_sk != 1);  // M contiguous
+  const bool b_mn = (b_sk != 1);  // N contiguous
+  // tile width: fewest "waves x tile cost" over the SMs
+  const int64_t tm = ceil_div(M, TB_M);
+  const int sms = sm_count();
+  const int64_t cost256 = ceil_div(tm * ceil_div(N, 256), sms) * 256;
+  const int64_t cost128 = ceil_div(tm * ceil_div(N, 128), sms) * 128;
+  const int BN = (N <= 128 || cost128 < cost256) ? 128 : 256;
+
+  CUtensorMap tmA, tmB;
+  int rc;
+  {
+    uint64_t dims[2], str[1];
+    uint32_t box[2];
+    if (a_mn) { dims[0] = (uint64_t)M; dims[1] = (uint64_t)K; str[0] = (uint64_t)a_sk * 2; box[0] = 64; box[1] = TB_K; }
+    else      { dims[0] = (uint64_t)K; dims[1] = (uint64_t)M; str[0] = (uint64_t)a_sm * 2; box[0] = TB_K; box[1] = TB_M; }
+    if ((rc = encode_tmap_sw128(&tmA, a, dtype, 2, dims, str, box))) return rc;
+    if (b_mn) { dims[0] = (uint64_t)N; dims[1] = (uint64_t)K; str[0] = (uint64_t)b_sk * 2; box[0] = 64; box[1] = TB_K; }
+    else      { dims[0] = (uint64_t)K; dims[1] = (uint64_t)N; str[0] = (uint64_t)b_sn * 2; box[0] = TB_K; box[1] = (uint32_t)BN; }
+    if ((rc = encode_tmap_sw128(&tmB, b, dtype, 2, dims, str, box))) return rc;
+  }
+  GemmParams p;
+  p.C = c; p.bias = bias; p.M = (int)M; p.N = (int)N; p.K = (int)K; p.ldc = ldc;
+  p.relu = relu; p.accumulate = accumulate;
+  p.tiles_m = (int)tm; p.tiles_n = (int)ceil_div(N, BN);
+  TFB_DISPATCH_16(dtype, T, {
+    if (BN == 256) return dispatch_major<T, 256>(a_mn, b_mn, tmA, tmB, p, st);
+    return dispatch_major<T, 128>(a_mn, b_mn, tmA, tmB, p, st);
+  })
+}
+
+}  // namespace tfb

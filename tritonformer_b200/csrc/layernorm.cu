@@ -1,0 +1,312 @@
+// LayerNorm forward / backward for sm_100a: HBM-bound, 128-bit accesses, fp32 math.
+//
+// Forward : one warp per row, the row held in registers between the mean, variance and
+//           write passes, so x is read once and y written once (4 bytes / element).
+// Backward: a CTA owns all columns (8 per thread) and walks groups of rows; it writes dx
+//           and keeps the per-column sums for dalpha / dbeta in registers, which leave the
+//           CTA once as fp32 partial rows.  finalize_partials() folds those rows.
+#include "common.cuh"
+
+namespace tfb {
+
+// ------------------------------------------------------------------------------ forward
+template <typename T, int NV>
+__global__ void __launch_bounds__(128) ln_fwd_vec_kernel(
+    const T* __restrict__ x, const T* __restrict__ alpha, const T* __restrict__ beta,
+    T* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd,
+    int64_t rows, int d, int64_t x_ld, int64_t y_ld, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int nvec = d >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * x_ld);
+  float v[NV][8];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = i * 32 + lane;
+    if (c < nvec) {
+      unpack8<T>(ld_stream16(xr + c), v[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s += v[i][j];
+    }
+  }
+  const float mu = warp_sum(s) / (float)d;
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    if (i * 32 + lane < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float t = v[i][j] - mu;
+        q += t * t;
+      }
+    }
+  }
+  const float rs = rsqrtf(warp_sum(q) / (float)d + eps);
+  if (lane == 0) {
+    mean[row] = mu;
+    rstd[row] = rs;
+  }
+  uint4* yr = reinterpret_cast<uint4*>(y + row * y_ld);
+  const uint4* av = reinterpret_cast<const uint4*>(alpha);
+  const uint4* bv = reinterpret_cast<const uint4*>(beta);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = i * 32 + lane;
+    if (c < nvec) {
+      float a[8], b[8], o[8];
+      unpack8<T>(__ldg(av + c), a);
+      unpack8<T>(__ldg(bv + c), b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = a[j] * ((v[i][j] - mu) * rs) + b[j];
+      st_stream16(yr + c, pack8<T>(o));
+    }
+  }
+}
+
+// Any d, any alignment: the row is re-read (from L1/L2) for each pass.
+template <typename T>
+__global__ void __launch_bounds__(128) ln_fwd_generic_kernel(
+    const T* __restrict__ x, const T* __restrict__ alpha, const T* __restrict__ beta,
+    T* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd,
+    int64_t rows, int d, int64_t x_ld, int64_t y_ld, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const T* xr = x + row * x_ld;
+  float s = 0.f;
+  for (int c = lane; c < d; c += 32) s += Num<T>::to_f(xr[c]);
+  const float mu = warp_sum(s) / (float)d;
+  float q = 0.f;
+  for (int c = lane; c < d; c += 32) {
+    const float t = Num<T>::to_f(xr[c]) - mu;
+    q += t * t;
+  }
+  const float rs = rsqrtf(warp_sum(q) / (float)d + eps);
+  if (lane == 0) {
+    mean[row] = mu;
+    rstd[row] = rs;
+  }
+  T* yr = y + row * y_ld;
+  for (int c = lane; c < d; c += 32)
+    yr[c] = Num<T>::from_f(Num<T>::to_f(alpha[c]) * ((Num<T>::to_f(xr[c]) - mu) * rs) +
+                           Num<T>::to_f(beta[c]));
+}
+
+// ----------------------------------------------------------------------------- backward
+constexpr int LN_RB = 4;  // rows per CTA iteration
+
+template <typename T, bool VEC, int MAXT>
+__global__ void __launch_bounds__(MAXT) ln_bwd_kernel(
+    const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ alpha,
+    const float* __restrict__ mean, const float* __restrict__ rstd, T* __restrict__ dx,
+    float* __restrict__ partials, int64_t rows, int d, int64_t dy_ld, int64_t x_ld,
+    int64_t dx_ld) {
+  __shared__ float red[2][32][2 * LN_RB];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nwarp = blockDim.x >> 5;
+  const int c0 = tid * 8;
+  const bool active = c0 < d;
+  const int ncol = active ? min(8, d - c0) : 0;  // < 8 only on the scalar path
+
+  float a[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) a[j] = (j < ncol) ? Num<T>::to_f(alpha[c0 + j]) : 0.f;
+  float acc_a[8], acc_b[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc_a[j] = acc_b[j] = 0.f;
+
+  const float inv_d = 1.f / (float)d;
+  int buf = 0;
+  for (int64_t r0 = (int64_t)blockIdx.x * LN_RB; r0 < rows; r0 += (int64_t)gridDim.x * LN_RB) {
+    float xh[LN_RB][8], g[LN_RB][8];
+    float s[2 * LN_RB];
+#pragma unroll
+    for (int r = 0; r < LN_RB; ++r) {
+      const int64_t row = r0 + r;
+      s[2 * r] = s[2 * r + 1] = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) xh[r][j] = g[r][j] = 0.f;
+      if (row < rows && active) {
+        float xv[8], dv[8];
+        if (VEC) {
+          unpack8<T>(ld_stream16(x + row * x_ld + c0), xv);
+          unpack8<T>(ld_stream16(dy + row * dy_ld + c0), dv);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            xv[j] = (j < ncol) ? Num<T>::to_f(x[row * x_ld + c0 + j]) : 0.f;
+            dv[j] = (j < ncol) ? Num<T>::to_f(dy[row * dy_ld + c0 + j]) : 0.f;
+          }
+        }
+        const float mu = __ldg(mean + row), rs = __ldg(rstd + row);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float h = (j < ncol) ? (xv[j] - mu) * rs : 0.f;
+          xh[r][j] = h;
+          g[r][j] = dv[j] * a[j];
+          acc_a[j] += dv[j] * h;
+          acc_b[j] += dv[j];
+          s[2 * r] += g[r][j] * h;
+          s[2 * r + 1] += g[r][j];
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 2 * LN_RB; ++i) s[i] = warp_sum(s[i]);
+    if (lane == 0) {
+#pragma unroll
+      for (int i = 0; i < 2 * LN_RB; ++i) red[buf][warp][i] = s[i];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 2 * LN_RB; ++i) {
+      float t = 0.f;
+      for (int w = 0; w < nwarp; ++w) t += red[buf][w][i];
+      s[i] = t * inv_d;
+    }
+    buf ^= 1;
+#pragma unroll
+    for (int r = 0; r < LN_RB; ++r) {
+      const int64_t row = r0 + r;
+      if (row < rows && active) {
+        const float rs = __ldg(rstd + row);
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rs * (g[r][j] - xh[r][j] * s[2 * r] - s[2 * r + 1]);
+        if (VEC) {
+          st_stream16(dx + row * dx_ld + c0, pack8<T>(o));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (j < ncol) dx[row * dx_ld + c0 + j] = Num<T>::from_f(o[j]);
+        }
+      }
+    }
+  }
+  if (active) {
+    float* pa = partials + (int64_t)blockIdx.x * 2 * d;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (j < ncol) {
+        pa[c0 + j] = acc_a[j];
+        pa[d + c0 + j] = acc_b[j];
+      }
+    }
+  }
+}
+
+// out0[c] (c < split) / out1[c - split] = sum over n rows of partials[r, c]; ncols total.
+template <typename T>
+__global__ void __launch_bounds__(256) finalize_partials_kernel(
+    const float* __restrict__ partials, int64_t n, int ncols, int split, T* __restrict__ out0,
+    T* __restrict__ out1) {
+  __shared__ float sm[8][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
+  float s = 0.f;
+  if (c < ncols)
+    for (int64_t r = ry; r < n; r += 8) s += partials[r * ncols + c];
+  sm[ry][cx] = s;
+  __syncthreads();
+  if (ry == 0 && c < ncols) {
+#pragma unroll
+    for (int i = 1; i < 8; ++i) s += sm[i][cx];
+    if (c < split) out0[c] = Num<T>::from_f(s);
+    else out1[c - split] = Num<T>::from_f(s);
+  }
+}
+
+template <typename T>
+int finalize_partials(const float* partials, int64_t n, int ncols, int split, void* out0,
+                      void* out1, cudaStream_t st) {
+  finalize_partials_kernel<T><<<(unsigned)ceil_div(ncols, 32), 256, 0, st>>>(
+      partials, n, ncols, split, (T*)out0, (T*)out1);
+  return launched("finalize_partials");
+}
+template int finalize_partials<__half>(const float*, int64_t, int, int, void*, void*, cudaStream_t);
+template int finalize_partials<__nv_bfloat16>(const float*, int64_t, int, int, void*, void*, cudaStream_t);
+
+static int ln_bwd_threads(int64_t d) { return (int)(ceil_div(ceil_div(d, 8), 32) * 32); }
+
+template <typename T>
+static int ln_bwd_launch(const void* dy, const void* x, const void* alpha, const float* mean,
+                         const float* rstd, void* dx, void* dalpha, void* dbeta, float* partials,
+                         int64_t n_partials, int64_t rows, int d, int64_t dy_ld, int64_t x_ld,
+                         int64_t dx_ld, bool vec, int threads, cudaStream_t st) {
+#define TFB_LN_BWD(V, MT)                                                                     \
+  ln_bwd_kernel<T, V, MT><<<(unsigned)n_partials, threads, 0, st>>>(                          \
+      (const T*)dy, (const T*)x, (const T*)alpha, mean, rstd, (T*)dx, partials, rows, d, dy_ld, \
+      x_ld, dx_ld)
+  if (vec && threads <= 256) TFB_LN_BWD(true, 256);
+  else if (vec) TFB_LN_BWD(true, 1024);
+  else if (threads <= 256) TFB_LN_BWD(false, 256);
+  else TFB_LN_BWD(false, 1024);
+#undef TFB_LN_BWD
+  int rc = launched("layernorm_bwd");
+  if (rc) return rc;
+  return finalize_partials<T>(partials, n_partials, 2 * d, d, dalpha, dbeta, st);
+}
+
+}  // namespace tfb
+
+using namespace tfb;
+
+extern "C" int tfb_layernorm_fwd(const void* x, const void* alpha, const void* beta, void* y,
+                                 float* mean, float* rstd, int64_t rows, int64_t d, int64_t x_ld,
+                                 int64_t y_ld, float eps, int dtype, void* stream) {
+  TFB_REQUIRE(rows >= 0 && d > 0 && d < (1 << 30), "layernorm_fwd: bad shape rows=%lld d=%lld",
+              (long long)rows, (long long)d);
+  TFB_REQUIRE(x_ld >= d && y_ld >= d, "layernorm_fwd: row stride smaller than d");
+  if (rows == 0) return TFB_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const unsigned grid = (unsigned)ceil_div(rows, 4);
+  const bool vec = (d % 8 == 0) && (x_ld % 8 == 0) && (y_ld % 8 == 0) && aligned16(x) &&
+                   aligned16(y) && aligned16(alpha) && aligned16(beta) && d <= 2048;
+  TFB_DISPATCH_16(dtype, T, {
+    const T *xp = (const T*)x, *ap = (const T*)alpha, *bp = (const T*)beta;
+    T* yp = (T*)y;
+    if (!vec) {
+      ln_fwd_generic_kernel<T><<<grid, 128, 0, st>>>(xp, ap, bp, yp, mean, rstd, rows, (int)d, x_ld, y_ld, eps);
+    } else if (d <= 256) {
+      ln_fwd_vec_kernel<T, 1><<<grid, 128, 0, st>>>(xp, ap, bp, yp, mean, rstd, rows, (int)d, x_ld, y_ld, eps);
+    } else if (d <= 512) {
+      ln_fwd_vec_kernel<T, 2><<<grid, 128, 0, st>>>(xp, ap, bp, yp, mean, rstd, rows, (int)d, x_ld, y_ld, eps);
+    } else if (d <= 1024) {
+      ln_fwd_vec_kernel<T, 4><<<grid, 128, 0, st>>>(xp, ap, bp, yp, mean, rstd, rows, (int)d, x_ld, y_ld, eps);
+    } else {
+      ln_fwd_vec_kernel<T, 8><<<grid, 128, 0, st>>>(xp, ap, bp, yp, mean, rstd, rows, (int)d, x_ld, y_ld, eps);
+    }
+  })
+  return launched("layernorm_fwd");
+}
+
+extern "C" int64_t tfb_layernorm_bwd_partials(int64_t rows, int64_t d) {
+  (void)d;
+  int64_t n = ceil_div(rows, LN_RB);
+  const int64_t cap = 148 * 4;
+  if (n > cap) n = cap;
+  return n < 1 ? 1 : n;
+}
+
+extern "C" int tfb_layernorm_bwd(const void* dy, const void* x, const void* alpha,
+                                 const float* mean, const float* rstd, void* dx, void* dalpha,
+                                 void* dbeta, float* partials, int64_t n_partials, int64_t rows,
+                                 int64_t d, int64_t dy_ld, int64_t x_ld, int64_t dx_ld, int dtype,
+                                 void* stream) {
+  TFB_REQUIRE(rows > 0 && d > 0, "layernorm_bwd: bad shape rows=%lld d=%lld", (long long)rows,
+              (long long)d);
+  if (d > 8192) return fail(TFB_ERR_UNSUPPORTED, "layernorm_bwd: d=%lld > 8192", (long long)d);
+  TFB_REQUIRE(n_partials == tfb_layernorm_bwd_partials(rows, d),
+              "layernorm_bwd: scratch must hold tfb_layernorm_bwd_partials() rows");
+  TFB_REQUIRE(dy_ld >= d && x_ld >= d && dx_ld >= d, "layernorm_bwd: row stride smaller than d");
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool vec = (d % 8 == 0) && (x_ld % 8 == 0) && (dy_ld % 8 == 0) && (dx_ld % 8 == 0) &&
+                   aligned16(x) && aligned16(dy) && aligned16(dx);
+  const int threads = ln_bwd_threads(d);
+  TFB_DISPATCH_16(dtype, T, {
+    return ln_bwd_launch<T>(dy, x, alpha, mean, rstd, dx, dalpha, dbeta, partials, n_partials, rows,
+                            (int)d, dy_ld, x_ld, dx_ld, vec, threads, st);
+  })
+}

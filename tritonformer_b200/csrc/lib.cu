@@ -1,0 +1,58 @@
+// Library-wide state of the tritonformer_b200 C ABI: version, last error, launch counter,
+// test switches, and the GEMM entry point that picks between the two GEMM kernels.
+#include "common.cuh"
+
+namespace tfb {
+thread_local char g_err[512] = {0};
+std::atomic<int64_t> g_launches{0};
+std::atomic<int> g_force_generic_gemm{0};
+std::atomic<int> g_force_fallback_attn{0};
+
+int gemm_generic(const void*, const void*, void*, const void*, int64_t, int64_t, int64_t, int64_t, int64_t,
+                 int64_t, int64_t, int64_t, int, int, int, cudaStream_t);
+int gemm_tc05(const void*, const void*, void*, const void*, int64_t, int64_t, int64_t, int64_t, int64_t,
+              int64_t, int64_t, int64_t, int, int, int, cudaStream_t);
+bool gemm_tc05_eligible(const void*, const void*, const void*, const void*, int64_t, int64_t, int64_t, int64_t,
+                        int64_t, int64_t, int64_t, int64_t);
+int gemm_tc05_status(int reset);
+int attn_tc05_status(int reset);
+}  // namespace tfb
+
+using namespace tfb;
+
+extern "C" int tfb_version(void) { return 1; }
+extern "C" const char* tfb_last_error(void) { return g_err; }
+extern "C" int64_t tfb_launch_count(void) { return g_launches.load(); }
+
+extern "C" int tfb_device_status(int reset) {
+  cudaDeviceSynchronize();
+  const int a = gemm_tc05_status(reset);
+  const int b = attn_tc05_status(reset);
+  return a ? a : b;
+}
+
+extern "C" void tfb_debug_set(int key, int value) {
+  if (key == 0) g_force_generic_gemm.store(value);
+  if (key == 1) g_force_fallback_attn.store(value);
+}
+
+extern "C" int tfb_gemm(const void* a, const void* b, void* c, const void* bias, int64_t M, int64_t N,
+                        int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int64_t ldc,
+                        int relu, int accumulate, int dtype, void* stream, int* path) {
+  TFB_REQUIRE(M >= 0 && N >= 0 && K >= 0, "gemm: negative dimension");
+  TFB_REQUIRE(M < (1LL << 31) && N < (1LL << 31) && K < (1LL << 31), "gemm: dimension exceeds 2^31");
+  TFB_REQUIRE(a_sm == 1 || a_sk == 1, "gemm: A needs a unit stride (a_sm=%lld a_sk=%lld)", (long long)a_sm,
+              (long long)a_sk);
+  TFB_REQUIRE(b_sk == 1 || b_sn == 1, "gemm: B needs a unit stride (b_sk=%lld b_sn=%lld)", (long long)b_sk,
+              (long long)b_sn);
+  TFB_REQUIRE(ldc >= N, "gemm: ldc=%lld smaller than N=%lld", (long long)ldc, (long long)N);
+  TFB_REQUIRE(dtype == TFB_F16 || dtype == TFB_BF16, "gemm: dtype %d: expected fp16 or bf16", dtype);
+  if (M == 0 || N == 0) return TFB_OK;
+  TFB_REQUIRE(K > 0, "gemm: empty contraction");
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool fast = !g_force_generic_gemm.load() &&
+                    gemm_tc05_eligible(a, b, c, bias, M, N, K, a_sm, a_sk, b_sk, b_sn, ldc);
+  if (path) *path = fast ? 1 : 0;
+  if (fast) return gemm_tc05(a, b, c, bias, M, N, K, a_sm, a_sk, b_sk, b_sn, ldc, relu, accumulate, dtype, st);
+  return gemm_generic(a, b, c, bias, M, N, K, a_sm, a_sk, b_sk, b_sn, ldc, relu, accumulate, dtype, st);
+}

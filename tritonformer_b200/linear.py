@@ -1,0 +1,171 @@
+"""Linear autograd Functions (drop-in for tritonformer/linear.py:10-102).
+
+Weights are stored (in_features, out_features) and applied as x @ W.  Every product -- forward,
+input gradient and weight gradient -- is one call of the same GEMM entry point with different
+operand strides; the weight gradient contracts over all B*T rows at once in fp32 instead of
+producing per-batch partials and summing them.  Bias and ReLU are applied in the GEMM epilogue.
+The incoming gradient is never modified (the reference masks it in place).
+"""
+import ctypes
+
+import torch
+from torch.autograd import Function
+
+from . import _lib
+from ._amp import amp_backward, amp_forward
+
+
+def _as_rows(x: torch.Tensor) -> torch.Tensor:
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(1) != 1 and x2.stride(0) != 1:
+        x2 = x2.contiguous()
+    return x2
+
+
+def gemm(a, a_sm, a_sk, b, b_sk, b_sn, m, n, k, bias=None, relu=False, out=None, accumulate=False):
+    """C[m,n] = act(sum_k A(m,k) B(k,n) + bias) with element strides for A and B."""
+    if out is None:
+        out = torch.empty((m, n), device=a.device, dtype=a.dtype)
+    path = ctypes.c_int(0)
+    _lib.check(_lib.lib.tfb_gemm(
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), bias.data_ptr() if bias is not None else None,
+        m, n, k, a_sm, a_sk, b_sk, b_sn, out.stride(0), 1 if relu else 0, 1 if accumulate else 0,
+        _lib.dtype_code(a.dtype), _lib.stream_ptr(a.device), ctypes.byref(path)))
+    return out
+
+
+def _check_linear(x, w, bias):
+    assert x.is_cuda and w.is_cuda, "Linear expects CUDA tensors"
+    assert x.dim() >= 2 and w.dim() == 2, "Incorrect number of dimensions for LHS or RHS"
+    assert x.shape[-1] == w.shape[0], (
+        f"Dimension mismatch. Expected a.shape[2] ({x.shape[-1]}) to be equal to b.shape[0] ({w.shape[0]})")
+    assert x.dtype in (torch.float16, torch.bfloat16) and w.dtype == x.dtype, "Linear expects matching fp16/bf16"
+    if bias is not None:
+        assert bias.dtype == x.dtype and bias.numel() == w.shape[1], "bias must be (out_features,)"
+
+
+def linear_forward(x, w, bias, relu):
+    _check_linear(x, w, bias)
+    x2 = _as_rows(x)
+    if w.stride(0) != 1 and w.stride(1) != 1:
+        w = w.contiguous()
+    m, k = x2.shape
+    n = w.shape[1]
+    y = gemm(x2, x2.stride(0), x2.stride(1), w, w.stride(0), w.stride(1), m, n, k,
+             bias=bias.contiguous() if bias is not None else None, relu=relu)
+    return y.view(*x.shape[:-1], n)
+
+
+def linear_backward(dy, x, w, need_dx=True, need_dw=True):
+    """dX = dY Wᵀ, dW = Xᵀ dY (contraction over every row of the flattened batch)."""
+    x2, dy2 = _as_rows(x), _as_rows(dy)
+    m, k = x2.shape
+    n = w.shape[1]
+    dx = dw = None
+    if need_dx:
+        # B(kk, nn) = W[nn, kk]
+        dx = gemm(dy2, dy2.stride(0), dy2.stride(1), w, w.stride(1), w.stride(0), m, k, n).view(x.shape)
+    if need_dw:
+        # A(mm, kk) = X[kk, mm]
+        dw = gemm(x2, x2.stride(1), x2.stride(0), dy2, dy2.stride(0), dy2.stride(1), k, n, m)
+    return dx, dw
+
+
+def relu_backward(dy, act):
+    dy = dy.contiguous()
+    act = act.contiguous()
+    dz = torch.empty_like(dy)
+    _lib.check(_lib.lib.tfb_relu_bwd(dy.data_ptr(), act.data_ptr(), dz.data_ptr(), dy.numel(),
+                                     _lib.dtype_code(dy.dtype), _lib.stream_ptr(dy.device)))
+    return dz
+
+
+def column_sum(x):
+    """Sum over every leading dimension -> (last_dim,), fp32 accumulation."""
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    rows, cols = x2.shape
+    out = torch.empty((cols,), device=x.device, dtype=x.dtype)
+    n = _lib.lib.tfb_colsum_partials(rows, cols)
+    partials = torch.empty((n, cols), device=x.device, dtype=torch.float32)
+    _lib.check(_lib.lib.tfb_colsum(x2.data_ptr(), out.data_ptr(), partials.data_ptr(), n, rows, cols,
+                                   x2.stride(0) if rows > 1 else cols, _lib.dtype_code(x.dtype),
+                                   _lib.stream_ptr(x.device)))
+    return out
+
+
+def _backward(ctx, grad_output, has_bias, has_relu):
+    if has_relu:
+        x, w, act = ctx.saved_tensors
+        dz = relu_backward(grad_output.to(x.dtype), act)
+    else:
+        x, w = ctx.saved_tensors
+        dz = grad_output.to(x.dtype)
+    dx, dw = linear_backward(dz, x, w, ctx.needs_input_grad[0], ctx.needs_input_grad[1])
+    if not has_bias:
+        return dx, dw
+    db = column_sum(dz) if ctx.needs_input_grad[2] else None
+    return dx, dw, db
+
+
+class LinearNoBias(Function):
+    """y = x @ W"""
+
+    @staticmethod
+    @amp_forward
+    def forward(ctx, input, weight):
+        ctx.save_for_backward(input, weight)
+        return linear_forward(input, weight, None, False)
+
+    @staticmethod
+    @amp_backward
+    def backward(ctx, grad_output):
+        return _backward(ctx, grad_output, False, False)
+
+
+class LinearBias(Function):
+    """y = x @ W + b"""
+
+    @staticmethod
+    @amp_forward
+    def forward(ctx, input, weight, bias):
+        ctx.save_for_backward(input, weight)
+        return linear_forward(input, weight, bias, False)
+
+    @staticmethod
+    @amp_backward
+    def backward(ctx, grad_output):
+        return _backward(ctx, grad_output, True, False)
+
+
+class LinearNoBiasReLU(Function):
+    """y = relu(x @ W)"""
+
+    @staticmethod
+    @amp_forward
+    def forward(ctx, input, weight):
+        out = linear_forward(input, weight, None, True)
+        ctx.save_for_backward(input, weight, out)
+        return out
+
+    @staticmethod
+    @amp_backward
+    def backward(ctx, grad_output):
+        return _backward(ctx, grad_output, False, True)
+
+
+class LinearBiasReLU(Function):
+    """y = relu(x @ W + b)"""
+
+    @staticmethod
+    @amp_forward
+    def forward(ctx, input, weight, bias):
+        out = linear_forward(input, weight, bias, True)
+        ctx.save_for_backward(input, weight, out)
+        return out
+
+    @staticmethod
+    @amp_backward
+    def backward(ctx, grad_output):
+        return _backward(ctx, grad_output, True, True)
