@@ -1,0 +1,357 @@
+#!/usr/bin/env python
+"""Forward+backward throughput of the transformer on the tritonformer_b200 kernels.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config 410m|840m|1.4b] [--impl b200|reference]
+
+One process per GPU (torchrun sets RANK/LOCAL_RANK/WORLD_SIZE for N > 1).  A step is one
+`model(tokens, tokens)` + `loss.backward()` under autocast on synthetic tokens, plus, for N > 1, the
+gradient all-reduce; per-GPU batch is fixed (weak scaling).  Rank 0 prints ONE JSON line.
+
+`--impl reference` times the fp32 plain-PyTorch restatement of the reference model (oracle/) on the
+host cores, on a bounded sample of the same configuration, and prints the same line shape.
+"""
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CONFIGS = {
+    # name: (d_model, layers, heads, ffn, vocab, ctx, batch/GPU, dtype, linear bias, ALiBi)
+    "410m": (1024, 24, 16, 4096, 50304, 2048, 4, "fp16", False, False),
+    "840m": (1536, 24, 12, 6144, 50304, 4096, 1, "fp16", False, False),
+    "1.4b": (2048, 24, 16, 8192, 50304, 2048, 2, "bf16", True, True),
+}
+METRIC = "fwd+bwd tokens/s, 410M ctx2048 fp16 AMP"
+
+
+def make_config(name):
+    from tritonformer_b200.transformer import TransformerConfig
+    d, L, H, ffn, V, T, B, dt, lb, ab = CONFIGS[name]
+    cfg = TransformerConfig(vocab_size=V, hidden_size=d, max_position_embeddings=T, num_attention_heads=H,
+                            head_dim=d // H, ffn_dim=ffn, num_hidden_layers=L, use_linear_bias=lb, attn_bias=ab)
+    return cfg, B, T, (torch.float16 if dt == "fp16" else torch.bfloat16)
+
+
+def algorithmic_flops(cfg, batch, seq):
+    """fwd+bwd FLOPs per step: 6*tok*P_mm (every linear incl. the LM head over all positions) plus
+    causal attention at half cost (2 products forward, 5 backward)."""
+    d, L, ffn, V = cfg.hidden_size, cfg.num_hidden_layers, cfg.ffn_dim, cfg.vocab_size
+    hd = d // cfg.num_attention_heads
+    p_mm = L * (4 * d * d + 2 * d * ffn) + d * V
+    return 6.0 * batch * seq * p_mm + 7.0 * L * batch * cfg.num_attention_heads * seq * seq * hd
+
+
+def common_flops(cfg, batch, seq, n_params):
+    """The widespread 6*N*tok + 12*L*d*T*tok convention (printed for comparison only)."""
+    return 6.0 * n_params * batch * seq + 12.0 * cfg.num_hidden_layers * cfg.hidden_size * seq * batch * seq
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"tflops": p.get("bf16_tflops_sustained", 1400.5), "tflops_burst": p.get("bf16_tflops", 1652.3),
+                "hbm_gbs": p.get("hbm_gbs", 6535.4), "source": "measured"}
+    return {"tflops": 1400.0, "tflops_burst": 1590.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+            except ValueError:
+                continue
+            for nm, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------- CPU baseline
+def cpu_reference_step_time(config_name, steps, warmup, sample_batch=1, sample_seq=512):
+    """Seconds per fwd+bwd step of the fp32 oracle model on the host cores, on a bounded sample
+    (sample_batch x sample_seq tokens) of the configuration."""
+    from oracle.model import OracleTransformer, init_weights
+    cfg, _, _, _ = make_config(config_name)
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    gen = torch.Generator().manual_seed(1234)
+    model = OracleTransformer(cfg)
+    init_weights(model, cfg.num_hidden_layers, lm_head_std=0.02, generator=gen)
+    ids = torch.randint(0, cfg.vocab_size, (sample_batch, sample_seq), generator=gen)
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        _, loss = model(ids, ids)
+        loss.backward()
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    return statistics.median(times), cores, cfg, sample_batch, sample_seq
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 6))
+    warmup = max(1, min(args.warmup, 2))
+    t, cores, cfg, sb, ss = cpu_reference_step_time(args.config, steps, warmup)
+    tok_s = sb * ss / t
+    sample = f"{args.config} model, {sb}x{ss} tokens per step, {steps} timed steps (bounded sample of the workload)"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tok_s, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{args.config} fwd+bwd, CPU fp32 restatement of the reference model", "sample": sample},
+        "tflops": algorithmic_flops(cfg, sb, ss) / t / 1e12,
+        "cpu_baseline": {"value": tok_s, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------- GPU arm
+def build_model(cfg, dtype, device, seed=1234):
+    """Random-init weights of the architecture: N(0, 0.02) everywhere incl. the LM head
+    (the reference init zeroes the head, which would zero every other gradient)."""
+    from tritonformer_b200.transformer import Transformer
+    torch.manual_seed(seed)
+    model = Transformer(cfg, device=device)
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    with torch.no_grad():
+        w = model.logits_out.weight
+        w.copy_(torch.empty(w.shape).normal_(0.0, 0.02, generator=gen).to(w.dtype))
+        if cfg.use_linear_bias:
+            for n, p in model.named_parameters():
+                if n.endswith("bias") and "layernorm" not in n:
+                    p.copy_(torch.empty(p.shape).normal_(0.0, 0.02, generator=gen).to(p.dtype))
+    if dtype is torch.bfloat16:
+        table = model.attn_bias
+        model = model.to(torch.bfloat16)
+        if table is not None:
+            model.attn_bias = table  # the ALiBi table keeps the reference's fp16 rounding
+    return model
+
+
+def run_b200_arm(args):
+    import tritonformer_b200._lib as L
+    from tritonformer_b200 import linear as tlinear
+    from tritonformer_b200.dp import GradBuckets, broadcast_parameters
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device: there is no CPU fallback"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    cfg, B, T, dtype = make_config(args.config)
+    model = build_model(cfg, dtype, dev)
+    broadcast_parameters(model)
+    n_params = sum(p.numel() for p in model.parameters())
+    buckets = GradBuckets(model.parameters())
+    loss_scale = 4096.0 if dtype is torch.float16 else 1.0
+
+    gen = torch.Generator().manual_seed(1234 + rank)
+    host_tokens = [torch.randint(0, cfg.vocab_size, (B, T), generator=gen).pin_memory() for _ in range(4)]
+    static_ids = torch.empty((B, T), dtype=torch.int64, device=dev)
+    static_ids.copy_(host_tokens[0])
+    static_loss = torch.zeros((), device=dev, dtype=torch.float32)
+
+    def step(ids):
+        with torch.autocast("cuda", dtype=dtype):
+            _, loss = model(ids, ids)
+        (loss * loss_scale).backward()
+        return loss.detach()
+
+    # eager warm-up (also fills every per-shape cache before graph capture)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            step(static_ids)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    buckets.check_views()
+
+    graph = None
+    launches_per_step = None
+    if not args.no_graph:
+        graph = torch.cuda.CUDAGraph()
+        n0 = L.launch_count()
+        with torch.cuda.graph(graph):
+            static_loss.copy_(step(static_ids))
+        launches_per_step = L.launch_count() - n0
+    else:
+        n0 = L.launch_count()
+        step(static_ids)
+        launches_per_step = L.launch_count() - n0
+
+    def run_step():
+        if graph is not None:
+            graph.replay()
+        else:
+            static_loss.copy_(step(static_ids))
+        buckets.all_reduce_mean()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        run_step()
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        run_step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    clocks = sampler.stop() if sampler else None
+    buckets.check_views()
+
+    # end to end through the public API: pinned host tokens in, loss value out, every step
+    barrier()
+    t0 = time.perf_counter()
+    last = 0.0
+    for i in range(args.steps):
+        static_ids.copy_(host_tokens[i % len(host_tokens)], non_blocking=True)
+        run_step()
+        last = float(static_loss.item())
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = t.tolist()
+
+    # dominant kernel family (the GEMMs) timed live, one eager step with events around every call
+    roof = None
+    if rank == 0:
+        peaks = measured_peaks()
+        recs = []
+        tlinear.PROFILE = recs
+        step(static_ids)
+        tlinear.PROFILE = None
+        torch.cuda.synchronize()
+        gflop = sum(r[0] for r in recs)
+        gms = sum(r[1].elapsed_time(r[2]) for r in recs)
+        achieved = gflop / (gms * 1e-3) / 1e12 if gms > 0 else 0.0
+        roof = {"bound": "tensor", "kernel": "gemm_tc05_kernel (all linear fwd/dX/dW products of one step)",
+                "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
+                "traffic": None, "launches": len(recs), "peak_source": peaks["source"] + " sustained bf16 cuBLAS",
+                "gemm_ms_per_step": gms}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        t_cpu, cores, _, sb, ss = cpu_reference_step_time(args.config, 2, 1)
+        cpu = {"value": sb * ss / t_cpu, "unit": "tokens/s", "cores": cores, "kind": "port",
+               "sample": f"{args.config} model, {sb}x{ss} tokens per step, 2 timed steps, fp32 oracle on host cores"}
+
+    if rank == 0:
+        flops = algorithmic_flops(cfg, B, T)
+        tok_s = world * B * T / (ms * 1e-3)
+        tflops_gpu = flops / (ms * 1e-3) / 1e12
+        line = {
+            "metric": METRIC if args.config == "410m" else f"fwd+bwd tokens/s, {args.config}",
+            "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "fp16" if dtype is torch.float16 else "bf16", "data": "synthetic",
+            "config": {"workload": f"{args.config} GPT fwd+bwd: d{cfg.hidden_size} L{cfg.num_hidden_layers} "
+                                   f"H{cfg.num_attention_heads} ffn{cfg.ffn_dim} V{cfg.vocab_size} ctx{T} batch{B}/GPU",
+                       "global_batch": world * B, "seq_len": T, "parallelism": f"dp{world}",
+                       "cuda_graph": graph is not None, "loss_scale": loss_scale,
+                       "l2": "working set per step (>= 0.8 GB of weights plus activations) exceeds the 126 MB L2"},
+            "tflops_per_gpu": tflops_gpu,
+            "frac_of_measured_bf16_peak": tflops_gpu / measured_peaks()["tflops"],
+            "frac_of_nominal_fp16_peak": tflops_gpu / 2250.0,
+            "tflops_per_gpu_6N_convention": common_flops(cfg, B, T, n_params) / (ms * 1e-3) / 1e12,
+            "readme_rtx3090_tflops": 50.1719 if args.config == "410m" else None,
+            "loss": last,
+            "clocks": clocks,
+            "e2e": {"value": world * B * T / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": B * T * 8, "d2h_bytes_per_step": 4},
+            "gpu_launches": int(launches_per_step * args.steps),
+            "launches_per_step": int(launches_per_step),
+            "roofline": roof,
+            "cpu_baseline": cpu,
+            "device_status": L.device_status(),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--config", default="410m", choices=sorted(CONFIGS))
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_b200_arm(args)
+
+
+if __name__ == "__main__":
+    main()

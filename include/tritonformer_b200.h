@@ -130,10 +130,10 @@ int tfb_gemm(const void* a, const void* b, void* c, const void* bias,
  * (tritonformer/kernels/attention.py:9-217, kernels/biased_attention.py:9-245).
  * q,k,v,o: (B,H,T,hd) with element strides {b,h,t} each and unit stride on hd.
  * Causal. Optional additive bias, one of:
- *   slopes != NULL : ALiBi, bias(i,j) = -slope[h]*(i-j), slopes fp32 (H,).  If
- *                    alibi_round != 0 the product is rounded the way the reference table is
- *                    built (element dtype product of rounded distance and rounded slope,
- *                    transformer.py:55-75).
+ *   slopes != NULL : ALiBi, bias(i,j) = -slope[h]*(i-j), slopes fp32 (H,).  With
+ *                    alibi_round = 1 (fp16) or 2 (bf16) each entry is rebuilt the way the
+ *                    reference table is (transformer.py:55-75): distance and slope rounded
+ *                    to that type and multiplied in it; 0 = exact fp32 product.
  *   bias != NULL   : dense (H,T,T) table of dtype `dtype`, element strides bias_sh, bias_si,
  *                    unit stride on j (entries above the diagonal are ignored).
  * lse: (B,H,T) fp32 contiguous = natural-log-sum-exp of the scaled, biased scores.  */

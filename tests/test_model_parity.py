@@ -1,0 +1,113 @@
+"""GPU parity of the whole model: logits, loss and every parameter gradient of the CUDA path against
+the fp32 oracle model on identical (already rounded) weights and tokens.
+
+Tolerances: loss |d|/|ref| <= 1e-3; logits and each parameter gradient max|d|/max|ref| <= 2e-2 and
+||d||/||ref|| <= 2e-2.  fp16 runs scale the loss by 2^12 before backward (dlogits = p/N is below
+fp16's subnormal range otherwise) and unscale the gradients in fp32."""
+import pytest
+import torch
+
+from oracle.model import OracleTransformer, init_weights
+from util import max_rel, norm_rel
+
+pytestmark = pytest.mark.gpu
+
+
+def _pair(cfg, dtype, seed=1234):
+    """CUDA model and oracle holding bit-identical (rounded) parameters."""
+    from tritonformer_b200.transformer import Transformer
+    gen = torch.Generator().manual_seed(seed)
+    oracle = OracleTransformer(cfg, bias_dtype=torch.float16)
+    init_weights(oracle, cfg.num_hidden_layers, lm_head_std=0.02, generator=gen)
+    if cfg.use_linear_bias:  # exercise the bias paths
+        with torch.no_grad():
+            for n, p in oracle.named_parameters():
+                if n.endswith("bias") and "layernorm" not in n:
+                    p.normal_(0.0, 0.02, generator=gen)
+    model = Transformer(cfg, device="cuda")
+    sd = {k: v for k, v in oracle.state_dict().items() if k != "attn_bias"}
+    model.load_state_dict(sd, strict=False)
+    if dtype is torch.bfloat16:
+        bias = model.attn_bias
+        model = model.to(torch.bfloat16)
+        if bias is not None:
+            model.attn_bias = bias  # the table keeps the reference's fp16 rounding
+    # copy the rounded values back so both sides hold the same numbers
+    rounded = {k: v.detach().float().cpu() for k, v in model.state_dict().items() if k != "attn_bias"}
+    oracle.load_state_dict(rounded, strict=False)
+    return model, oracle
+
+
+def _step(cfg, dtype, batch, seq, loss_scale, oracle_device):
+    model, oracle = _pair(cfg, dtype)
+    oracle = oracle.to(oracle_device)
+    gen = torch.Generator().manual_seed(99)
+    ids = torch.randint(0, cfg.vocab_size, (batch, seq), generator=gen)
+    with torch.autocast("cuda", dtype=dtype):
+        logits, loss = model(ids.cuda(), ids.cuda())
+    (loss * loss_scale).backward()
+    ids_o = ids.to(oracle_device)
+    logits_r, loss_r = oracle(ids_o, ids_o)
+    loss_r.backward()
+    assert abs(loss.item() - loss_r.item()) / abs(loss_r.item()) <= 1e-3, (loss.item(), loss_r.item())
+    lr = logits_r.detach().to("cuda")
+    assert max_rel(logits.float(), lr) <= 2e-2 and norm_rel(logits.float(), lr) <= 2e-2
+    grads_r = dict(oracle.named_parameters())
+    worst = (0.0, "")
+    for name, p in model.named_parameters():
+        assert p.grad is not None, name
+        g = p.grad.float() / loss_scale
+        r = grads_r[name].grad.to("cuda")
+        assert g.shape == r.shape, name
+        e1, e2 = max_rel(g, r), norm_rel(g, r)
+        worst = max(worst, (max(e1, e2), name))
+        assert e1 <= 2e-2 and e2 <= 2e-2, f"{name}: max-rel {e1:.3e} norm-rel {e2:.3e}"
+    return worst
+
+
+def _cfg(**kw):
+    from tritonformer_b200.transformer import TransformerConfig
+    return TransformerConfig(**kw)
+
+
+def test_small_model_fp16_no_bias():
+    cfg = _cfg(vocab_size=1024, hidden_size=256, max_position_embeddings=256, num_attention_heads=4, head_dim=64,
+               ffn_dim=1024, num_hidden_layers=3, use_linear_bias=False, attn_bias=False)
+    _step(cfg, torch.float16, 2, 256, 4096.0, "cuda")
+
+
+def test_small_model_fp16_bias_alibi_hd32():
+    cfg = _cfg(vocab_size=1000, hidden_size=192, max_position_embeddings=256, num_attention_heads=6, head_dim=32,
+               ffn_dim=768, num_hidden_layers=2, use_linear_bias=True, attn_bias=True)
+    _step(cfg, torch.float16, 3, 128, 4096.0, "cuda")
+
+
+def test_small_model_bf16_bias_alibi_hd128():
+    cfg = _cfg(vocab_size=2048, hidden_size=512, max_position_embeddings=256, num_attention_heads=4, head_dim=128,
+               ffn_dim=2048, num_hidden_layers=2, use_linear_bias=True, attn_bias=True)
+    _step(cfg, torch.bfloat16, 2, 256, 1.0, "cuda")
+
+
+def test_160m_config_fp16_against_cpu_oracle():
+    """The CPU-runnable configuration: d768, 12 layers, 12 heads, ctx 1024, batch 2, vocab 50304."""
+    cfg = _cfg(vocab_size=50304, hidden_size=768, max_position_embeddings=1024, num_attention_heads=12, head_dim=64,
+               ffn_dim=3072, num_hidden_layers=12, use_linear_bias=False, attn_bias=False)
+    _step(cfg, torch.float16, 2, 1024, 4096.0, "cpu")
+
+
+def test_reference_init_known_answer():
+    """Reference init zeroes the LM head: loss = ln(V), every gradient below the head is exactly 0."""
+    import math
+    from tritonformer_b200.transformer import Transformer
+    cfg = _cfg(vocab_size=512, hidden_size=128, max_position_embeddings=128, num_attention_heads=2, head_dim=64,
+               ffn_dim=512, num_hidden_layers=2, use_linear_bias=False, attn_bias=False)
+    torch.manual_seed(0)
+    model = Transformer(cfg, device="cuda")
+    ids = torch.randint(0, 512, (2, 128), device="cuda")
+    with torch.autocast("cuda", dtype=torch.float16):
+        logits, loss = model(ids, ids)
+    loss.backward()
+    assert abs(loss.item() - math.log(512)) < 1e-4 and float(logits.abs().max()) == 0.0
+    for name, p in model.named_parameters():
+        if "logits_out" not in name:
+            assert float(p.grad.abs().max()) == 0.0, name

@@ -58,6 +58,10 @@ def _load():
 
 
 lib = _load()
+if os.environ.get("TFB_FORCE_GENERIC_GEMM") == "1":  # test switch, see tfb_debug_set
+    lib.tfb_debug_set(0, 1)
+if os.environ.get("TFB_FORCE_GENERIC_ATTN") == "1":
+    lib.tfb_debug_set(1, 1)
 
 
 def dtype_code(t: torch.dtype) -> int:

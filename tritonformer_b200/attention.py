@@ -33,7 +33,7 @@ class _Bias:
     """Resolved form of the attn_bias argument."""
     __slots__ = ("slopes", "rounded", "table")
 
-    def __init__(self, slopes=None, rounded=False, table=None):
+    def __init__(self, slopes=None, rounded=0, table=None):
         self.slopes, self.rounded, self.table = slopes, rounded, table
 
 
@@ -60,8 +60,8 @@ def _resolve_bias(attn_bias, heads, seq, dtype):
         if len(_alibi_cache) > 64:
             _alibi_cache.clear()
         _alibi_cache[key] = hit
-    if hit is not False and attn_bias.dtype == dtype:
-        return _Bias(slopes=hit, rounded=True)
+    if hit is not False:
+        return _Bias(slopes=hit, rounded=1 if attn_bias.dtype is torch.float16 else 2)
     table = attn_bias if attn_bias.dtype == dtype else attn_bias.to(dtype)
     return _Bias(table=_unit_inner(table))
 
@@ -95,7 +95,7 @@ def attention_forward(q, k, v, bias: _Bias):
     _lib.check(_lib.lib.tfb_attention_fwd(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), b, h, t, hd,
         _lib.strides3(q), _lib.strides3(k), _lib.strides3(v), _lib.strides3(out),
-        bias.slopes.data_ptr() if bias.slopes is not None else None, 1 if bias.rounded else 0,
+        bias.slopes.data_ptr() if bias.slopes is not None else None, int(bias.rounded),
         tab.data_ptr() if tab is not None else None,
         tab.stride(0) if tab is not None else 0, tab.stride(1) if tab is not None else 0,
         _lib.dtype_code(q.dtype), _lib.stream_ptr(q.device), ctypes.byref(path)))
@@ -115,7 +115,7 @@ def attention_backward(d_out, out, q, k, v, lse, bias: _Bias):
         dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), b, h, t, hd,
         _lib.strides3(q), _lib.strides3(k), _lib.strides3(v), _lib.strides3(out), _lib.strides3(d_out),
         _lib.strides3(dq), _lib.strides3(dk), _lib.strides3(dv),
-        bias.slopes.data_ptr() if bias.slopes is not None else None, 1 if bias.rounded else 0,
+        bias.slopes.data_ptr() if bias.slopes is not None else None, int(bias.rounded),
         tab.data_ptr() if tab is not None else None,
         tab.stride(0) if tab is not None else 0, tab.stride(1) if tab is not None else 0,
         scratch.data_ptr(), nbytes, _lib.dtype_code(q.dtype), _lib.stream_ptr(q.device),

@@ -43,7 +43,7 @@ extern "C" int tfb_attention_fwd(const void* q, const void* k, const void* v, vo
   a.sq = mk(q_strides); a.sk = mk(k_strides); a.sv = mk(v_strides); a.so = mk(o_strides);
   a.B = (int)B; a.H = (int)H; a.T = (int)T;
   a.scale = 1.0f / sqrtf((float)hd);
-  a.bias_mode = slopes ? (alibi_round ? 2 : 1) : (bias ? 3 : 0);
+  a.bias_mode = slopes ? (alibi_round == 1 ? 2 : alibi_round == 2 ? 4 : 1) : (bias ? 3 : 0);
   a.slopes = slopes; a.bias = bias; a.bias_sh = bias_sh; a.bias_si = bias_si;
   if (path) *path = 0;
   return attn_generic_fwd(a, (int)hd, dtype, (cudaStream_t)stream);
@@ -80,7 +80,7 @@ extern "C" int tfb_attention_bwd(const void* q, const void* k, const void* v, co
   a.sdo = mk(do_strides); a.sdq = mk(dq_strides); a.sdk = mk(dk_strides); a.sdv = mk(dv_strides);
   a.B = (int)B; a.H = (int)H; a.T = (int)T;
   a.scale = 1.0f / sqrtf((float)hd);
-  a.bias_mode = slopes ? (alibi_round ? 2 : 1) : (bias ? 3 : 0);
+  a.bias_mode = slopes ? (alibi_round == 1 ? 2 : alibi_round == 2 ? 4 : 1) : (bias ? 3 : 0);
   a.slopes = slopes; a.bias = bias; a.bias_sh = bias_sh; a.bias_si = bias_si;
   if (path) *path = 0;
   return attn_generic_bwd(a, (int)hd, dtype, (cudaStream_t)stream);

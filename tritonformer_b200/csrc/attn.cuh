@@ -14,7 +14,7 @@ struct AttnArgs {
   AttnStrides sq, sk, sv, so, sdo, sdq, sdk, sdv;
   int B, H, T;
   float scale;         // 1/sqrt(hd)
-  int bias_mode;       // 0 none, 1 ALiBi fp32, 2 ALiBi rounded like the reference table, 3 dense table
+  int bias_mode;       // 0 none, 1 ALiBi fp32, 2 / 4 ALiBi rounded like an fp16 / bf16 reference table, 3 dense table
   const float* slopes;
   const void* bias;
   int64_t bias_sh, bias_si;

@@ -46,15 +46,13 @@ template <> struct Mma16816<__nv_bfloat16> {
 };
 
 // additive bias (natural units) for query i, key j (j <= i)
+// modes 2 / 4 rebuild the reference ALiBi table entry: the (negative) distance and the slope are
+// rounded to fp16 (2) or bf16 (4) and multiplied in that type.
 template <typename T>
 __device__ __forceinline__ float bias_at(int mode, float slope, const T* table_h, int64_t si, int i, int j) {
   if (mode == 1) return -slope * (float)(i - j);
-  if (mode == 2) {
-    // the reference table: element-type product of the rounded (negative) distance and rounded slope
-    const T d = Num<T>::from_f(-(float)(i - j));
-    const T s = Num<T>::from_f(slope);
-    return Num<T>::to_f(__hmul(d, s));
-  }
+  if (mode == 2) return __half2float(__hmul(__float2half_rn(-(float)(i - j)), __float2half_rn(slope)));
+  if (mode == 4) return __bfloat162float(__hmul(__float2bfloat16_rn(-(float)(i - j)), __float2bfloat16_rn(slope)));
   if (mode == 3) return Num<T>::to_f(table_h[(int64_t)i * si + j]);
   return 0.f;
 }
@@ -111,7 +109,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_fwd_kernel(const AttnArgs a) 
   const T* qp = (const T*)a.q + b * a.sq.b + h * a.sq.h + (int64_t)q0 * a.sq.t;
   const T* kp = (const T*)a.k + b * a.sk.b + h * a.sk.h;
   const T* vp = (const T*)a.v + b * a.sv.b + h * a.sv.h;
-  const float slope = (a.bias_mode == 1 || a.bias_mode == 2) ? a.slopes[h] : 0.f;
+  const float slope = (a.bias_mode != 0 && a.bias_mode != 3) ? a.slopes[h] : 0.f;
   const T* table_h = a.bias_mode == 3 ? (const T*)a.bias + h * a.bias_sh : nullptr;
   const float c2 = a.scale * kLog2e;
 
@@ -263,7 +261,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_bwd_kv_kernel(const AttnArgs 
   const int j0 = kt * AT;
   const T* qp = (const T*)a.q + b * a.sq.b + h * a.sq.h;
   const T* gp = (const T*)a.d_o + b * a.sdo.b + h * a.sdo.h;
-  const float slope = (a.bias_mode == 1 || a.bias_mode == 2) ? a.slopes[h] : 0.f;
+  const float slope = (a.bias_mode != 0 && a.bias_mode != 3) ? a.slopes[h] : 0.f;
   const T* table_h = a.bias_mode == 3 ? (const T*)a.bias + h * a.bias_sh : nullptr;
   const float c2 = a.scale * kLog2e;
 
@@ -411,7 +409,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_bwd_q_kernel(const AttnArgs a
   const int i0 = qt * AT;
   const T* kp = (const T*)a.k + b * a.sk.b + h * a.sk.h;
   const T* vp = (const T*)a.v + b * a.sv.b + h * a.sv.h;
-  const float slope = (a.bias_mode == 1 || a.bias_mode == 2) ? a.slopes[h] : 0.f;
+  const float slope = (a.bias_mode != 0 && a.bias_mode != 3) ? a.slopes[h] : 0.f;
   const T* table_h = a.bias_mode == 3 ? (const T*)a.bias + h * a.bias_sh : nullptr;
   const float c2 = a.scale * kLog2e;
 
@@ -516,16 +514,24 @@ static int bwd_launch(const AttnArgs& a, cudaStream_t st) {
   {
     auto kern = attn_bwd_kv_kernel<T, HD>;
     const int bytes = (int)sizeof(BwdKvSmem<T, HD>);
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    if (e != cudaSuccess) return fail(TFB_ERR_LAUNCH, "attention_bwd: smem attribute: %s", cudaGetErrorString(e));
+    static bool attr_set = false;  // benign race: the call is idempotent
+    if (!attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+      if (e != cudaSuccess) return fail(TFB_ERR_LAUNCH, "attention_bwd: smem attribute: %s", cudaGetErrorString(e));
+      attr_set = true;
+    }
     kern<<<grid, AT_THREADS, bytes, st>>>(a);
     if ((rc = launched("attention_bwd_kv(generic)"))) return rc;
   }
   {
     auto kern = attn_bwd_q_kernel<T, HD>;
     const int bytes = (int)sizeof(BwdQSmem<T, HD>);
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    if (e != cudaSuccess) return fail(TFB_ERR_LAUNCH, "attention_bwd: smem attribute: %s", cudaGetErrorString(e));
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+      if (e != cudaSuccess) return fail(TFB_ERR_LAUNCH, "attention_bwd: smem attribute: %s", cudaGetErrorString(e));
+      attr_set = true;
+    }
     kern<<<grid, AT_THREADS, bytes, st>>>(a);
     if ((rc = launched("attention_bwd_q(generic)"))) return rc;
   }

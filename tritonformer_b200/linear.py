@@ -22,15 +22,26 @@ def _as_rows(x: torch.Tensor) -> torch.Tensor:
     return x2
 
 
+# When set to a list, every GEMM call appends (flops, start_event, end_event): used by the
+# benchmark to time the kernel family live on the launching stream.
+PROFILE = None
+
+
 def gemm(a, a_sm, a_sk, b, b_sk, b_sn, m, n, k, bias=None, relu=False, out=None, accumulate=False):
     """C[m,n] = act(sum_k A(m,k) B(k,n) + bias) with element strides for A and B."""
     if out is None:
         out = torch.empty((m, n), device=a.device, dtype=a.dtype)
     path = ctypes.c_int(0)
+    if PROFILE is not None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
     _lib.check(_lib.lib.tfb_gemm(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), bias.data_ptr() if bias is not None else None,
         m, n, k, a_sm, a_sk, b_sk, b_sn, out.stride(0), 1 if relu else 0, 1 if accumulate else 0,
         _lib.dtype_code(a.dtype), _lib.stream_ptr(a.device), ctypes.byref(path)))
+    if PROFILE is not None:
+        e1.record()
+        PROFILE.append((2.0 * m * n * k, e0, e1, path.value, (m, n, k)))
     return out
 
 
