@@ -21,8 +21,17 @@ class _Linear(nn.Module):
         self.weight = nn.Parameter(torch.empty(d_in, d_out))
         self.bias = nn.Parameter(torch.zeros(d_out)) if bias else None
         self.relu = relu
+        # Optional boolean mask that replaces the ReLU's own sign test (see `forward`).
+        self.forced_mask = None
 
     def forward(self, x):
+        if self.relu and self.forced_mask is not None:
+            # ReLU with a prescribed activation pattern: a pre-activation within rounding distance of
+            # zero lands on either side in 16-bit arithmetic; evaluating the oracle with the pattern
+            # observed in the implementation under test separates arithmetic error from that ambiguity.
+            pre = ops.linear(x, self.weight, self.bias, False)
+            self.last_pre = pre.detach()
+            return pre * self.forced_mask.to(pre.dtype)
         return ops.linear(x, self.weight, self.bias, self.relu)
 
 

@@ -38,7 +38,15 @@ def _run(dims, has_bias, relu, dtype):
     assert torch.equal(dy, keep), "incoming gradient must not be modified"
     xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
     br = bias.detach().float().requires_grad_(True) if has_bias else None
-    yr = ops.linear(xr, wr, br, relu)
+    yr = ops.linear(xr, wr, br, False)
+    if relu:
+        # A pre-activation within rounding distance of zero may land on either side in 16-bit
+        # arithmetic; the oracle is evaluated with the kernel's own mask so that such units do not
+        # turn into whole-row differences of dX.  The masks must agree wherever |pre-act| is not tiny.
+        mask = y.detach() > 0
+        pre = yr.detach()
+        assert bool(((pre > 0) == mask)[pre.abs() > 1e-2].all()), "ReLU mask disagrees away from zero"
+        yr = yr * mask
     yr.backward(dy.float())
     got = [y, x.grad, w.grad] + ([bias.grad] if has_bias else [])
     want = [yr, xr.grad, wr.grad] + ([br.grad] if has_bias else [])
@@ -52,8 +60,8 @@ def _check(got, want, dtype):
         # one rounding of an fp32-accumulated result: 2^-11 (fp16) / 2^-8 (bf16) relative
         assert norm_rel(a, b) < (1e-3 if dtype is torch.float16 else 6e-3), nm
     if dtype is torch.float16:
-        assert_close(got[0], want[0], 1e-2, "y")  # the reference tests' atol on values of order 1
-        assert_close(got[1], want[1], 1e-2, "dx")
+        assert_close(got[0], want[0], 1e-2, "y", rtol=1e-3)  # the reference tests' atol + one fp16 rounding
+        assert_close(got[1], want[1], 1e-2, "dx", rtol=1e-3)
 
 
 @pytest.mark.parametrize("dims", RAGGED)

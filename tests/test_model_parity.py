@@ -1,9 +1,15 @@
 """GPU parity of the whole model: logits, loss and every parameter gradient of the CUDA path against
 the fp32 oracle model on identical (already rounded) weights and tokens.
 
-Tolerances: loss |d|/|ref| <= 1e-3; logits and each parameter gradient max|d|/max|ref| <= 2e-2 and
-||d||/||ref|| <= 2e-2.  fp16 runs scale the loss by 2^12 before backward (dlogits = p/N is below
-fp16's subnormal range otherwise) and unscale the gradients in fp32."""
+Tolerances: loss |d|/|ref| <= 1e-3; logits max|d|/max|ref| and ||d||/||ref|| <= 2e-2; each parameter
+gradient max|d|/max|ref| <= 2e-2 and ||d||/||ref|| <= 2e-2 against the oracle evaluated with the ReLU
+activation pattern of the CUDA run (the two patterns must agree except where the pre-activation is
+within 16-bit rounding distance of zero).  Against the unconstrained oracle the stated bound is
+LOOSE_TOL: with randomly initialised weights a ~2e-4 (fp16) / ~2e-3 (bf16) fraction of hidden units
+has a pre-activation that rounds to the other side of zero, and each such unit moves every gradient
+below it by a full unit's worth -- about 2 % (fp16) / 6 % (bf16) in norm for ANY 16-bit implementation.
+fp16 runs scale the loss by 2^12 before backward (dlogits = p/N is below fp16's normal range otherwise)
+and unscale the gradients in fp32."""
 import pytest
 import torch
 
@@ -38,31 +44,72 @@ def _pair(cfg, dtype, seed=1234):
     return model, oracle
 
 
+LOOSE_TOL = {torch.float16: 1.5e-1, torch.bfloat16: 3e-1}
+
+
+def _grad_errors(model, oracle, loss_scale):
+    ref = dict(oracle.named_parameters())
+    rows = []
+    for name, p in model.named_parameters():
+        assert p.grad is not None, name
+        g = p.grad.float() / loss_scale
+        r = ref[name].grad.to("cuda")
+        assert g.shape == r.shape, name
+        rows.append((max(max_rel(g, r), norm_rel(g, r)), name, max_rel(g, r), norm_rel(g, r)))
+    rows.sort(reverse=True)
+    return rows
+
+
 def _step(cfg, dtype, batch, seq, loss_scale, oracle_device):
     model, oracle = _pair(cfg, dtype)
     oracle = oracle.to(oracle_device)
     gen = torch.Generator().manual_seed(99)
     ids = torch.randint(0, cfg.vocab_size, (batch, seq), generator=gen)
+    masks = []
+    hooks = [layer.mlp.dense_h_to_4h.register_forward_hook(lambda m, i, o: masks.append((o > 0).detach()))
+             for layer in model.layer_list]
     with torch.autocast("cuda", dtype=dtype):
         logits, loss = model(ids.cuda(), ids.cuda())
+    for h in hooks:
+        h.remove()
     (loss * loss_scale).backward()
     ids_o = ids.to(oracle_device)
+
+    # 1. unconstrained oracle: loss, logits, loose gradient bound
     logits_r, loss_r = oracle(ids_o, ids_o)
     loss_r.backward()
     assert abs(loss.item() - loss_r.item()) / abs(loss_r.item()) <= 1e-3, (loss.item(), loss_r.item())
     lr = logits_r.detach().to("cuda")
     assert max_rel(logits.float(), lr) <= 2e-2 and norm_rel(logits.float(), lr) <= 2e-2
-    grads_r = dict(oracle.named_parameters())
-    worst = (0.0, "")
-    for name, p in model.named_parameters():
-        assert p.grad is not None, name
-        g = p.grad.float() / loss_scale
-        r = grads_r[name].grad.to("cuda")
-        assert g.shape == r.shape, name
-        e1, e2 = max_rel(g, r), norm_rel(g, r)
-        worst = max(worst, (max(e1, e2), name))
-        assert e1 <= 2e-2 and e2 <= 2e-2, f"{name}: max-rel {e1:.3e} norm-rel {e2:.3e}"
-    return worst
+    rows = _grad_errors(model, oracle, loss_scale)
+    print(f"unconstrained oracle, worst gradient error {rows[0][0]:.3e} ({rows[0][1]})")
+    assert rows[0][0] <= LOOSE_TOL[dtype], rows[:4]
+
+    # 2. oracle with the CUDA run's activation pattern: the 2e-2 bound on every parameter gradient
+    oracle.zero_grad(set_to_none=True)
+    for layer, mask in zip(oracle.layer_list, masks):
+        layer.mlp.dense_h_to_4h.forced_mask = mask.to(oracle_device)
+    _, loss_m = oracle(ids_o, ids_o)
+    loss_m.backward()
+    flipped = 0.0
+    for layer, mask in zip(oracle.layer_list, masks):
+        lin = layer.mlp.dense_h_to_4h
+        pre = lin.last_pre
+        differ = (pre > 0) != lin.forced_mask
+        flipped = max(flipped, differ.float().mean().item())
+        # only pre-activations within rounding distance of zero may differ in sign
+        if differ.any():
+            assert pre[differ].abs().max().item() <= (4e-3 if dtype is torch.float16 else 3e-2) * pre.abs().max().item()
+        lin.forced_mask = None
+    assert flipped <= (2e-3 if dtype is torch.float16 else 1.5e-2), flipped
+    rows = _grad_errors(model, oracle, loss_scale)
+    print(f"fraction of ReLU units whose sign differs: {flipped:.2e}; worst parameter-gradient errors "
+          "(max-rel, norm-rel) with the pattern fixed:")
+    for _, name, e1, e2 in rows[:6]:
+        print(f"  {name}: {e1:.3e} {e2:.3e}")
+    bad = [f"{n}: max-rel {e1:.3e} norm-rel {e2:.3e}" for _, n, e1, e2 in rows if e1 > 2e-2 or e2 > 2e-2]
+    assert not bad, "; ".join(bad)
+    return rows[0]
 
 
 def _cfg(**kw):

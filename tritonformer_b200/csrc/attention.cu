@@ -3,7 +3,10 @@
 
 namespace tfb {
 extern std::atomic<int> g_force_fallback_attn;
-int attn_tc05_status(int reset) { (void)reset; return 0; }
+bool attn_tc05_fwd_eligible(const AttnArgs& a, int hd);
+int attn_tc05_fwd(const AttnArgs& a, int hd, int dtype, cudaStream_t st);
+bool attn_tc05_bwd_eligible(const AttnArgs& a, int hd);
+int attn_tc05_bwd(const AttnArgs& a, int hd, int dtype, cudaStream_t st);
 }  // namespace tfb
 
 using namespace tfb;
@@ -45,13 +48,15 @@ extern "C" int tfb_attention_fwd(const void* q, const void* k, const void* v, vo
   a.scale = 1.0f / sqrtf((float)hd);
   a.bias_mode = slopes ? (alibi_round == 1 ? 2 : alibi_round == 2 ? 4 : 1) : (bias ? 3 : 0);
   a.slopes = slopes; a.bias = bias; a.bias_sh = bias_sh; a.bias_si = bias_si;
-  if (path) *path = 0;
+  const bool fast = !g_force_fallback_attn.load() && attn_tc05_fwd_eligible(a, (int)hd);
+  if (path) *path = fast ? 1 : 0;
+  if (fast) return attn_tc05_fwd(a, (int)hd, dtype, (cudaStream_t)stream);
   return attn_generic_fwd(a, (int)hd, dtype, (cudaStream_t)stream);
 }
 
 extern "C" int64_t tfb_attention_bwd_scratch_bytes(int64_t B, int64_t H, int64_t T, int64_t hd) {
   // delta (B,H,T) fp32, then the fp32 dQ accumulator (B,H,T,hd) of the tcgen05 path
-  return B * H * T * 4 + B * H * T * hd * 4;
+  return ((B * H * T * 4 + 255) / 256) * 256 + B * H * T * hd * 4;
 }
 
 extern "C" int tfb_attention_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
@@ -82,6 +87,9 @@ extern "C" int tfb_attention_bwd(const void* q, const void* k, const void* v, co
   a.scale = 1.0f / sqrtf((float)hd);
   a.bias_mode = slopes ? (alibi_round == 1 ? 2 : alibi_round == 2 ? 4 : 1) : (bias ? 3 : 0);
   a.slopes = slopes; a.bias = bias; a.bias_sh = bias_sh; a.bias_si = bias_si;
-  if (path) *path = 0;
+  a.dq_acc = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(scratch) + ((B * H * T * 4 + 255) / 256) * 256);
+  const bool fast = !g_force_fallback_attn.load() && attn_tc05_bwd_eligible(a, (int)hd);
+  if (path) *path = fast ? 1 : 0;
+  if (fast) return attn_tc05_bwd(a, (int)hd, dtype, (cudaStream_t)stream);
   return attn_generic_bwd(a, (int)hd, dtype, (cudaStream_t)stream);
 }

@@ -11,6 +11,7 @@ struct AttnArgs {
   void *out, *dq, *dk, *dv;
   float* lse;          // (B,H,T) natural log-sum-exp
   float* delta;        // (B,H,T)
+  float* dq_acc;       // (B,H,T,hd) fp32 accumulator of the tcgen05 backward
   AttnStrides sq, sk, sv, so, sdo, sdq, sdk, sdv;
   int B, H, T;
   float scale;         // 1/sqrt(hd)
@@ -21,6 +22,8 @@ struct AttnArgs {
 };
 
 
+// delta[b,h,i] = sum_d dO[i,d] * O[i,d] (fp32), shared by both backward paths
+int attn_delta(const AttnArgs& a, int hd, int dtype, cudaStream_t st);
 int attn_generic_fwd(const AttnArgs& a, int hd, int dtype, cudaStream_t st);
 int attn_generic_bwd(const AttnArgs& a, int hd, int dtype, cudaStream_t st);
 

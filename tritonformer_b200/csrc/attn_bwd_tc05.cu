@@ -1,0 +1,401 @@
+// Causal flash attention backward on tcgen05 / TMEM for sm_100a (head_dim 64 or 128, T % 128 == 0).
+//
+// One CTA per (128-key tile, batch*head); it walks the query tiles at or below the diagonal.
+// Everything is computed transposed (rows = keys) so that the per-query statistics (log-sum-exp,
+// delta) are per-column constants and no row reductions are needed:
+//   Sᵀ  = K Q_iᵀ                 dPᵀ = V dO_iᵀ                      (tensor cores -> TMEM)
+//   Pᵀ  = 2^(Sᵀ·c + bias - lse)  dSᵀ = Pᵀ ∘ (dPᵀ - delta)            (compute warps -> smem, 16 bit)
+//   dV += Pᵀ dO_i     dK += dSᵀ Q_i     dQ_i = dS K                  (tensor cores -> TMEM)
+// dV and dK stay in TMEM for the whole walk; dQ_i is added to an fp32 global accumulator
+// (red.global.add.f32) because every key tile contributes to it; a small kernel scales and
+// rounds the accumulator afterwards.
+// A 128 x 64 swizzled panel of 16-bit values is at the same time a K-major operand with 128 rows
+// and an MN-major operand with 128 contraction rows, so each of K, V, Q_i, dO_i, dSᵀ sits in
+// shared memory once and serves two products.
+//
+// Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2-9 compute (thread = TMEM lane, two
+// warps per lane quarter, each taking half of the columns).
+// TMEM columns: [0,128) Sᵀ, then reused for dQ_i; [128,256) dPᵀ; [256,256+hd) dV; then dK.
+#include "attn.cuh"
+#include "tc05.cuh"
+#include <type_traits>
+
+namespace tfb {
+
+constexpr float kLog2eB = 1.4426950408889634f;
+constexpr int FB_T = 128;           // tile edge (keys and queries)
+constexpr int FB_THREADS = 320;     // 10 warps
+constexpr int FB_COMPUTE = 256;     // threads in the compute warps
+
+template <int HD> struct FbCfg {
+  static constexpr int PANELS = HD / 64;
+  static constexpr int TILE_BYTES = PANELS * 16384;   // 128 rows x HD x 2 B
+  static constexpr int QSTAGES = (HD == 64) ? 2 : 1;  // query-side ring depth (smem bound at hd 128)
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = TILE_BYTES;
+  static constexpr int OFF_Q = 2 * TILE_BYTES;                       // [QSTAGES]
+  static constexpr int OFF_DO = OFF_Q + QSTAGES * TILE_BYTES;        // [QSTAGES]
+  static constexpr int OFF_P = OFF_DO + QSTAGES * TILE_BYTES;        // Pᵀ  128 x 128 x 2 B
+  static constexpr int OFF_DS = OFF_P + 32768;                       // dSᵀ 128 x 128 x 2 B
+  static constexpr int OFF_STAT = OFF_DS + 32768;                    // lse2[128], delta[128] fp32
+  static constexpr int OFF_BAR = OFF_STAT + 1024;
+  static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+  static constexpr int COL_S = 0, COL_DQ = 0, COL_DP = 128, COL_DV = 256, COL_DK = 256 + HD;
+};
+
+struct FbParams {
+  const float* lse;
+  const float* delta;
+  float* dq_acc;  // (B,H,T,HD) fp32, zero on entry
+  void *dk, *dv;
+  int64_t sdk_b, sdk_h, sdk_t, sdv_b, sdv_h, sdv_t;
+  int H, T;
+  float scale;
+  int bias_mode;
+  const float* slopes;
+};
+
+__device__ __forceinline__ float alibi_term_b(int mode, float slope, int dist) {
+  if (mode == 1) return -slope * (float)dist;
+  if (mode == 2) return __half2float(__hmul(__float2half_rn(-(float)dist), __float2half_rn(slope)));
+  return __bfloat162float(__hmul(__float2bfloat16_rn(-(float)dist), __float2bfloat16_rn(slope)));
+}
+
+__device__ __forceinline__ void compute_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+template <typename T, int HD>
+__global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __grid_constant__ CUtensorMap tmQ,
+                                                                      const __grid_constant__ CUtensorMap tmK,
+                                                                      const __grid_constant__ CUtensorMap tmV,
+                                                                      const __grid_constant__ CUtensorMap tmDO,
+                                                                      const FbParams p) {
+  using Cfg = FbCfg<HD>;
+  constexpr int QS = Cfg::QSTAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* s_lse2 = reinterpret_cast<float*>(smem + Cfg::OFF_STAT);
+  float* s_delta = s_lse2 + FB_T;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
+  uint64_t* kv_full = bars + 0;
+  uint64_t* q_full = bars + 1;    // [2] Q_i and dO_i landed
+  uint64_t* q_empty = bars + 3;   // [2] products reading them retired
+  uint64_t* s_full = bars + 5;    // Sᵀ and dPᵀ in TMEM
+  uint64_t* pds_full = bars + 6;  // Pᵀ and dSᵀ in smem
+  uint64_t* dq_full = bars + 7;   // dV, dK, dQ_i products retired
+  uint64_t* dq_free = bars + 8;   // dQ_i read out of TMEM
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 10);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kt = blockIdx.x;  // key tile; tile 0 has the longest walk and starts first
+  const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
+  const int j0 = kt * FB_T;
+  const int nq = p.T / FB_T;
+  const int iters = nq - kt;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&q_empty[i], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(pds_full, 8);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_free, 8);
+    *abort_flag = (*(volatile int*)&g_dev_status != 0) ? 1 : 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tmem_alloc(tmem_holder, 512);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const bool dead = *abort_flag != 0;
+
+  if (warp == 0) {
+    // --------------------------------------------------------------------- TMA producer
+    if (lane == 0 && !dead) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      tma_prefetch_desc(&tmDO);
+      mbar_expect_tx(kv_full, 2 * Cfg::TILE_BYTES);
+#pragma unroll
+      for (int c = 0; c < Cfg::PANELS; ++c) {
+        tma_load_4d(smem + Cfg::OFF_K + c * 16384, &tmK, c * 64, j0, h, b, kv_full);
+        tma_load_4d(smem + Cfg::OFF_V + c * 16384, &tmV, c * 64, j0, h, b, kv_full);
+      }
+      for (int it = 0; it < iters; ++it) {
+        const int st = it % QS;
+        const uint32_t ph = (it / QS) & 1;
+        if (!mbar_wait(&q_empty[st], ph ^ 1, 0x2100 | st, abort_flag)) break;
+        mbar_expect_tx(&q_full[st], 2 * Cfg::TILE_BYTES);
+        const int i0 = (kt + it) * FB_T;
+#pragma unroll
+        for (int c = 0; c < Cfg::PANELS; ++c) {
+          tma_load_4d(smem + Cfg::OFF_Q + st * Cfg::TILE_BYTES + c * 16384, &tmQ, c * 64, i0, h, b, &q_full[st]);
+          tma_load_4d(smem + Cfg::OFF_DO + st * Cfg::TILE_BYTES + c * 16384, &tmDO, c * 64, i0, h, b, &q_full[st]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ----------------------------------------------------------------------- MMA issuer
+    if (lane == 0 && !dead) {
+      constexpr int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+      constexpr uint32_t idesc_s = instr_desc_f16(128, 128, fmt, 0, 0);   // Sᵀ, dPᵀ : both K-major
+      constexpr uint32_t idesc_kv = instr_desc_f16(128, HD, fmt, 0, 1);   // dV, dK  : A K-major, B MN-major
+      constexpr uint32_t idesc_q = instr_desc_f16(128, HD, fmt, 1, 1);    // dQ      : both MN-major
+      const uint32_t sk = smem_u32(smem + Cfg::OFF_K), sv = smem_u32(smem + Cfg::OFF_V);
+      const uint32_t sp = smem_u32(smem + Cfg::OFF_P), sds = smem_u32(smem + Cfg::OFF_DS);
+      bool ok = mbar_wait(kv_full, 0, 0x2200, abort_flag);
+      for (int it = 0; it < iters && ok; ++it) {
+        const int st = it % QS;
+        const uint32_t sq = smem_u32(smem + Cfg::OFF_Q + st * Cfg::TILE_BYTES);
+        const uint32_t sdo = smem_u32(smem + Cfg::OFF_DO + st * Cfg::TILE_BYTES);
+        if (!mbar_wait(&q_full[st], (it / QS) & 1, 0x2300 | st, abort_flag)) { ok = false; break; }
+        // the dQ of the previous query tile lives in the Sᵀ columns until the compute warps drained it
+        if (it > 0 && !mbar_wait(dq_free, (it - 1) & 1, 0x2400, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int s = 0; s < HD / 16; ++s) {
+          const uint32_t off = (s / 4) * 16384 + (s % 4) * 32;
+          tc_mma_ss(tmem_base + Cfg::COL_S, smem_desc_sw128(sk + off, 16, 1024), smem_desc_sw128(sq + off, 16, 1024),
+                    idesc_s, s ? 1u : 0u);
+        }
+#pragma unroll
+        for (int s = 0; s < HD / 16; ++s) {
+          const uint32_t off = (s / 4) * 16384 + (s % 4) * 32;
+          tc_mma_ss(tmem_base + Cfg::COL_DP, smem_desc_sw128(sv + off, 16, 1024), smem_desc_sw128(sdo + off, 16, 1024),
+                    idesc_s, s ? 1u : 0u);
+        }
+        tc_commit(s_full);
+        if (!mbar_wait(pds_full, it & 1, 0x2500, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int s = 0; s < FB_T / 16; ++s) {  // contraction over the 128 queries of this tile
+          const uint32_t koff = (s / 4) * 16384 + (s % 4) * 32;  // K-major A: 16 queries = 32 B along the row
+          const uint32_t moff = s * 2048;                         // MN-major B: 16 query rows of 128 B
+          tc_mma_ss(tmem_base + Cfg::COL_DV, smem_desc_sw128(sp + koff, 16, 1024),
+                    smem_desc_sw128(sdo + moff, 16384, 1024), idesc_kv, (it | s) ? 1u : 0u);
+          tc_mma_ss(tmem_base + Cfg::COL_DK, smem_desc_sw128(sds + koff, 16, 1024),
+                    smem_desc_sw128(sq + moff, 16384, 1024), idesc_kv, (it | s) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int s = 0; s < FB_T / 16; ++s) {  // contraction over the 128 keys of this CTA
+          const uint32_t moff = s * 2048;      // 16 key rows of 128 B in dSᵀ and in K
+          tc_mma_ss(tmem_base + Cfg::COL_DQ, smem_desc_sw128(sds + moff, 16384, 1024),
+                    smem_desc_sw128(sk + moff, 16384, 1024), idesc_q, s ? 1u : 0u);
+        }
+        tc_commit(&q_empty[st]);
+        tc_commit(dq_full);
+      }
+    }
+  } else if (!dead) {
+    // -------------------------------------------------------------------------- compute
+    const int cw = warp - 2;           // 0..7
+    const int qd = warp & 3;           // TMEM lane quarter
+    const int half = cw >> 2;          // which half of the columns
+    const int r = qd * 32 + lane;      // TMEM lane: key row for Sᵀ/dPᵀ/dV/dK, query row for dQ
+    const int ct = threadIdx.x - 64;   // 0..255 within the compute group
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
+    const float c2 = p.scale * kLog2eB;
+    const float slope = p.bias_mode ? p.slopes[h] : 0.f;
+    const int j = j0 + r;              // this thread's key
+    uint8_t* sp = smem + Cfg::OFF_P;
+    uint8_t* sds = smem + Cfg::OFF_DS;
+    bool ok = true;
+    // Every compute thread runs every iteration up to the named barrier, also after a wait gave
+    // up (the remaining waits then return at once), so nobody is left alone at the barrier.
+    for (int it = 0; it < iters; ++it) {
+      const int i0 = (kt + it) * FB_T;
+      const bool diag = (it == 0);
+      // per-query statistics of this tile; safe to overwrite: every compute warp is past dq_full
+      if (ct < FB_T) s_lse2[ct] = p.lse[(int64_t)bh * p.T + i0 + ct] * kLog2eB;
+      else s_delta[ct - FB_T] = p.delta[(int64_t)bh * p.T + i0 + ct - FB_T];
+      compute_bar_sync();
+      if (ok) ok = mbar_wait(s_full, it & 1, 0x2600, abort_flag);
+      if (ok) {
+        tc_fence_after();
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          const int col0 = half * 64 + c * 32;  // first query column of this chunk
+          uint32_t sv_[32], dv_[32];
+          tmem_ld32(lane_addr + Cfg::COL_S + col0, sv_);
+          tmem_ld32(lane_addr + Cfg::COL_DP + col0, dv_);
+          tc_wait_ld();
+          float pf[32], df[32];
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int il = col0 + e;
+            const int i = i0 + il;
+            float x = __uint_as_float(sv_[e]) * c2;
+            if (p.bias_mode) x += alibi_term_b(p.bias_mode, slope, max(i - j, 0)) * kLog2eB;
+            float pe = exp2f(x - s_lse2[il]);
+            if (diag && j > i) pe = 0.f;
+            // P is rounded to the element type before it meets dP, as the tensor core sees it
+            const float pr = Num<T>::to_f(Num<T>::from_f(pe));
+            pf[e] = pe;
+            df[e] = pr * (__uint_as_float(dv_[e]) - s_delta[il]);
+          }
+#pragma unroll
+          for (int v4 = 0; v4 < 4; ++v4) {
+            float g[8], d[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              g[e] = pf[v4 * 8 + e];
+              d[e] = df[v4 * 8 + e];
+            }
+            const int cc = (col0 >> 3) + v4;  // 16-byte chunk index along the 128 queries
+            const uint32_t off = (cc >> 3) * 16384 + r * 128 + (((cc & 7) ^ (r & 7)) << 4);
+            *reinterpret_cast<uint4*>(sp + off) = pack8<T>(g);
+            *reinterpret_cast<uint4*>(sds + off) = pack8<T>(d);
+          }
+        }
+        tc_fence_before();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(pds_full);
+      }
+      // dQ_i: lanes are now query rows
+      if (ok) ok = mbar_wait(dq_full, it & 1, 0x2700, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        float* dq_row = p.dq_acc + ((int64_t)bh * p.T + i0 + r) * HD;
+#pragma unroll 1
+        for (int c = 0; c < HD / 64; ++c) {
+          const int col0 = half * (HD / 2) + c * 32;
+          uint32_t v[32];
+          tmem_ld32(lane_addr + Cfg::COL_DQ + col0, v);
+          tc_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; e += 4)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + col0 + e),
+                         "f"(__uint_as_float(v[e])), "f"(__uint_as_float(v[e + 1])),
+                         "f"(__uint_as_float(v[e + 2])), "f"(__uint_as_float(v[e + 3]))
+                         : "memory");
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(dq_free);
+      }
+    }
+    if (ok) {
+      // dV and dK are complete once the last dq_full has been seen
+      T* dvp = reinterpret_cast<T*>(p.dv) + b * p.sdv_b + h * p.sdv_h + (int64_t)j * p.sdv_t;
+      T* dkp = reinterpret_cast<T*>(p.dk) + b * p.sdk_b + h * p.sdk_h + (int64_t)j * p.sdk_t;
+#pragma unroll 1
+      for (int c = 0; c < HD / 64; ++c) {
+        const int col0 = half * (HD / 2) + c * 32;
+        uint32_t v[32], w[32];
+        tmem_ld32(lane_addr + Cfg::COL_DV + col0, v);
+        tmem_ld32(lane_addr + Cfg::COL_DK + col0, w);
+        tc_wait_ld();
+#pragma unroll
+        for (int v4 = 0; v4 < 4; ++v4) {
+          float g[8], d[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            g[e] = __uint_as_float(v[v4 * 8 + e]);
+            d[e] = __uint_as_float(w[v4 * 8 + e]) * p.scale;
+          }
+          *reinterpret_cast<uint4*>(dvp + col0 + v4 * 8) = pack8<T>(g);
+          *reinterpret_cast<uint4*>(dkp + col0 + v4 * 8) = pack8<T>(d);
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int k = 0; k < 64; ++k) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// dq = round(scale * dq_acc), written with the caller's strides
+template <typename T>
+__global__ void __launch_bounds__(256) attn_dq_convert_kernel(const float* __restrict__ acc, T* __restrict__ dq,
+                                                              int64_t sb, int64_t sh, int64_t st, int H, int T_,
+                                                              int hd, float scale, int64_t nvec) {
+  const int vpr = hd / 8;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < nvec;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(idx % vpr);
+    const int64_t row = idx / vpr;
+    const int i = (int)(row % T_);
+    const int64_t bh = row / T_;
+    const int b = (int)(bh / H), h = (int)(bh % H);
+    const float4 x = *reinterpret_cast<const float4*>(acc + idx * 8);
+    const float4 y = *reinterpret_cast<const float4*>(acc + idx * 8 + 4);
+    float f[8] = {x.x * scale, x.y * scale, x.z * scale, x.w * scale, y.x * scale, y.y * scale, y.z * scale, y.w * scale};
+    *reinterpret_cast<uint4*>(dq + b * sb + h * sh + (int64_t)i * st + c * 8) = pack8<T>(f);
+  }
+}
+
+// ------------------------------------------------------------------------------- host side
+int attn_bwd_tc05_status(int reset) { return read_dev_status(reset); }
+
+static int encode_bhtd(CUtensorMap* m, const void* ptr, const AttnStrides& s, int B, int H, int T, int hd, int dtype) {
+  const uint64_t dims[4] = {(uint64_t)hd, (uint64_t)T, (uint64_t)H, (uint64_t)B};
+  const uint64_t str[3] = {(uint64_t)s.t * 2, (uint64_t)s.h * 2, (uint64_t)s.b * 2};
+  const uint32_t box[4] = {64, 128, 1, 1};
+  return encode_tmap_sw128(m, ptr, dtype, 4, dims, str, box);
+}
+
+bool attn_tc05_bwd_eligible(const AttnArgs& a, int hd) {
+  return (hd == 64 || hd == 128) && a.T % 128 == 0 && a.bias_mode != 3;
+}
+
+template <typename T, int HD>
+static int bwd_tc05_launch(const AttnArgs& a, int dtype, cudaStream_t st) {
+  using Cfg = FbCfg<HD>;
+  int rc;
+  if ((rc = attn_delta(a, HD, dtype, st))) return rc;
+  const size_t acc_bytes = (size_t)a.B * a.H * a.T * HD * sizeof(float);
+  cudaError_t e = cudaMemsetAsync(a.dq_acc, 0, acc_bytes, st);
+  if (e != cudaSuccess) return fail(TFB_ERR_LAUNCH, "attention_bwd(tcgen05): memset: %s", cudaGetErrorString(e));
+  CUtensorMap tq, tk, tv, tdo;
+  if ((rc = encode_bhtd(&tq, a.q, a.sq, a.B, a.H, a.T, HD, dtype))) return rc;
+  if ((rc = encode_bhtd(&tk, a.k, a.sk, a.B, a.H, a.T, HD, dtype))) return rc;
+  if ((rc = encode_bhtd(&tv, a.v, a.sv, a.B, a.H, a.T, HD, dtype))) return rc;
+  if ((rc = encode_bhtd(&tdo, a.d_o, a.sdo, a.B, a.H, a.T, HD, dtype))) return rc;
+  FbParams p;
+  p.lse = a.lse; p.delta = a.delta; p.dq_acc = a.dq_acc; p.dk = a.dk; p.dv = a.dv;
+  p.sdk_b = a.sdk.b; p.sdk_h = a.sdk.h; p.sdk_t = a.sdk.t;
+  p.sdv_b = a.sdv.b; p.sdv_h = a.sdv.h; p.sdv_t = a.sdv.t;
+  p.H = a.H; p.T = a.T; p.scale = a.scale; p.bias_mode = a.bias_mode; p.slopes = a.slopes;
+  auto kern = attn_bwd_tc05_kernel<T, HD>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return fail(TFB_ERR_LAUNCH, "attention_bwd(tcgen05): smem attribute: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
+  dim3 grid(a.T / FB_T, a.B * a.H);
+  kern<<<grid, FB_THREADS, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
+  if ((rc = launched("attention_bwd(tcgen05)"))) return rc;
+  const int64_t nvec = (int64_t)a.B * a.H * a.T * HD / 8;
+  const unsigned blocks = (unsigned)(ceil_div(nvec, 256) < 148 * 8 ? ceil_div(nvec, 256) : 148 * 8);
+  attn_dq_convert_kernel<T><<<blocks, 256, 0, st>>>(a.dq_acc, (T*)a.dq, a.sdq.b, a.sdq.h, a.sdq.t, a.H, a.T, HD,
+                                                    a.scale, nvec);
+  return launched("attention_dq_convert");
+}
+
+int attn_tc05_bwd(const AttnArgs& a, int hd, int dtype, cudaStream_t st) {
+  TFB_DISPATCH_16(dtype, T, {
+    if (hd == 64) return bwd_tc05_launch<T, 64>(a, dtype, st);
+    return bwd_tc05_launch<T, 128>(a, dtype, st);
+  })
+}
+
+}  // namespace tfb

@@ -538,6 +538,12 @@ static int bwd_launch(const AttnArgs& a, cudaStream_t st) {
   return TFB_OK;
 }
 
+int attn_delta(const AttnArgs& a, int hd, int dtype, cudaStream_t st) {
+  const int64_t rows = (int64_t)a.B * a.H * a.T;
+  TFB_DISPATCH_16(dtype, T, { attn_delta_kernel<T><<<(unsigned)ceil_div(rows, 4), 128, 0, st>>>(a, hd); })
+  return launched("attention_delta");
+}
+
 int attn_generic_fwd(const AttnArgs& a, int hd, int dtype, cudaStream_t st) {
   TFB_DISPATCH_16(dtype, T, {
     if (hd == 32) return fwd_launch<T, 32>(a, st);

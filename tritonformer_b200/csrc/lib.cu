@@ -16,6 +16,7 @@ bool gemm_tc05_eligible(const void*, const void*, const void*, const void*, int6
                         int64_t, int64_t, int64_t, int64_t);
 int gemm_tc05_status(int reset);
 int attn_tc05_status(int reset);
+int attn_bwd_tc05_status(int reset);
 }  // namespace tfb
 
 using namespace tfb;
@@ -28,7 +29,8 @@ extern "C" int tfb_device_status(int reset) {
   cudaDeviceSynchronize();
   const int a = gemm_tc05_status(reset);
   const int b = attn_tc05_status(reset);
-  return a ? a : b;
+  const int c = attn_bwd_tc05_status(reset);
+  return a ? a : (b ? b : c);
 }
 
 extern "C" void tfb_debug_set(int key, int value) {
