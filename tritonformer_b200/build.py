@@ -1,6 +1,6 @@
 """Builds libtritonformer_b200.so (sm_100a only) from csrc/ with nvcc, in-tree.
 
-    python -m tritonformer_b200.build [--force]
+    python tritonformer_b200/build.py [--force]
 
 Objects are rebuilt when their source (or any header) is newer.  nvcc cross-compiles
 without a GPU, so this runs on a build host as well as on the B200 box.

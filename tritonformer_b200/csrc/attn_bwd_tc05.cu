@@ -22,6 +22,8 @@
 
 namespace tfb {
 
+extern std::atomic<int> g_attn_debug;
+
 constexpr float kLog2eB = 1.4426950408889634f;
 constexpr int FB_T = 128;           // tile edge (keys and queries)
 constexpr int FB_THREADS = 320;     // 10 warps
@@ -53,6 +55,7 @@ struct FbParams {
   float scale;
   int bias_mode;
   const float* slopes;
+  int debug;  // test switch: bit 0 skips the dQ accumulation (timing experiments only)
 };
 
 __device__ __forceinline__ float alibi_term_b(int mode, float slope, int dist) {
@@ -271,6 +274,7 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
           uint32_t v[32];
           tmem_ld32(lane_addr + Cfg::COL_DQ + col0, v);
           tc_wait_ld();
+          if (!(p.debug & 1))
 #pragma unroll
           for (int e = 0; e < 32; e += 4)
             asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + col0 + e),
@@ -374,6 +378,7 @@ static int bwd_tc05_launch(const AttnArgs& a, int dtype, cudaStream_t st) {
   p.sdk_b = a.sdk.b; p.sdk_h = a.sdk.h; p.sdk_t = a.sdk.t;
   p.sdv_b = a.sdv.b; p.sdv_h = a.sdv.h; p.sdv_t = a.sdv.t;
   p.H = a.H; p.T = a.T; p.scale = a.scale; p.bias_mode = a.bias_mode; p.slopes = a.slopes;
+  p.debug = g_attn_debug.load();
   auto kern = attn_bwd_tc05_kernel<T, HD>;
   static bool attr_set = false;
   if (!attr_set) {

@@ -7,6 +7,7 @@ thread_local char g_err[512] = {0};
 std::atomic<int64_t> g_launches{0};
 std::atomic<int> g_force_generic_gemm{0};
 std::atomic<int> g_force_fallback_attn{0};
+std::atomic<int> g_attn_debug{0};
 
 int gemm_generic(const void*, const void*, void*, const void*, int64_t, int64_t, int64_t, int64_t, int64_t,
                  int64_t, int64_t, int64_t, int, int, int, cudaStream_t);
@@ -36,6 +37,7 @@ extern "C" int tfb_device_status(int reset) {
 extern "C" void tfb_debug_set(int key, int value) {
   if (key == 0) g_force_generic_gemm.store(value);
   if (key == 1) g_force_fallback_attn.store(value);
+  if (key == 2) g_attn_debug.store(value);
 }
 
 extern "C" int tfb_gemm(const void* a, const void* b, void* c, const void* bias, int64_t M, int64_t N,
