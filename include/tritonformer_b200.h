@@ -71,6 +71,20 @@ int tfb_layernorm_bwd(const void* dy, const void* x, const void* alpha,
                       int64_t rows, int64_t d, int64_t dy_ld, int64_t x_ld, int64_t dx_ld,
                       int dtype, void* stream);
 
+/* LayerNorm backward for callers that cannot supply scratch memory (no counterpart in the
+ * reference, which allocates freely through torch): same results as tfb_layernorm_bwd, but the
+ * fp32 partial sums live in a fixed array inside the library image (about 9.7 MB, held by every
+ * GPU that loads the library) and the call allocates nothing.  Limit: d <= 4096; wider rows are
+ * rejected with TFB_ERR_UNSUPPORTED.  The first call on a device looks up the array's device
+ * address (with that device current); make that first call outside any stream capture.  All
+ * calls share the one array: two calls whose kernels overlap on the GPU (different streams)
+ * race on it, so keep them stream-ordered.                                                  */
+int tfb_layernorm_bwd_static(const void* dy, const void* x, const void* alpha,
+                             const float* mean, const float* rstd, void* dx,
+                             void* dalpha, void* dbeta,
+                             int64_t rows, int64_t d, int64_t dy_ld, int64_t x_ld, int64_t dx_ld,
+                             int dtype, void* stream);
+
 /* -------------------------------------------------------------------- Softmax
  * Replaces softmax_fwd / softmax_bwd (tritonformer/kernels/softmax.py:7-111).
  * Row softmax over the last dim; the backward writes a fresh tensor (the reference

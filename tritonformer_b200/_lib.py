@@ -28,6 +28,7 @@ _SIGNATURES = {
     "tfb_layernorm_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _f32, _i32, _vp]),
     "tfb_layernorm_bwd_partials": (_i64, [_i64, _i64]),
     "tfb_layernorm_bwd": (_i32, [_vp] * 9 + [_i64] * 6 + [_i32, _vp]),
+    "tfb_layernorm_bwd_static": (_i32, [_vp] * 8 + [_i64] * 5 + [_i32, _vp]),
     "tfb_softmax_fwd": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp]),
     "tfb_softmax_bwd": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
     "tfb_cross_entropy_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
@@ -47,7 +48,7 @@ EXPORTS = tuple(sorted(_SIGNATURES))
 def _load():
     if not os.path.exists(LIB_PATH):
         raise RuntimeError(
-            "tritonformer_b200: %s is missing. Build it with `python -m tritonformer_b200.build` "
+            "tritonformer_b200: %s is missing. Build it with `python tritonformer_b200/build.py` "
             "(needs nvcc); there is no fallback implementation." % LIB_PATH)
     lib = ctypes.CDLL(LIB_PATH)
     for name, (res, args) in _SIGNATURES.items():

@@ -310,3 +310,72 @@ extern "C" int tfb_layernorm_bwd(const void* dy, const void* x, const void* alph
                             (int)d, dy_ld, x_ld, dx_ld, vec, threads, st);
   })
 }
+
+// ------------------------------------------------------------------------------------------
+// LayerNorm backward without caller-provided scratch.
+//
+// Some hosts of this library cannot hand it scratch memory: a binding that marshals only the
+// operator's own inputs and outputs, or a service whose device memory is carved up once at
+// start-up and which keeps cudaMalloc / cudaFree (device-wide synchronising calls) off its
+// request path.  For them the fp32 partial column sums live in the fixed device array below
+// instead of a buffer the caller allocates.  The array belongs to the library image: every
+// GPU that loads the library carries it (kStaticRows * 2 * kStaticMaxD floats) until exit.
+constexpr int kStaticRows = 296;    // partial rows (two CTAs per SM)
+constexpr int kStaticMaxD = 4096;   // widest supported row
+static __device__ __align__(256) float g_ln_static_scratch[(size_t)kStaticRows * 2 * kStaticMaxD];
+
+namespace {
+struct StaticScratch {
+  std::atomic<float*> ptr[64];
+};
+StaticScratch g_static_scratch;
+
+// Device address of the array on the current device.  `g_ln_static_scratch` named in host code
+// is only a handle for the runtime, not something a kernel may dereference; the address has
+// to be asked for once per device, with that device current.
+int static_scratch_for_current_device(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64)
+    return tfb::fail(TFB_ERR_LAUNCH, "layernorm_bwd_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  float* p = g_static_scratch.ptr[dev].load(std::memory_order_acquire);
+  if (!p) {
+    void* sym = nullptr;
+    e = cudaGetSymbolAddress(&sym, g_ln_static_scratch);
+    if (e != cudaSuccess || !sym)
+      return tfb::fail(TFB_ERR_LAUNCH, "layernorm_bwd_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    p = static_cast<float*>(sym);
+    g_static_scratch.ptr[dev].store(p, std::memory_order_release);
+  }
+  *out = p;
+  return TFB_OK;
+}
+}  // namespace
+
+extern "C" int tfb_layernorm_bwd_static(const void* dy, const void* x, const void* alpha, const float* mean,
+                                        const float* rstd, void* dx, void* dalpha, void* dbeta, int64_t rows,
+                                        int64_t d, int64_t dy_ld, int64_t x_ld, int64_t dx_ld, int dtype,
+                                        void* stream) {
+  TFB_REQUIRE(rows > 0 && d > 0, "layernorm_bwd_static: bad shape rows=%lld d=%lld", (long long)rows, (long long)d);
+  if (d > kStaticMaxD)
+    return fail(TFB_ERR_UNSUPPORTED,
+                "layernorm_bwd_static: d=%lld exceeds the built-in scratch (rows of at most %d elements); "
+                "use tfb_layernorm_bwd with caller-provided scratch",
+                (long long)d, kStaticMaxD);
+  TFB_REQUIRE(dy_ld >= d && x_ld >= d && dx_ld >= d, "layernorm_bwd_static: row stride smaller than d");
+  float* scratch = nullptr;
+  int rc = static_scratch_for_current_device(&scratch);
+  if (rc) return rc;
+  int64_t n = ceil_div(rows, LN_RB);
+  if (n > kStaticRows) n = kStaticRows;
+  // Every one of the n partial rows is rewritten in full by the first kernel before the second
+  // reads it, so nothing in the array has to be cleared between calls.
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool vec = (d % 8 == 0) && (x_ld % 8 == 0) && (dy_ld % 8 == 0) && (dx_ld % 8 == 0) && aligned16(x) &&
+                   aligned16(dy) && aligned16(dx);
+  const int threads = ln_bwd_threads(d);
+  TFB_DISPATCH_16(dtype, T, {
+    return ln_bwd_launch<T>(dy, x, alpha, mean, rstd, dx, dalpha, dbeta, scratch, n, rows, (int)d, dy_ld, x_ld,
+                            dx_ld, vec, threads, st);
+  })
+}
