@@ -337,6 +337,146 @@ def run_b200_arm(args):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------ per-kernel micro-benchmarks
+def _time_cuda(fn, iters, warmup):
+    """Seconds per call, device time only: the calls are captured into a CUDA graph and replayed so
+    that host-side launch work is not part of the measurement."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(warmup):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(iters):
+            fn()
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e-3
+
+
+def run_kernel_bench(args):
+    """Isolated kernels through the C ABI on synthetic inputs: one JSON line per case with the achieved
+    rate against the measured peak (burst bf16 cuBLAS for tensor kernels, STREAM-style copy for HBM ones).
+    HBM-bound cases use inputs larger than the 126 MB L2."""
+    import ctypes
+    import tritonformer_b200._lib as L
+    from tritonformer_b200 import attention as A
+    from tritonformer_b200 import crossentropy as CE
+    from tritonformer_b200 import layernorm as LN
+    from tritonformer_b200 import linear as LIN
+    from tritonformer_b200 import softmax as SM
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = measured_peaks()
+    iters, warmup = (1, 1) if args.small else (args.steps, max(args.warmup, 3))
+    out = []
+
+    def emit(kernel, case, seconds, work, unit, bound):
+        peak = peaks["tflops_burst"] if bound == "tensor" else peaks["hbm_gbs"]
+        ach = work / seconds / (1e12 if bound == "tensor" else 1e9)
+        line = {"kernel": kernel, "case": case, "us": seconds * 1e6,
+                "roofline": {"bound": bound, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak,
+                             "peak_source": peaks["source"]}}
+        out.append(line)
+        print(json.dumps(line), flush=True)
+
+    torch.manual_seed(0)
+    which = args.kernel
+    if which in ("gemm", "all"):
+        shapes = [("fwd proj", 8192, 1024, 1024, False, True), ("fwd fc1", 8192, 4096, 1024, False, True),
+                  ("fwd fc2", 8192, 1024, 4096, False, True), ("fwd head", 8192, 50304, 1024, False, True),
+                  ("dX fc1", 8192, 1024, 4096, False, False), ("dX head", 8192, 1024, 50304, False, False),
+                  ("dW proj", 1024, 1024, 8192, True, True), ("dW fc1", 1024, 4096, 8192, True, True),
+                  ("dW head", 1024, 50304, 8192, True, True)]
+        if args.small:
+            shapes = shapes[1:2] + shapes[6:7]
+        for name, m, n, k, a_mn, b_mn in shapes:
+            a = torch.randn((k, m) if a_mn else (m, k), device=dev).half()
+            b = torch.randn((k, n) if b_mn else (n, k), device=dev).half()
+            c = torch.empty((m, n), device=dev, dtype=torch.float16)
+            a_sm, a_sk = (1, m) if a_mn else (k, 1)
+            b_sk, b_sn = (n, 1) if b_mn else (1, k)
+            fn = lambda: LIN.gemm(a, a_sm, a_sk, b, b_sk, b_sn, m, n, k, out=c)
+            emit("gemm_tc05_kernel", f"{name} M{m} N{n} K{k}", _time_cuda(fn, iters, warmup), 2.0 * m * n * k,
+                 "TFLOP/s", "tensor")
+    if which in ("attn", "all"):
+        cases = [("B4 H16 T2048 hd64 fp16", 4, 16, 2048, 64, torch.float16, False),
+                 ("B4 H16 T2048 hd64 fp16 ALiBi", 4, 16, 2048, 64, torch.float16, True),
+                 ("B1 H12 T4096 hd128 fp16", 1, 12, 4096, 128, torch.float16, False),
+                 ("B2 H16 T2048 hd128 bf16 ALiBi", 2, 16, 2048, 128, torch.bfloat16, True)]
+        if args.small:
+            cases = [("B1 H8 T2048 hd64 fp16", 1, 8, 2048, 64, torch.float16, False)]
+        for name, bsz, h, t, hd, dt, alibi in cases:
+            mk = lambda: torch.randn((bsz, t, h * hd), device=dev).to(dt).view(bsz, t, h, hd).transpose(1, 2)
+            q, k, v, do = mk(), mk(), mk(), mk()
+            slopes = torch.tensor([2.0 ** (-8.0 * (i + 1) / h) for i in range(h)], device=dev) if alibi else None
+            bias = A._Bias(slopes=slopes)
+            res = {}
+            def fwd():
+                res["o"], res["lse"], _ = A.attention_forward(q, k, v, bias)
+            fl = 2.0 * bsz * h * t * t * hd  # two products, causal half
+            emit("attn_fwd_tc05_kernel", name, _time_cuda(fwd, iters, warmup), fl, "TFLOP/s", "tensor")
+            bwd = lambda: A.attention_backward(do, res["o"], q, k, v, res["lse"], bias)
+            emit("attn_bwd_tc05_kernel (+delta, dQ convert)", name, _time_cuda(bwd, iters, warmup), 2.5 * fl,
+                 "TFLOP/s", "tensor")
+    if which in ("layernorm", "all"):
+        rows, d = (32768, 1024) if args.small else (131072, 1024)
+        x = torch.randn((rows, d), device=dev).half()
+        dy = torch.randn((rows, d), device=dev).half()
+        al, be = torch.randn(d, device=dev).half(), torch.randn(d, device=dev).half()
+        res = {}
+        def fwd():
+            res["y"], res["st"] = LN.layernorm_forward(x, al, be, 1e-5)
+        emit("ln_fwd_vec_kernel", f"rows {rows} d {d} fp16", _time_cuda(fwd, iters, warmup), 4.0 * rows * d, "GB/s", "hbm")
+        bwd = lambda: LN.layernorm_backward(dy, x, al, res["st"])
+        emit("ln_bwd_kernel (+finalize)", f"rows {rows} d {d} fp16", _time_cuda(bwd, iters, warmup), 6.0 * rows * d,
+             "GB/s", "hbm")
+    if which in ("crossentropy", "all"):
+        n, v = (2048, 50304) if args.small else (8188, 50304)
+        logits = torch.randn((n, v), device=dev).half()
+        labels = torch.randint(0, v, (n,), device=dev)
+        loss = torch.empty(n, device=dev, dtype=torch.float16)
+        lse = torch.empty(n, device=dev, dtype=torch.float32)
+        g = torch.ones(n, device=dev, dtype=torch.float16)
+        dl = torch.empty_like(logits)
+        st = L.stream_ptr(dev)
+        fwd = lambda: L.check(L.lib.tfb_cross_entropy_fwd(logits.data_ptr(), labels.data_ptr(), loss.data_ptr(), None,
+                                                          lse.data_ptr(), n, v, v, 0, st))
+        emit("ce_fwd_kernel", f"rows {n} vocab {v} fp16", _time_cuda(fwd, iters, warmup), 2.0 * n * v, "GB/s", "hbm")
+        bwd = lambda: L.check(L.lib.tfb_cross_entropy_bwd(logits.data_ptr(), labels.data_ptr(), lse.data_ptr(),
+                                                          g.data_ptr(), 1, dl.data_ptr(), n, v, v, v, 0, st))
+        emit("ce_bwd_kernel", f"rows {n} vocab {v} fp16", _time_cuda(bwd, iters, warmup), 4.0 * n * v, "GB/s", "hbm")
+    if which in ("softmax", "all"):
+        rows, cols = (65536, 1024) if args.small else (131072, 1024)
+        x = torch.randn((1, rows, cols), device=dev)
+        dy = torch.randn((1, rows, cols), device=dev)
+        y = torch.empty_like(x)
+        dx = torch.empty_like(x)
+        st = L.stream_ptr(dev)
+        fwd = lambda: L.check(L.lib.tfb_softmax_fwd(x.data_ptr(), y.data_ptr(), rows, cols, cols, cols, 2, st))
+        emit("softmax_fwd_vec_kernel", f"rows {rows} cols {cols} fp32", _time_cuda(fwd, iters, warmup), 8.0 * rows * cols,
+             "GB/s", "hbm")
+        bwd = lambda: L.check(L.lib.tfb_softmax_bwd(dy.data_ptr(), y.data_ptr(), dx.data_ptr(), rows, cols, cols, cols,
+                                                    cols, 2, st))
+        emit("softmax_bwd_vec_kernel", f"rows {rows} cols {cols} fp32", _time_cuda(bwd, iters, warmup),
+             12.0 * rows * cols, "GB/s", "hbm")
+    if which in ("relu", "all"):
+        n = 8192 * 4096 * (1 if args.small else 4)
+        a, b = torch.randn(n, device=dev).half(), torch.randn(n, device=dev).half()
+        emit("relu_bwd_vec_kernel", f"{n} elements fp16", _time_cuda(lambda: LIN.relu_backward(a, b), iters, warmup),
+             6.0 * n, "GB/s", "hbm")
+    assert L.device_status() == 0
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -346,8 +486,14 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--kernel", default=None,
+                    choices=["all", "gemm", "attn", "layernorm", "crossentropy", "softmax", "relu"],
+                    help="run the isolated-kernel micro-benchmarks instead of the model step")
+    ap.add_argument("--small", action="store_true", help="with --kernel: one small case, one launch (for ncu captures)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.kernel:
+        run_kernel_bench(args)
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_b200_arm(args)

@@ -5,6 +5,7 @@ namespace tfb {
 extern std::atomic<int> g_force_fallback_attn;
 bool attn_tc05_fwd_eligible(const AttnArgs& a, int hd);
 int attn_tc05_fwd(const AttnArgs& a, int hd, int dtype, cudaStream_t st);
+int attn_fwd2_tc05(const AttnArgs& a, int dtype, cudaStream_t st);
 bool attn_tc05_bwd_eligible(const AttnArgs& a, int hd);
 int attn_tc05_bwd(const AttnArgs& a, int hd, int dtype, cudaStream_t st);
 }  // namespace tfb
@@ -50,6 +51,7 @@ extern "C" int tfb_attention_fwd(const void* q, const void* k, const void* v, vo
   a.slopes = slopes; a.bias = bias; a.bias_sh = bias_sh; a.bias_si = bias_si;
   const bool fast = !g_force_fallback_attn.load() && attn_tc05_fwd_eligible(a, (int)hd);
   if (path) *path = fast ? 1 : 0;
+  if (fast && hd == 64) return attn_fwd2_tc05(a, dtype, (cudaStream_t)stream);  // two query tiles per CTA
   if (fast) return attn_tc05_fwd(a, (int)hd, dtype, (cudaStream_t)stream);
   return attn_generic_fwd(a, (int)hd, dtype, (cudaStream_t)stream);
 }

@@ -42,7 +42,10 @@ template <int HD> struct FbCfg {
   static constexpr int OFF_STAT = OFF_DS + 32768;                    // lse2[128], delta[128] fp32
   static constexpr int OFF_BAR = OFF_STAT + 1024;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
-  static constexpr int COL_S = 0, COL_DQ = 0, COL_DP = 128, COL_DV = 256, COL_DK = 256 + HD;
+  static constexpr int COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 256 + HD;
+  // dQ_i has columns of its own when they fit (hd 64); otherwise it reuses the Sᵀ columns
+  static constexpr bool DQ_ALIASED = (256 + 3 * HD > 512);
+  static constexpr int COL_DQ = DQ_ALIASED ? 0 : 256 + 2 * HD;
 };
 
 struct FbParams {
@@ -64,9 +67,15 @@ __device__ __forceinline__ float alibi_term_b(int mode, float slope, int dist) {
   return __bfloat162float(__hmul(__float2bfloat16_rn(-(float)dist), __float2bfloat16_rn(slope)));
 }
 
+__device__ __forceinline__ float ex2_approx_b(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ void compute_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
-template <typename T, int HD>
+template <typename T, int HD, bool BIAS>
 __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __grid_constant__ CUtensorMap tmQ,
                                                                       const __grid_constant__ CUtensorMap tmK,
                                                                       const __grid_constant__ CUtensorMap tmV,
@@ -155,14 +164,15 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
       const uint32_t sk = smem_u32(smem + Cfg::OFF_K), sv = smem_u32(smem + Cfg::OFF_V);
       const uint32_t sp = smem_u32(smem + Cfg::OFF_P), sds = smem_u32(smem + Cfg::OFF_DS);
       bool ok = mbar_wait(kv_full, 0, 0x2200, abort_flag);
-      for (int it = 0; it < iters && ok; ++it) {
+      // Sᵀ = K Q_iᵀ and dPᵀ = V dO_iᵀ of query tile `it`
+      auto issue_scores = [&](int it) -> bool {
         const int st = it % QS;
+        if (!mbar_wait(&q_full[st], (it / QS) & 1, 0x2300 | st, abort_flag)) return false;
+        // when dQ shares the Sᵀ columns, the previous dQ must have been drained first
+        if (Cfg::DQ_ALIASED && it > 0 && !mbar_wait(dq_free, (it - 1) & 1, 0x2400, abort_flag)) return false;
+        tc_fence_after();
         const uint32_t sq = smem_u32(smem + Cfg::OFF_Q + st * Cfg::TILE_BYTES);
         const uint32_t sdo = smem_u32(smem + Cfg::OFF_DO + st * Cfg::TILE_BYTES);
-        if (!mbar_wait(&q_full[st], (it / QS) & 1, 0x2300 | st, abort_flag)) { ok = false; break; }
-        // the dQ of the previous query tile lives in the Sᵀ columns until the compute warps drained it
-        if (it > 0 && !mbar_wait(dq_free, (it - 1) & 1, 0x2400, abort_flag)) { ok = false; break; }
-        tc_fence_after();
 #pragma unroll
         for (int s = 0; s < HD / 16; ++s) {
           const uint32_t off = (s / 4) * 16384 + (s % 4) * 32;
@@ -176,7 +186,16 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
                     idesc_s, s ? 1u : 0u);
         }
         tc_commit(s_full);
+        return true;
+      };
+      if (ok) ok = issue_scores(0);
+      for (int it = 0; it < iters && ok; ++it) {
+        const int st = it % QS;
+        const uint32_t sq = smem_u32(smem + Cfg::OFF_Q + st * Cfg::TILE_BYTES);
+        const uint32_t sdo = smem_u32(smem + Cfg::OFF_DO + st * Cfg::TILE_BYTES);
         if (!mbar_wait(pds_full, it & 1, 0x2500, abort_flag)) { ok = false; break; }
+        // dQ columns of their own: the previous dQ must have been drained before it is overwritten
+        if (!Cfg::DQ_ALIASED && it > 0 && !mbar_wait(dq_free, (it - 1) & 1, 0x2400, abort_flag)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int s = 0; s < FB_T / 16; ++s) {  // contraction over the 128 queries of this tile
@@ -195,6 +214,8 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
         }
         tc_commit(&q_empty[st]);
         tc_commit(dq_full);
+        // the next tile's scores run on the tensor core while the compute warps drain dQ_i
+        if (it + 1 < iters) ok = issue_scores(it + 1);
       }
     }
   } else if (!dead) {
@@ -232,17 +253,26 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
           tc_wait_ld();
           float pf[32], df[32];
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int il = col0 + e;
-            const int i = i0 + il;
-            float x = __uint_as_float(sv_[e]) * c2;
-            if (p.bias_mode) x += alibi_term_b(p.bias_mode, slope, max(i - j, 0)) * kLog2eB;
-            float pe = exp2f(x - s_lse2[il]);
-            if (diag && j > i) pe = 0.f;
-            // P is rounded to the element type before it meets dP, as the tensor core sees it
-            const float pr = Num<T>::to_f(Num<T>::from_f(pe));
-            pf[e] = pe;
-            df[e] = pr * (__uint_as_float(dv_[e]) - s_delta[il]);
+          for (int e4 = 0; e4 < 8; ++e4) {
+            const float4 l4 = *reinterpret_cast<const float4*>(s_lse2 + col0 + e4 * 4);
+            const float4 d4 = *reinterpret_cast<const float4*>(s_delta + col0 + e4 * 4);
+            const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
+            const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const int e = e4 * 4 + k;
+              float pe;
+              if (!BIAS && !diag) {
+                pe = ex2_approx_b(fmaf(__uint_as_float(sv_[e]), c2, -lv[k]));
+              } else {
+                const int i = i0 + col0 + e;
+                float x = fmaf(__uint_as_float(sv_[e]), c2, -lv[k]);
+                if (BIAS) x += alibi_term_b(p.bias_mode, slope, max(i - j, 0)) * kLog2eB;
+                pe = (j > i) ? 0.f : ex2_approx_b(x);
+              }
+              pf[e] = pe;
+              df[e] = pe * (__uint_as_float(dv_[e]) - dl[k]);
+            }
           }
 #pragma unroll
           for (int v4 = 0; v4 < 4; ++v4) {
@@ -379,15 +409,17 @@ static int bwd_tc05_launch(const AttnArgs& a, int dtype, cudaStream_t st) {
   p.sdv_b = a.sdv.b; p.sdv_h = a.sdv.h; p.sdv_t = a.sdv.t;
   p.H = a.H; p.T = a.T; p.scale = a.scale; p.bias_mode = a.bias_mode; p.slopes = a.slopes;
   p.debug = g_attn_debug.load();
-  auto kern = attn_bwd_tc05_kernel<T, HD>;
   static bool attr_set = false;
   if (!attr_set) {
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    e = cudaFuncSetAttribute(attn_bwd_tc05_kernel<T, HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_bwd_tc05_kernel<T, HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return fail(TFB_ERR_LAUNCH, "attention_bwd(tcgen05): smem attribute: %s", cudaGetErrorString(e));
     attr_set = true;
   }
   dim3 grid(a.T / FB_T, a.B * a.H);
-  kern<<<grid, FB_THREADS, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
+  if (a.bias_mode) attn_bwd_tc05_kernel<T, HD, true><<<grid, FB_THREADS, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
+  else attn_bwd_tc05_kernel<T, HD, false><<<grid, FB_THREADS, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
   if ((rc = launched("attention_bwd(tcgen05)"))) return rc;
   const int64_t nvec = (int64_t)a.B * a.H * a.T * HD / 8;
   const unsigned blocks = (unsigned)(ceil_div(nvec, 256) < 148 * 8 ? ceil_div(nvec, 256) : 148 * 8);

@@ -1,0 +1,395 @@
+// Causal flash attention forward on tcgen05 / TMEM, two query tiles per CTA (head_dim 64, T % 128 == 0).
+//
+// One CTA owns 256 consecutive queries of one (batch, head) as two 128-row tiles A and B, each with
+// its own score buffer and output accumulator in TMEM and its own four softmax warps.  The tensor
+// core alternates between the tiles: while the warps of one tile turn scores into probabilities, it
+// multiplies the other tile's probabilities with V and computes that tile's next scores, so the
+// exponential unit and the tensor core both stay busy.  K_j / V_j tiles (128 keys) are loaded once
+// per CTA through 2-stage TMA rings and serve both query tiles.
+//   warp 0      TMA producer
+//   warp 1      MMA issuer (one elected lane)
+//   warps 2-5   softmax of tile A        warps 6-9   softmax of tile B
+// A softmax thread owns one query row (= TMEM lane): it reads its 128 scores into registers once,
+// applies scale / ALiBi / causal mask in the log2 domain, and updates the running maximum lazily
+// (the accumulator row is rescaled only when the maximum grew by more than 2^8; P stays below 2^8,
+// inside fp16/bf16 range), so in the steady state no TMEM round trip of O is needed.
+// TMEM columns: [0,128) S_A, [128,256) S_B, [256,320) O_A, [320,384) O_B.
+#include "attn.cuh"
+#include "tc05.cuh"
+#include <type_traits>
+
+namespace tfb {
+
+namespace {
+
+constexpr float kLog2e2 = 1.4426950408889634f;
+constexpr float kLn2_2 = 0.6931471805599453f;
+constexpr int F2_HD = 64;
+constexpr int F2_TILE = 128;
+constexpr int F2_THREADS = 320;
+constexpr int F2_TILE_BYTES = 16384;  // 128 rows x 64 x 2 B
+constexpr int F2_OFF_Q = 0;                        // [2]
+constexpr int F2_OFF_K = 2 * F2_TILE_BYTES;        // [2]
+constexpr int F2_OFF_V = 4 * F2_TILE_BYTES;        // [2]
+constexpr int F2_OFF_P = 6 * F2_TILE_BYTES;        // [2] x 32 KB
+constexpr int F2_OFF_BAR = F2_OFF_P + 2 * 32768;
+constexpr int F2_SMEM_BYTES = F2_OFF_BAR + 256 + 1024;
+constexpr int F2_COL_S = 0, F2_COL_O = 256;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+struct F2Params {
+  void* out;
+  float* lse;
+  int64_t so_b, so_h, so_t;
+  int H, T;
+  float scale;
+  int bias_mode;
+  const float* slopes;
+};
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ float alibi_term2(int mode, float slope, int dist) {
+  if (mode == 1) return -slope * (float)dist;
+  if (mode == 2) return __half2float(__hmul(__float2half_rn(-(float)dist), __float2half_rn(slope)));
+  return __bfloat162float(__hmul(__float2bfloat16_rn(-(float)dist), __float2bfloat16_rn(slope)));
+}
+
+}  // namespace
+
+template <typename T, bool BIAS>
+__global__ void __launch_bounds__(F2_THREADS, 1) attn_fwd2_tc05_kernel(const __grid_constant__ CUtensorMap tmQ,
+                                                                       const __grid_constant__ CUtensorMap tmK,
+                                                                       const __grid_constant__ CUtensorMap tmV,
+                                                                       const F2Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + F2_OFF_BAR);
+  uint64_t* q_full = bars + 0;
+  uint64_t* k_full = bars + 1;    // [2]
+  uint64_t* k_empty = bars + 3;   // [2]
+  uint64_t* v_full = bars + 5;    // [2]
+  uint64_t* v_empty = bars + 7;   // [2]
+  uint64_t* s_full = bars + 9;    // [2 tiles] scores of the tile are in TMEM
+  uint64_t* p_full = bars + 11;   // [2 tiles] probabilities in smem, accumulator rescaled
+  uint64_t* pv_done = bars + 13;  // [2 tiles] P·V of the tile retired
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nq = p.T / F2_TILE;                      // query tiles in the sequence
+  const int pair = (gridDim.x - 1) - blockIdx.x;     // longest rows first
+  const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
+  const int tile_a = 2 * pair, tile_b = 2 * pair + 1;
+  const bool has_b = tile_b < nq;
+  const int last_a = tile_a;                         // last key tile each query tile attends to
+  const int last_b = tile_b;
+  const int jmax = has_b ? last_b : last_a;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 4);
+      mbar_init(&pv_done[i], 1);
+    }
+    *abort_flag = (*(volatile int*)&g_dev_status != 0) ? 1 : 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tmem_alloc(tmem_holder, 512);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const bool dead = *abort_flag != 0;
+
+  if (warp == 0) {
+    // --------------------------------------------------------------------- TMA producer
+    if (lane == 0 && !dead) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      mbar_expect_tx(q_full, (has_b ? 2 : 1) * F2_TILE_BYTES);
+      tma_load_4d(smem + F2_OFF_Q, &tmQ, 0, tile_a * F2_TILE, h, b, q_full);
+      if (has_b) tma_load_4d(smem + F2_OFF_Q + F2_TILE_BYTES, &tmQ, 0, tile_b * F2_TILE, h, b, q_full);
+      for (int j = 0; j <= jmax; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&k_empty[st], ph ^ 1, 0x3100 | st, abort_flag)) break;
+        mbar_expect_tx(&k_full[st], F2_TILE_BYTES);
+        tma_load_4d(smem + F2_OFF_K + st * F2_TILE_BYTES, &tmK, 0, j * F2_TILE, h, b, &k_full[st]);
+        if (!mbar_wait(&v_empty[st], ph ^ 1, 0x3200 | st, abort_flag)) break;
+        mbar_expect_tx(&v_full[st], F2_TILE_BYTES);
+        tma_load_4d(smem + F2_OFF_V + st * F2_TILE_BYTES, &tmV, 0, j * F2_TILE, h, b, &v_full[st]);
+      }
+    }
+  } else if (warp == 1) {
+    // ----------------------------------------------------------------------- MMA issuer
+    if (lane == 0 && !dead) {
+      constexpr int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+      constexpr uint32_t idesc_s = instr_desc_f16(128, 128, fmt, 0, 0);
+      constexpr uint32_t idesc_o = instr_desc_f16(128, F2_HD, fmt, 0, 1);
+      bool ok = mbar_wait(q_full, 0, 0x3300, abort_flag);
+      int k_ready = -1, v_ready = -1;  // highest key tile whose K / V load has been waited for
+      auto active = [&](int x, int j) { return x == 0 ? (j <= last_a) : (has_b && j <= last_b); };
+      // S_x(j) = Q_x K_jᵀ
+      auto issue_s = [&](int x, int j) -> bool {
+        const int st = j & 1;
+        if (k_ready < j) {
+          if (!mbar_wait(&k_full[st], (j >> 1) & 1, 0x3400 | st, abort_flag)) return false;
+          k_ready = j;
+        }
+        tc_fence_after();
+        const uint32_t sq = smem_u32(smem + F2_OFF_Q + x * F2_TILE_BYTES);
+        const uint32_t sk = smem_u32(smem + F2_OFF_K + st * F2_TILE_BYTES);
+#pragma unroll
+        for (int s = 0; s < F2_HD / 16; ++s)
+          tc_mma_ss(tmem_base + F2_COL_S + x * 128, smem_desc_sw128(sq + s * 32, 16, 1024),
+                    smem_desc_sw128(sk + s * 32, 16, 1024), idesc_s, s ? 1u : 0u);
+        tc_commit(&s_full[x]);
+        // K_j is free once the last query tile that attends to it has been multiplied
+        const bool last_user = (x == 1) || !active(1, j);
+        if (last_user) tc_commit(&k_empty[st]);
+        return true;
+      };
+      // O_x += P_x(j) V_j
+      auto issue_pv = [&](int x, int j) -> bool {
+        const int st = j & 1;
+        if (!mbar_wait(&p_full[x], j & 1, 0x3500 | x, abort_flag)) return false;
+        if (v_ready < j) {
+          if (!mbar_wait(&v_full[st], (j >> 1) & 1, 0x3600 | st, abort_flag)) return false;
+          v_ready = j;
+        }
+        tc_fence_after();
+        const uint32_t sp = smem_u32(smem + F2_OFF_P + x * 32768);
+        const uint32_t sv = smem_u32(smem + F2_OFF_V + st * F2_TILE_BYTES);
+#pragma unroll
+        for (int s = 0; s < F2_TILE / 16; ++s)
+          tc_mma_ss(tmem_base + F2_COL_O + x * F2_HD, smem_desc_sw128(sp + (s / 4) * 16384 + (s % 4) * 32, 16, 1024),
+                    smem_desc_sw128(sv + s * 2048, 16384, 1024), idesc_o, (j | s) ? 1u : 0u);
+        tc_commit(&pv_done[x]);
+        const bool last_user = (x == 1) || !active(1, j);
+        if (last_user) tc_commit(&v_empty[st]);
+        return true;
+      };
+      if (ok) ok = issue_s(0, 0);
+      if (ok && has_b) ok = issue_s(1, 0);
+      for (int j = 0; j <= jmax && ok; ++j) {
+        for (int x = 0; x < 2 && ok; ++x) {
+          if (!active(x, j)) continue;
+          ok = issue_pv(x, j);
+          if (ok && active(x, j + 1)) ok = issue_s(x, j + 1);
+        }
+      }
+    }
+  } else if (!dead) {
+    // -------------------------------------------------------------------------- softmax
+    const int x = (warp - 2) >> 2;     // query tile of this warp: 0 = A, 1 = B
+    const int qd = warp & 3;           // TMEM lane quarter
+    if (x == 0 || has_b) {
+      const int r = qd * 32 + lane;    // row within the tile == TMEM lane
+      const int my_tile = x == 0 ? tile_a : tile_b;
+      const int i = my_tile * F2_TILE + r;
+      const int jlast = x == 0 ? last_a : last_b;
+      const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
+      const uint32_t s_addr = lane_addr + F2_COL_S + x * 128;
+      const uint32_t o_addr = lane_addr + F2_COL_O + x * F2_HD;
+      const float c2 = p.scale * kLog2e2;
+      const float slope = p.bias_mode ? p.slopes[h] : 0.f;
+      uint8_t* sp = smem + F2_OFF_P + x * 32768;
+      float m_run = -INFINITY;   // true running maximum
+      float m_used = -INFINITY;  // maximum the accumulator and the running sum are expressed against
+      float l_run = 0.f;
+      bool ok = true;
+      for (int j = 0; j <= jlast && ok; ++j) {
+        const int j0 = j * F2_TILE;
+        const bool diag = (j == jlast);
+        const bool plain = !BIAS && !diag;  // scores need only the common scale
+        if (!mbar_wait(&s_full[x], j & 1, 0x3700 | x, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        // ---- pass 1: row maximum (four independent chains; the next chunk is in flight meanwhile)
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        {
+          uint32_t buf[2][32];
+          tmem_ld32(s_addr, buf[0]);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            tc_wait_ld();
+            if (c < 3) tmem_ld32(s_addr + (c + 1) * 32, buf[(c + 1) & 1]);
+            const uint32_t* v = buf[c & 1];
+            if (plain) {
+#pragma unroll
+              for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(v[e]));
+            } else {
+#pragma unroll
+              for (int e = 0; e < 32; ++e) {
+                const int jj = j0 + c * 32 + e;
+                float t = __uint_as_float(v[e]) * c2;
+                if (BIAS) t += alibi_term2(p.bias_mode, slope, max(i - jj, 0)) * kLog2e2;
+                if (jj > i) t = -INFINITY;
+                mx4[e & 3] = fmaxf(mx4[e & 3], t);
+              }
+            }
+          }
+        }
+        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        if (plain) mx *= c2;  // c2 > 0: scaling commutes with the maximum
+        m_run = fmaxf(m_run, mx);
+        // the previous P·V of this tile must have retired before P's buffer or O is touched
+        if (j > 0 && !mbar_wait(&pv_done[x], (j - 1) & 1, 0x3800 | x, abort_flag)) { ok = false; break; }
+        if (j == 0) {
+          m_used = m_run;
+        } else {
+          const bool grow = (m_run - m_used) > kRescaleThreshold;
+          if (__any_sync(0xffffffffu, grow)) {
+            tc_fence_after();
+            const float f = grow ? ex2_approx(m_used - m_run) : 1.f;
+#pragma unroll
+            for (int c = 0; c < F2_HD / 32; ++c) {
+              uint32_t v[32];
+              tmem_ld32(o_addr + c * 32, v);
+              tc_wait_ld();
+#pragma unroll
+              for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * f);
+              tmem_st32(o_addr + c * 32, v);
+            }
+            tc_wait_st();
+            l_run *= f;
+            if (grow) m_used = m_run;
+          }
+        }
+        // ---- pass 2: p = 2^(s - m_used), partial row sums, P into swizzled smem
+        float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+          uint32_t buf[2][32];
+          tmem_ld32(s_addr, buf[0]);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            tc_wait_ld();
+            if (c < 3) tmem_ld32(s_addr + (c + 1) * 32, buf[(c + 1) & 1]);
+            const uint32_t* v = buf[c & 1];
+            float g[32];
+            if (plain) {
+              const float neg_m = -m_used;
+#pragma unroll
+              for (int e = 0; e < 32; ++e) g[e] = ex2_approx(fmaf(__uint_as_float(v[e]), c2, neg_m));
+            } else {
+#pragma unroll
+              for (int e = 0; e < 32; ++e) {
+                const int jj = j0 + c * 32 + e;
+                float t = __uint_as_float(v[e]) * c2;
+                if (BIAS) t += alibi_term2(p.bias_mode, slope, max(i - jj, 0)) * kLog2e2;
+                g[e] = (jj > i) ? 0.f : ex2_approx(t - m_used);
+              }
+            }
+#pragma unroll
+            for (int e = 0; e < 32; ++e) ls4[e & 3] += g[e];
+#pragma unroll
+            for (int v4 = 0; v4 < 4; ++v4) {
+              float h8[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) h8[e] = g[v4 * 8 + e];
+              const int cc = c * 4 + v4;  // 16-byte chunk index along the 128 keys
+              uint8_t* dst = sp + (cc >> 3) * 16384 + r * 128 + (((cc & 7) ^ (r & 7)) << 4);
+              *reinterpret_cast<uint4*>(dst) = pack8<T>(h8);
+            }
+          }
+        }
+        l_run += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+        tc_fence_before();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[x]);
+      }
+      if (ok && mbar_wait(&pv_done[x], jlast & 1, 0x3900 | x, abort_flag)) {
+        tc_fence_after();
+        const float inv = 1.f / l_run;
+        T* orow = reinterpret_cast<T*>(p.out) + b * p.so_b + h * p.so_h + (int64_t)i * p.so_t;
+#pragma unroll
+        for (int c = 0; c < F2_HD / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld32(o_addr + c * 32, v);
+          tc_wait_ld();
+#pragma unroll
+          for (int v4 = 0; v4 < 4; ++v4) {
+            float g[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) g[e] = __uint_as_float(v[v4 * 8 + e]) * inv;
+            *reinterpret_cast<uint4*>(orow + c * 32 + v4 * 8) = pack8<T>(g);
+          }
+        }
+        p.lse[(int64_t)bh * p.T + i] = (m_used + log2f(l_run)) * kLn2_2;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int k = 0; k < 64; ++k) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------- host side
+int attn_fwd2_tc05_status(int reset) { return read_dev_status(reset); }
+
+template <typename T>
+static int fwd2_launch(const AttnArgs& a, int dtype, cudaStream_t st) {
+  CUtensorMap tq, tk, tv;
+  int rc;
+  const uint32_t box[4] = {64, 128, 1, 1};
+  const uint64_t dims[4] = {(uint64_t)F2_HD, (uint64_t)a.T, (uint64_t)a.H, (uint64_t)a.B};
+  {
+    const uint64_t s[3] = {(uint64_t)a.sq.t * 2, (uint64_t)a.sq.h * 2, (uint64_t)a.sq.b * 2};
+    if ((rc = encode_tmap_sw128(&tq, a.q, dtype, 4, dims, s, box))) return rc;
+  }
+  {
+    const uint64_t s[3] = {(uint64_t)a.sk.t * 2, (uint64_t)a.sk.h * 2, (uint64_t)a.sk.b * 2};
+    if ((rc = encode_tmap_sw128(&tk, a.k, dtype, 4, dims, s, box))) return rc;
+  }
+  {
+    const uint64_t s[3] = {(uint64_t)a.sv.t * 2, (uint64_t)a.sv.h * 2, (uint64_t)a.sv.b * 2};
+    if ((rc = encode_tmap_sw128(&tv, a.v, dtype, 4, dims, s, box))) return rc;
+  }
+  F2Params p;
+  p.out = a.out; p.lse = a.lse; p.so_b = a.so.b; p.so_h = a.so.h; p.so_t = a.so.t;
+  p.H = a.H; p.T = a.T; p.scale = a.scale; p.bias_mode = a.bias_mode; p.slopes = a.slopes;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd2_tc05_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         F2_SMEM_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_fwd2_tc05_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               F2_SMEM_BYTES);
+    if (e != cudaSuccess) return fail(TFB_ERR_LAUNCH, "attention_fwd(tcgen05): smem attribute: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
+  const int nq = a.T / F2_TILE;
+  dim3 grid((nq + 1) / 2, a.B * a.H);
+  if (a.bias_mode) attn_fwd2_tc05_kernel<T, true><<<grid, F2_THREADS, F2_SMEM_BYTES, st>>>(tq, tk, tv, p);
+  else attn_fwd2_tc05_kernel<T, false><<<grid, F2_THREADS, F2_SMEM_BYTES, st>>>(tq, tk, tv, p);
+  return launched("attention_fwd(tcgen05, two tiles)");
+}
+
+int attn_fwd2_tc05(const AttnArgs& a, int dtype, cudaStream_t st) {
+  TFB_DISPATCH_16(dtype, T, { return fwd2_launch<T>(a, dtype, st); })
+}
+
+}  // namespace tfb

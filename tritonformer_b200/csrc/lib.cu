@@ -18,6 +18,7 @@ bool gemm_tc05_eligible(const void*, const void*, const void*, const void*, int6
 int gemm_tc05_status(int reset);
 int attn_tc05_status(int reset);
 int attn_bwd_tc05_status(int reset);
+int attn_fwd2_tc05_status(int reset);
 }  // namespace tfb
 
 using namespace tfb;
@@ -31,7 +32,8 @@ extern "C" int tfb_device_status(int reset) {
   const int a = gemm_tc05_status(reset);
   const int b = attn_tc05_status(reset);
   const int c = attn_bwd_tc05_status(reset);
-  return a ? a : (b ? b : c);
+  const int d = attn_fwd2_tc05_status(reset);
+  return a ? a : (b ? b : (c ? c : d));
 }
 
 extern "C" void tfb_debug_set(int key, int value) {
