@@ -46,8 +46,12 @@ int64_t tfb_launch_count(void);
  * Synchronises the device; meant for tests and post-mortems.  reset != 0 clears it.      */
 int tfb_device_status(int reset);
 /* Test switches.  key 0: value 1 sends every GEMM to the generic-stride kernel.
- *                key 1: value 1 sends every attention call to the mma.sync kernels.      */
+ *                key 1: value 1 sends every attention call to the mma.sync kernels.
+ *                key 2: bit 0 skips the dQ accumulation, bit 1 turns the timing counters on. */
 void tfb_debug_set(int key, int value);
+/* Timing counters of the attention backward kernel (16 cycle sums, filled while tfb_debug_set(2, 2)
+ * is in effect); copies and clears them.  Synchronises the device.                        */
+int tfb_debug_counters(unsigned long long* out16);
 
 /* ------------------------------------------------------------------ LayerNorm
  * Replaces layernorm_fwd + layernorm_fwd_kernel (tritonformer/kernels/layernorm.py:9-87).

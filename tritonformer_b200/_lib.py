@@ -25,6 +25,7 @@ _SIGNATURES = {
     "tfb_launch_count": (_i64, []),
     "tfb_device_status": (_i32, [_i32]),
     "tfb_debug_set": (None, [_i32, _i32]),
+    "tfb_debug_counters": (_i32, [_c.POINTER(_c.c_uint64)]),
     "tfb_layernorm_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _f32, _i32, _vp]),
     "tfb_layernorm_bwd_partials": (_i64, [_i64, _i64]),
     "tfb_layernorm_bwd": (_i32, [_vp] * 9 + [_i64] * 6 + [_i32, _vp]),

@@ -14,8 +14,11 @@
 // shared memory once and serves two products.
 //
 // Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2-9 compute (thread = TMEM lane, two
-// warps per lane quarter, each taking half of the columns).
-// TMEM columns: [0,128) Sᵀ, then reused for dQ_i; [128,256) dPᵀ; [256,256+hd) dV; then dK.
+// warps per lane quarter, each taking half of the columns), warps 10-13 drain dQ_i.
+// At head_dim 64 the scores of tile i+1 are issued before the gradient products of tile i, so the
+// compute warps work on tile i+1 while the tensor core finishes tile i.
+// TMEM columns: [0,128) Sᵀ; [128,256) dPᵀ; [256,256+hd) dV; then dK; then dQ_i (at head_dim 128
+// dQ_i reuses the Sᵀ columns).
 #include "attn.cuh"
 #include "tc05.cuh"
 #include <type_traits>
@@ -26,7 +29,7 @@ extern std::atomic<int> g_attn_debug;
 
 constexpr float kLog2eB = 1.4426950408889634f;
 constexpr int FB_T = 128;           // tile edge (keys and queries)
-constexpr int FB_THREADS = 320;     // 10 warps
+constexpr int FB_THREADS = 448;     // 14 warps: TMA, MMA, 8 compute, 4 dQ drain
 constexpr int FB_COMPUTE = 256;     // threads in the compute warps
 
 template <int HD> struct FbCfg {
@@ -39,8 +42,8 @@ template <int HD> struct FbCfg {
   static constexpr int OFF_DO = OFF_Q + QSTAGES * TILE_BYTES;        // [QSTAGES]
   static constexpr int OFF_P = OFF_DO + QSTAGES * TILE_BYTES;        // Pᵀ  128 x 128 x 2 B
   static constexpr int OFF_DS = OFF_P + 32768;                       // dSᵀ 128 x 128 x 2 B
-  static constexpr int OFF_STAT = OFF_DS + 32768;                    // lse2[128], delta[128] fp32
-  static constexpr int OFF_BAR = OFF_STAT + 1024;
+  static constexpr int OFF_STAT = OFF_DS + 32768;                    // 2 x (lse2[128], delta[128]) fp32
+  static constexpr int OFF_BAR = OFF_STAT + 2048;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
   static constexpr int COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 256 + HD;
   // dQ_i has columns of its own when they fit (hd 64); otherwise it reuses the Sᵀ columns
@@ -67,10 +70,23 @@ __device__ __forceinline__ float alibi_term_b(int mode, float slope, int dist) {
   return __bfloat162float(__hmul(__float2bfloat16_rn(-(float)dist), __float2bfloat16_rn(slope)));
 }
 
+// Cycle counters for the timing switch (debug bit 1): [0] CTA iterations, [1..5] compute warp 2:
+// wait scores, math, wait previous products, smem write, barrier+stats; [6..9] MMA thread: wait P/dS,
+// wait Q/dO, wait dQ drain, total; [10,11] drain warp: wait, drain; [12] CTA lifetime.
+static __device__ unsigned long long g_prof[16];
+#define PROF_T(var) long long var = prof ? clock64() : 0
+#define PROF_ADD(idx, t0, t1) do { if (prof) atomicAdd(&g_prof[idx], (unsigned long long)((t1) - (t0))); } while (0)
+
 __device__ __forceinline__ float ex2_approx_b(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  typename Num<T>::T2 h = Num<T>::from_f2(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
 }
 
 __device__ __forceinline__ void compute_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
@@ -85,14 +101,13 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
   constexpr int QS = Cfg::QSTAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  float* s_lse2 = reinterpret_cast<float*>(smem + Cfg::OFF_STAT);
-  float* s_delta = s_lse2 + FB_T;
+  float* s_stat = reinterpret_cast<float*>(smem + Cfg::OFF_STAT);  // [2 parities][lse2[128], delta[128]]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
   uint64_t* kv_full = bars + 0;
   uint64_t* q_full = bars + 1;    // [2] Q_i and dO_i landed
   uint64_t* q_empty = bars + 3;   // [2] products reading them retired
   uint64_t* s_full = bars + 5;    // Sᵀ and dPᵀ in TMEM
-  uint64_t* pds_full = bars + 6;  // Pᵀ and dSᵀ in smem
+  uint64_t* pds_full = bars + 6;  // Pᵀ and dSᵀ in smem (and Sᵀ, dPᵀ consumed)
   uint64_t* dq_full = bars + 7;   // dV, dK, dQ_i products retired
   uint64_t* dq_free = bars + 8;   // dQ_i read out of TMEM
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 10);
@@ -114,7 +129,7 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
     mbar_init(s_full, 1);
     mbar_init(pds_full, 8);
     mbar_init(dq_full, 1);
-    mbar_init(dq_free, 8);
+    mbar_init(dq_free, 4);
     *abort_flag = (*(volatile int*)&g_dev_status != 0) ? 1 : 0;
     mbar_fence_init();
   }
@@ -163,13 +178,16 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
       constexpr uint32_t idesc_q = instr_desc_f16(128, HD, fmt, 1, 1);    // dQ      : both MN-major
       const uint32_t sk = smem_u32(smem + Cfg::OFF_K), sv = smem_u32(smem + Cfg::OFF_V);
       const uint32_t sp = smem_u32(smem + Cfg::OFF_P), sds = smem_u32(smem + Cfg::OFF_DS);
+      const bool prof = (p.debug & 2) != 0;
+      PROF_T(tm_start);
       bool ok = mbar_wait(kv_full, 0, 0x2200, abort_flag);
       // Sᵀ = K Q_iᵀ and dPᵀ = V dO_iᵀ of query tile `it`
       auto issue_scores = [&](int it) -> bool {
         const int st = it % QS;
+        PROF_T(a0);
         if (!mbar_wait(&q_full[st], (it / QS) & 1, 0x2300 | st, abort_flag)) return false;
-        // when dQ shares the Sᵀ columns, the previous dQ must have been drained first
-        if (Cfg::DQ_ALIASED && it > 0 && !mbar_wait(dq_free, (it - 1) & 1, 0x2400, abort_flag)) return false;
+        PROF_T(a1);
+        PROF_ADD(7, a0, a1);
         tc_fence_after();
         const uint32_t sq = smem_u32(smem + Cfg::OFF_Q + st * Cfg::TILE_BYTES);
         const uint32_t sdo = smem_u32(smem + Cfg::OFF_DO + st * Cfg::TILE_BYTES);
@@ -188,14 +206,16 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
         tc_commit(s_full);
         return true;
       };
-      if (ok) ok = issue_scores(0);
-      for (int it = 0; it < iters && ok; ++it) {
+      // dV += Pᵀ dO_i, dK += dSᵀ Q_i, dQ_i = dS K
+      auto issue_grads = [&](int it) -> bool {
         const int st = it % QS;
         const uint32_t sq = smem_u32(smem + Cfg::OFF_Q + st * Cfg::TILE_BYTES);
         const uint32_t sdo = smem_u32(smem + Cfg::OFF_DO + st * Cfg::TILE_BYTES);
-        if (!mbar_wait(pds_full, it & 1, 0x2500, abort_flag)) { ok = false; break; }
-        // dQ columns of their own: the previous dQ must have been drained before it is overwritten
-        if (!Cfg::DQ_ALIASED && it > 0 && !mbar_wait(dq_free, (it - 1) & 1, 0x2400, abort_flag)) { ok = false; break; }
+        // the dQ columns still hold the previous tile's dQ until the drain warps are done with it
+        PROF_T(a0);
+        if (it > 0 && !mbar_wait(dq_free, (it - 1) & 1, 0x2400, abort_flag)) return false;
+        PROF_T(a1);
+        PROF_ADD(8, a0, a1);
         tc_fence_after();
 #pragma unroll
         for (int s = 0; s < FB_T / 16; ++s) {  // contraction over the 128 queries of this tile
@@ -214,132 +234,190 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
         }
         tc_commit(&q_empty[st]);
         tc_commit(dq_full);
-        // the next tile's scores run on the tensor core while the compute warps drain dQ_i
-        if (it + 1 < iters) ok = issue_scores(it + 1);
+        return true;
+      };
+      if (ok) ok = issue_scores(0);
+      for (int it = 0; it < iters && ok; ++it) {
+        PROF_T(a0);
+        if (!mbar_wait(pds_full, it & 1, 0x2500, abort_flag)) { ok = false; break; }
+        PROF_T(a1);
+        PROF_ADD(6, a0, a1);
+        if (!Cfg::DQ_ALIASED) {
+          // Sᵀ/dPᵀ of this tile are consumed: the next tile's scores go first, so the compute warps
+          // can start on them while the three gradient products of this tile run
+          if (it + 1 < iters) ok = issue_scores(it + 1);
+          if (ok) ok = issue_grads(it);
+        } else {
+          // dQ_i reuses the Sᵀ columns: the next scores may only follow once dQ_i has been drained
+          ok = issue_grads(it);
+          if (ok && it + 1 < iters) {
+            ok = mbar_wait(dq_free, it & 1, 0x2450, abort_flag);
+            if (ok) ok = issue_scores(it + 1);
+          }
+        }
       }
+      PROF_T(tm_end);
+      PROF_ADD(9, tm_start, tm_end);
     }
-  } else if (!dead) {
+  } else if (warp < 10) {
     // -------------------------------------------------------------------------- compute
-    const int cw = warp - 2;           // 0..7
-    const int qd = warp & 3;           // TMEM lane quarter
-    const int half = cw >> 2;          // which half of the columns
-    const int r = qd * 32 + lane;      // TMEM lane: key row for Sᵀ/dPᵀ/dV/dK, query row for dQ
-    const int ct = threadIdx.x - 64;   // 0..255 within the compute group
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
-    const float c2 = p.scale * kLog2eB;
-    const float slope = p.bias_mode ? p.slopes[h] : 0.f;
-    const int j = j0 + r;              // this thread's key
-    uint8_t* sp = smem + Cfg::OFF_P;
-    uint8_t* sds = smem + Cfg::OFF_DS;
-    bool ok = true;
-    // Every compute thread runs every iteration up to the named barrier, also after a wait gave
-    // up (the remaining waits then return at once), so nobody is left alone at the barrier.
-    for (int it = 0; it < iters; ++it) {
-      const int i0 = (kt + it) * FB_T;
-      const bool diag = (it == 0);
-      // per-query statistics of this tile; safe to overwrite: every compute warp is past dq_full
-      if (ct < FB_T) s_lse2[ct] = p.lse[(int64_t)bh * p.T + i0 + ct] * kLog2eB;
-      else s_delta[ct - FB_T] = p.delta[(int64_t)bh * p.T + i0 + ct - FB_T];
-      compute_bar_sync();
-      if (ok) ok = mbar_wait(s_full, it & 1, 0x2600, abort_flag);
-      if (ok) {
-        tc_fence_after();
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          const int col0 = half * 64 + c * 32;  // first query column of this chunk
-          uint32_t sv_[32], dv_[32];
-          tmem_ld32(lane_addr + Cfg::COL_S + col0, sv_);
-          tmem_ld32(lane_addr + Cfg::COL_DP + col0, dv_);
-          tc_wait_ld();
-          float pf[32], df[32];
+    if (!dead) {
+      const int cw = warp - 2;           // 0..7
+      const int qd = warp & 3;           // TMEM lane quarter
+      const int half = cw >> 2;          // which half of the columns
+      const int r = qd * 32 + lane;      // TMEM lane = key row
+      const int ct = threadIdx.x - 64;   // 0..255 within the compute group
+      const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
+      const float c2 = p.scale * kLog2eB;
+      const float slope = BIAS ? p.slopes[h] : 0.f;
+      const int j = j0 + r;              // this thread's key
+      uint8_t* sp = smem + Cfg::OFF_P;
+      uint8_t* sds = smem + Cfg::OFF_DS;
+      bool ok = true;
+      const bool prof = (p.debug & 2) && threadIdx.x == 64;
+      // Every compute thread runs every iteration up to the named barrier, also after a wait gave
+      // up (the remaining waits then return at once), so nobody is left alone at the barrier.
+      for (int it = 0; it < iters; ++it) {
+        const int i0 = (kt + it) * FB_T;
+        const bool diag = (it == 0);
+        PROF_T(t0);
+        // per-query statistics of this tile, double buffered by iteration parity: a thread that is
+        // already here may share the CTA with one still computing the previous tile
+        float* s_lse2 = s_stat + (it & 1) * 256;
+        float* s_delta = s_lse2 + FB_T;
+        if (ct < FB_T) s_lse2[ct] = p.lse[(int64_t)bh * p.T + i0 + ct] * kLog2eB;
+        else s_delta[ct - FB_T] = p.delta[(int64_t)bh * p.T + i0 + ct - FB_T];
+        compute_bar_sync();
+        PROF_T(t1);
+        if (ok) ok = mbar_wait(s_full, it & 1, 0x2600, abort_flag);
+        PROF_T(t2);
+        PROF_ADD(5, t0, t1);
+        PROF_ADD(1, t1, t2);
+        if (prof) atomicAdd(&g_prof[0], 1ull);
+        uint32_t pk[32], dk_[32];  // this thread's 64 columns of Pᵀ and dSᵀ, packed 16-bit pairs
+        long long t3 = 0, t4 = 0;
+        if (ok) {
+          tc_fence_after();
 #pragma unroll
-          for (int e4 = 0; e4 < 8; ++e4) {
-            const float4 l4 = *reinterpret_cast<const float4*>(s_lse2 + col0 + e4 * 4);
-            const float4 d4 = *reinterpret_cast<const float4*>(s_delta + col0 + e4 * 4);
-            const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
-            const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+          for (int c = 0; c < 2; ++c) {
+            const int col0 = half * 64 + c * 32;  // first query column of this chunk
+            uint32_t sv_[32], dv_[32];
+            PROF_T(tl0);
+            tmem_ld32(lane_addr + Cfg::COL_S + col0, sv_);
+            tmem_ld32(lane_addr + Cfg::COL_DP + col0, dv_);
+            tc_wait_ld();
+            PROF_T(tl1);
+            PROF_ADD(14, tl0, tl1);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const int e = e4 * 4 + k;
-              float pe;
-              if (!BIAS && !diag) {
-                pe = ex2_approx_b(fmaf(__uint_as_float(sv_[e]), c2, -lv[k]));
-              } else {
-                const int i = i0 + col0 + e;
-                float x = fmaf(__uint_as_float(sv_[e]), c2, -lv[k]);
-                if (BIAS) x += alibi_term_b(p.bias_mode, slope, max(i - j, 0)) * kLog2eB;
-                pe = (j > i) ? 0.f : ex2_approx_b(x);
+            for (int e4 = 0; e4 < 8; ++e4) {
+              const float4 l4 = *reinterpret_cast<const float4*>(s_lse2 + col0 + e4 * 4);
+              const float4 d4 = *reinterpret_cast<const float4*>(s_delta + col0 + e4 * 4);
+              const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
+              const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+              float pe[4], de[4];
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const int e = e4 * 4 + k;
+                if (!BIAS && !diag) {
+                  pe[k] = ex2_approx_b(fmaf(__uint_as_float(sv_[e]), c2, -lv[k]));
+                } else {
+                  const int i = i0 + col0 + e;
+                  float x = fmaf(__uint_as_float(sv_[e]), c2, -lv[k]);
+                  if (BIAS) x += alibi_term_b(p.bias_mode, slope, max(i - j, 0)) * kLog2eB;
+                  pe[k] = (j > i) ? 0.f : ex2_approx_b(x);
+                }
+                de[k] = pe[k] * (__uint_as_float(dv_[e]) - dl[k]);
               }
-              pf[e] = pe;
-              df[e] = pe * (__uint_as_float(dv_[e]) - dl[k]);
+              pk[c * 16 + e4 * 2] = pack2<T>(pe[0], pe[1]);
+              pk[c * 16 + e4 * 2 + 1] = pack2<T>(pe[2], pe[3]);
+              dk_[c * 16 + e4 * 2] = pack2<T>(de[0], de[1]);
+              dk_[c * 16 + e4 * 2 + 1] = pack2<T>(de[2], de[3]);
             }
           }
+          // Pᵀ / dSᵀ of the previous tile are still being read by its gradient products
+          if (prof) t3 = clock64();
+          if (it > 0) ok = mbar_wait(dq_full, (it - 1) & 1, 0x2650, abort_flag);
+          if (prof) t4 = clock64();
+          PROF_ADD(2, t2, t3);
+          PROF_ADD(3, t3, t4);
+        }
+        if (ok) {
+#pragma unroll
+          for (int v4 = 0; v4 < 8; ++v4) {
+            const int cc = half * 8 + v4;  // 16-byte chunk index along the 128 queries
+            const uint32_t off = (cc >> 3) * 16384 + r * 128 + (((cc & 7) ^ (r & 7)) << 4);
+            *reinterpret_cast<uint4*>(sp + off) = make_uint4(pk[v4 * 4], pk[v4 * 4 + 1], pk[v4 * 4 + 2], pk[v4 * 4 + 3]);
+            *reinterpret_cast<uint4*>(sds + off) = make_uint4(dk_[v4 * 4], dk_[v4 * 4 + 1], dk_[v4 * 4 + 2], dk_[v4 * 4 + 3]);
+          }
+          PROF_T(t45);
+          tc_fence_before();
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(pds_full);
+          PROF_T(t5);
+          PROF_ADD(4, t4, t5);
+          PROF_ADD(13, t45, t5);
+        }
+      }
+      if (ok && mbar_wait(dq_full, (iters - 1) & 1, 0x2680, abort_flag)) {
+        // dV and dK are complete
+        tc_fence_after();
+        T* dvp = reinterpret_cast<T*>(p.dv) + b * p.sdv_b + h * p.sdv_h + (int64_t)j * p.sdv_t;
+        T* dkp = reinterpret_cast<T*>(p.dk) + b * p.sdk_b + h * p.sdk_h + (int64_t)j * p.sdk_t;
+#pragma unroll 1
+        for (int c = 0; c < HD / 64; ++c) {
+          const int col0 = half * (HD / 2) + c * 32;
+          uint32_t v[32], w[32];
+          tmem_ld32(lane_addr + Cfg::COL_DV + col0, v);
+          tmem_ld32(lane_addr + Cfg::COL_DK + col0, w);
+          tc_wait_ld();
 #pragma unroll
           for (int v4 = 0; v4 < 4; ++v4) {
             float g[8], d[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-              g[e] = pf[v4 * 8 + e];
-              d[e] = df[v4 * 8 + e];
+              g[e] = __uint_as_float(v[v4 * 8 + e]);
+              d[e] = __uint_as_float(w[v4 * 8 + e]) * p.scale;
             }
-            const int cc = (col0 >> 3) + v4;  // 16-byte chunk index along the 128 queries
-            const uint32_t off = (cc >> 3) * 16384 + r * 128 + (((cc & 7) ^ (r & 7)) << 4);
-            *reinterpret_cast<uint4*>(sp + off) = pack8<T>(g);
-            *reinterpret_cast<uint4*>(sds + off) = pack8<T>(d);
+            *reinterpret_cast<uint4*>(dvp + col0 + v4 * 8) = pack8<T>(g);
+            *reinterpret_cast<uint4*>(dkp + col0 + v4 * 8) = pack8<T>(d);
           }
         }
-        tc_fence_before();
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) mbar_arrive(pds_full);
       }
-      // dQ_i: lanes are now query rows
-      if (ok) ok = mbar_wait(dq_full, it & 1, 0x2700, abort_flag);
-      if (ok) {
-        tc_fence_after();
-        float* dq_row = p.dq_acc + ((int64_t)bh * p.T + i0 + r) * HD;
+    }
+  } else if (!dead) {
+    // ---------------------------------------------------------------------------- dQ drain
+    // warps 10-13: lanes are query rows here; each warp adds its 32 rows of dQ_i to the fp32 accumulator
+    const int qd = warp & 3;
+    const int r = qd * 32 + lane;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
+    const bool prof = (p.debug & 2) && warp == 10 && lane == 0;
+    for (int it = 0; it < iters; ++it) {
+      const int i0 = (kt + it) * FB_T;
+      PROF_T(a0);
+      if (!mbar_wait(dq_full, it & 1, 0x2700, abort_flag)) break;
+      PROF_T(a1);
+      PROF_ADD(10, a0, a1);
+      tc_fence_after();
+      float* dq_row = p.dq_acc + ((int64_t)bh * p.T + i0 + r) * HD;
 #pragma unroll 1
-        for (int c = 0; c < HD / 64; ++c) {
-          const int col0 = half * (HD / 2) + c * 32;
-          uint32_t v[32];
-          tmem_ld32(lane_addr + Cfg::COL_DQ + col0, v);
-          tc_wait_ld();
-          if (!(p.debug & 1))
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(lane_addr + Cfg::COL_DQ + c * 32, v);
+        tc_wait_ld();
+        if (!(p.debug & 1))
 #pragma unroll
           for (int e = 0; e < 32; e += 4)
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + col0 + e),
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + c * 32 + e),
                          "f"(__uint_as_float(v[e])), "f"(__uint_as_float(v[e + 1])),
                          "f"(__uint_as_float(v[e + 2])), "f"(__uint_as_float(v[e + 3]))
                          : "memory");
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(dq_free);
       }
-    }
-    if (ok) {
-      // dV and dK are complete once the last dq_full has been seen
-      T* dvp = reinterpret_cast<T*>(p.dv) + b * p.sdv_b + h * p.sdv_h + (int64_t)j * p.sdv_t;
-      T* dkp = reinterpret_cast<T*>(p.dk) + b * p.sdk_b + h * p.sdk_h + (int64_t)j * p.sdk_t;
-#pragma unroll 1
-      for (int c = 0; c < HD / 64; ++c) {
-        const int col0 = half * (HD / 2) + c * 32;
-        uint32_t v[32], w[32];
-        tmem_ld32(lane_addr + Cfg::COL_DV + col0, v);
-        tmem_ld32(lane_addr + Cfg::COL_DK + col0, w);
-        tc_wait_ld();
-#pragma unroll
-        for (int v4 = 0; v4 < 4; ++v4) {
-          float g[8], d[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            g[e] = __uint_as_float(v[v4 * 8 + e]);
-            d[e] = __uint_as_float(w[v4 * 8 + e]) * p.scale;
-          }
-          *reinterpret_cast<uint4*>(dvp + col0 + v4 * 8) = pack8<T>(g);
-          *reinterpret_cast<uint4*>(dkp + col0 + v4 * 8) = pack8<T>(d);
-        }
-      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_free);
+      PROF_T(a2);
+      PROF_ADD(11, a1, a2);
     }
   }
 
@@ -378,6 +456,15 @@ __global__ void __launch_bounds__(256) attn_dq_convert_kernel(const float* __res
 
 // ------------------------------------------------------------------------------- host side
 int attn_bwd_tc05_status(int reset) { return read_dev_status(reset); }
+
+// Copies the timing counters to `out` (16 values) and clears them.  Synchronises the device.
+int attn_bwd_tc05_counters(unsigned long long* out) {
+  cudaDeviceSynchronize();
+  if (cudaMemcpyFromSymbol(out, g_prof, sizeof(unsigned long long) * 16) != cudaSuccess) return -1;
+  unsigned long long z[16] = {0};
+  cudaMemcpyToSymbol(g_prof, z, sizeof(z));
+  return 0;
+}
 
 static int encode_bhtd(CUtensorMap* m, const void* ptr, const AttnStrides& s, int B, int H, int T, int hd, int dtype) {
   const uint64_t dims[4] = {(uint64_t)hd, (uint64_t)T, (uint64_t)H, (uint64_t)B};

@@ -19,6 +19,7 @@ int gemm_tc05_status(int reset);
 int attn_tc05_status(int reset);
 int attn_bwd_tc05_status(int reset);
 int attn_fwd2_tc05_status(int reset);
+int attn_bwd_tc05_counters(unsigned long long* out);
 }  // namespace tfb
 
 using namespace tfb;
@@ -35,6 +36,8 @@ extern "C" int tfb_device_status(int reset) {
   const int d = attn_fwd2_tc05_status(reset);
   return a ? a : (b ? b : (c ? c : d));
 }
+
+extern "C" int tfb_debug_counters(unsigned long long* out16) { return attn_bwd_tc05_counters(out16); }
 
 extern "C" void tfb_debug_set(int key, int value) {
   if (key == 0) g_force_generic_gemm.store(value);
