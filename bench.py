@@ -198,6 +198,7 @@ def run_b200_arm(args):
     broadcast_parameters(model)
     n_params = sum(p.numel() for p in model.parameters())
     buckets = GradBuckets(model.parameters())
+    tlinear.ACCUMULATE_INTO_GRAD = True  # weight-gradient GEMMs add into the bucket views themselves
     loss_scale = 4096.0 if dtype is torch.float16 else 1.0
 
     gen = torch.Generator().manual_seed(1234 + rank)

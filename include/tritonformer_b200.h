@@ -75,6 +75,15 @@ int tfb_layernorm_bwd(const void* dy, const void* x, const void* alpha,
                       int64_t rows, int64_t d, int64_t dy_ld, int64_t x_ld, int64_t dx_ld,
                       int dtype, void* stream);
 
+/* The same backward with the gradient of a residual branch folded in (no counterpart in the
+ * reference, where autograd adds the two with a separate kernel): dx = dLayerNorm(dy) + dres, for
+ * the pre-LN pattern h -> (LayerNorm(h), h).  dres may be NULL.                              */
+int tfb_layernorm_bwd_res(const void* dy, const void* x, const void* alpha,
+                          const float* mean, const float* rstd, const void* dres, void* dx,
+                          void* dalpha, void* dbeta, float* partials, int64_t n_partials,
+                          int64_t rows, int64_t d, int64_t dy_ld, int64_t x_ld, int64_t dres_ld,
+                          int64_t dx_ld, int dtype, void* stream);
+
 /* LayerNorm backward for callers that cannot supply scratch memory (no counterpart in the
  * reference, which allocates freely through torch): same results as tfb_layernorm_bwd, but the
  * fp32 partial sums live in a fixed array inside the library image (about 9.7 MB, held by every
@@ -142,6 +151,21 @@ int tfb_gemm(const void* a, const void* b, void* c, const void* bias,
              int64_t M, int64_t N, int64_t K,
              int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int64_t ldc,
              int relu, int accumulate, int dtype, void* stream, int* path);
+
+/* The same product with the epilogue fusions the model uses (no counterpart in the reference, which
+ * runs these as separate kernels: the residual add of transformer.py:245,250, mask_grad of
+ * kernels/activation.py:7-44, the gradient accumulation of autograd):
+ *   C[m,n] = mask( act( sum_k A(m,k) B(k,n) + bias[n] ) + addend[m,n] )
+ * addend (may be NULL; may be C itself to accumulate) has leading dimension ld_addend; mask (may be
+ * NULL) zeroes the result wherever mask[m,n] <= 0 (pass a saved ReLU output to get the ReLU
+ * gradient).  workspace (may be NULL) is fp32 scratch of at least M*N*4 bytes: when given and the
+ * output has too few tiles to fill the GPU, the contraction is split in two (deterministic).   */
+int tfb_gemm_fused(const void* a, const void* b, void* c, const void* bias,
+                   const void* addend, int64_t ld_addend, const void* mask, int64_t ld_mask,
+                   int64_t M, int64_t N, int64_t K,
+                   int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int64_t ldc,
+                   int relu, int dtype, void* workspace, int64_t workspace_bytes,
+                   void* stream, int* path);
 
 /* ------------------------------------------------------------------- Attention
  * Replaces flash_wrapper_fwd / flash_wrapper_fwd_attn_bias

@@ -65,13 +65,19 @@ def _step(cfg, dtype, batch, seq, loss_scale, oracle_device):
     oracle = oracle.to(oracle_device)
     gen = torch.Generator().manual_seed(99)
     ids = torch.randint(0, cfg.vocab_size, (batch, seq), generator=gen)
+    import tritonformer_b200.fused as fused
     masks = []
+    fused.CAPTURE_ACTIVATION_PATTERN = masks  # fused layers report their ReLU pattern here
     hooks = [layer.mlp.dense_h_to_4h.register_forward_hook(lambda m, i, o: masks.append((o > 0).detach()))
-             for layer in model.layer_list]
-    with torch.autocast("cuda", dtype=dtype):
-        logits, loss = model(ids.cuda(), ids.cuda())
-    for h in hooks:
-        h.remove()
+             for layer in model.layer_list]  # module-by-module layers report it through hooks
+    try:
+        with torch.autocast("cuda", dtype=dtype):
+            logits, loss = model(ids.cuda(), ids.cuda())
+    finally:
+        fused.CAPTURE_ACTIVATION_PATTERN = None
+        for h in hooks:
+            h.remove()
+    assert len(masks) == cfg.num_hidden_layers
     (loss * loss_scale).backward()
     ids_o = ids.to(oracle_device)
 
@@ -121,6 +127,53 @@ def test_small_model_fp16_no_bias():
     cfg = _cfg(vocab_size=1024, hidden_size=256, max_position_embeddings=256, num_attention_heads=4, head_dim=64,
                ffn_dim=1024, num_hidden_layers=3, use_linear_bias=False, attn_bias=False)
     _step(cfg, torch.float16, 2, 256, 4096.0, "cuda")
+
+
+@pytest.mark.parametrize("bias", [False, True])
+def test_small_model_module_by_module_layers(bias):
+    """The layer composed from the plain Functions, as the reference composes it (no fused blocks)."""
+    import tritonformer_b200.transformer as tr
+    cfg = _cfg(vocab_size=1024, hidden_size=256, max_position_embeddings=256, num_attention_heads=4, head_dim=64,
+               ffn_dim=1024, num_hidden_layers=2, use_linear_bias=bias, attn_bias=bias)
+    tr.USE_FUSED_BLOCKS = False
+    try:
+        _step(cfg, torch.float16, 2, 256, 4096.0, "cuda")
+    finally:
+        tr.USE_FUSED_BLOCKS = True
+
+
+def test_gradients_accumulated_into_existing_grad_buffers():
+    """With ACCUMULATE_INTO_GRAD the weight-gradient GEMMs add into .grad themselves: two steps give twice
+    the gradient of one, and .grad keeps its storage."""
+    import tritonformer_b200.linear as lin
+    from tritonformer_b200.dp import GradBuckets
+    from tritonformer_b200.transformer import Transformer
+    cfg = _cfg(vocab_size=1024, hidden_size=256, max_position_embeddings=128, num_attention_heads=4, head_dim=64,
+               ffn_dim=1024, num_hidden_layers=2, use_linear_bias=True, attn_bias=False)
+    torch.manual_seed(0)
+    model = Transformer(cfg, device="cuda")
+    with torch.no_grad():
+        model.logits_out.weight.normal_(0.0, 0.02)
+    ids = torch.randint(0, 1024, (2, 128), device="cuda")
+
+    def step():
+        with torch.autocast("cuda", dtype=torch.float16):
+            _, loss = model(ids, ids)
+        (loss * 1024.0).backward()
+
+    step()
+    once = {n: p.grad.detach().float().clone() for n, p in model.named_parameters()}
+    model.zero_grad(set_to_none=True)
+    buckets = GradBuckets(model.parameters())
+    lin.ACCUMULATE_INTO_GRAD = True
+    try:
+        step()
+        step()
+    finally:
+        lin.ACCUMULATE_INTO_GRAD = False
+    buckets.check_views()
+    for n, p in model.named_parameters():
+        assert norm_rel(p.grad.float(), 2.0 * once[n]) < 2e-3, n
 
 
 def test_small_model_fp16_bias_alibi_hd32():

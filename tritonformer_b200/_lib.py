@@ -29,6 +29,7 @@ _SIGNATURES = {
     "tfb_layernorm_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _f32, _i32, _vp]),
     "tfb_layernorm_bwd_partials": (_i64, [_i64, _i64]),
     "tfb_layernorm_bwd": (_i32, [_vp] * 9 + [_i64] * 6 + [_i32, _vp]),
+    "tfb_layernorm_bwd_res": (_i32, [_vp] * 10 + [_i64] * 7 + [_i32, _vp]),
     "tfb_layernorm_bwd_static": (_i32, [_vp] * 8 + [_i64] * 5 + [_i32, _vp]),
     "tfb_softmax_fwd": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp]),
     "tfb_softmax_bwd": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
@@ -38,6 +39,7 @@ _SIGNATURES = {
     "tfb_colsum_partials": (_i64, [_i64, _i64]),
     "tfb_colsum": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp]),
     "tfb_gemm": (_i32, [_vp, _vp, _vp, _vp] + [_i64] * 8 + [_i32, _i32, _i32, _vp, _pi32]),
+    "tfb_gemm_fused": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64] + [_i64] * 8 + [_i32, _i32, _vp, _i64, _vp, _pi32]),
     "tfb_attention_fwd": (_i32, [_vp] * 5 + [_i64] * 4 + [_pi64] * 4 + [_vp, _i32, _vp, _i64, _i64, _i32, _vp, _pi32]),
     "tfb_attention_bwd_scratch_bytes": (_i64, [_i64] * 4),
     "tfb_attention_bwd": (_i32, [_vp] * 9 + [_i64] * 4 + [_pi64] * 8 + [_vp, _i32, _vp, _i64, _i64, _vp, _i64, _i32, _vp, _pi32]),

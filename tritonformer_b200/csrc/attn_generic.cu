@@ -9,6 +9,7 @@
 // key/value tile for dK, dV and one CTA per query tile for dQ; delta = rowsum(dO*O) comes
 // from a small pre-pass.
 #include "attn.cuh"
+#include <type_traits>
 
 namespace tfb {
 
@@ -220,26 +221,31 @@ __global__ void __launch_bounds__(AT_THREADS) attn_fwd_kernel(const AttnArgs a) 
   }
 }
 
-// delta[b,h,i] = sum_d dO[i,d] * O[i,d]; one warp per row
-template <typename T>
-__global__ void __launch_bounds__(128) attn_delta_kernel(const AttnArgs a, int hd) {
+// delta[b,h,i] = sum_d dO[i,d] * O[i,d]; hd/8 lanes per row, one 16-byte load of each operand per lane
+template <typename T, int HD>
+__global__ void __launch_bounds__(256) attn_delta_kernel(const AttnArgs a) {
+  constexpr int LPR = HD / 8;          // lanes per row
+  constexpr int RPW = 32 / LPR;        // rows per warp
   const int lane = threadIdx.x & 31;
-  const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int sub = lane % LPR;
+  const int64_t row = ((int64_t)blockIdx.x * 8 + (threadIdx.x >> 5)) * RPW + lane / LPR;
   const int64_t total = (int64_t)a.B * a.H * a.T;
-  if (row >= total) return;
-  const int i = (int)(row % a.T);
-  const int64_t bh = row / a.T;
-  const int b = (int)(bh / a.H), h = (int)(bh % a.H);
-  const T* op = (const T*)a.o + b * a.so.b + h * a.so.h + (int64_t)i * a.so.t;
-  const T* gp = (const T*)a.d_o + b * a.sdo.b + h * a.sdo.h + (int64_t)i * a.sdo.t;
   float s = 0.f;
-  for (int c = lane * 2; c < hd; c += 64) {
-    const float2 x = Num<T>::to_f2(*reinterpret_cast<const typename Num<T>::T2*>(op + c));
-    const float2 y = Num<T>::to_f2(*reinterpret_cast<const typename Num<T>::T2*>(gp + c));
-    s += x.x * y.x + x.y * y.y;
+  if (row < total) {
+    const int i = (int)(row % a.T);
+    const int64_t bh = row / a.T;
+    const int b = (int)(bh / a.H), h = (int)(bh % a.H);
+    const T* op = (const T*)a.o + b * a.so.b + h * a.so.h + (int64_t)i * a.so.t + sub * 8;
+    const T* gp = (const T*)a.d_o + b * a.sdo.b + h * a.sdo.h + (int64_t)i * a.sdo.t + sub * 8;
+    float x[8], y[8];
+    unpack8<T>(ld_stream16(op), x);
+    unpack8<T>(ld_stream16(gp), y);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += x[j] * y[j];
   }
-  s = warp_sum(s);
-  if (lane == 0) a.delta[row] = s;
+#pragma unroll
+  for (int o = LPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (row < total && sub == 0) a.delta[row] = s;
 }
 
 // --------------------------------------------------------------------------- backward: dK, dV
@@ -506,9 +512,7 @@ static int fwd_launch(const AttnArgs& a, cudaStream_t st) {
 
 template <typename T, int HD>
 static int bwd_launch(const AttnArgs& a, cudaStream_t st) {
-  const int64_t rows = (int64_t)a.B * a.H * a.T;
-  attn_delta_kernel<T><<<(unsigned)ceil_div(rows, 4), 128, 0, st>>>(a, HD);
-  int rc = launched("attention_delta");
+  int rc = attn_delta(a, HD, sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? TFB_BF16 : TFB_F16, st);
   if (rc) return rc;
   dim3 grid(a.T / AT, a.B * a.H);
   {
@@ -540,7 +544,11 @@ static int bwd_launch(const AttnArgs& a, cudaStream_t st) {
 
 int attn_delta(const AttnArgs& a, int hd, int dtype, cudaStream_t st) {
   const int64_t rows = (int64_t)a.B * a.H * a.T;
-  TFB_DISPATCH_16(dtype, T, { attn_delta_kernel<T><<<(unsigned)ceil_div(rows, 4), 128, 0, st>>>(a, hd); })
+  TFB_DISPATCH_16(dtype, T, {
+    if (hd == 32) attn_delta_kernel<T, 32><<<(unsigned)ceil_div(rows, 8 * 8), 256, 0, st>>>(a);
+    else if (hd == 64) attn_delta_kernel<T, 64><<<(unsigned)ceil_div(rows, 8 * 4), 256, 0, st>>>(a);
+    else attn_delta_kernel<T, 128><<<(unsigned)ceil_div(rows, 8 * 2), 256, 0, st>>>(a);
+  })
   return launched("attention_delta");
 }
 

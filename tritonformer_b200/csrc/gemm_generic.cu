@@ -30,9 +30,9 @@ constexpr int GB_PER_THREAD = GB_M * GB_K / GB_THREADS;  // 16 elements of A and
 
 template <typename T>
 __global__ void __launch_bounds__(GB_THREADS) gemm_generic_kernel(
-    const T* __restrict__ A, const T* __restrict__ Bm, T* __restrict__ C, const T* __restrict__ bias,
-    int M, int N, int K, int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int64_t ldc,
-    int relu, int accumulate) {
+    const T* __restrict__ A, const T* __restrict__ Bm, T* C, const T* __restrict__ bias, const T* addend,
+    int64_t ld_addend, const T* mask, int64_t ld_mask, int M, int N, int K, int64_t a_sm, int64_t a_sk,
+    int64_t b_sk, int64_t b_sn, int64_t ldc, int relu) {
   __shared__ __align__(16) T As[GB_M][GB_K + GB_PAD];
   __shared__ __align__(16) T Bs[GB_N][GB_K + GB_PAD];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -120,24 +120,24 @@ __global__ void __launch_bounds__(GB_THREADS) gemm_generic_kernel(
           float v = acc[i][j][e];
           if (bias) v += Num<T>::to_f(bias[n]);
           if (relu) v = fmaxf(v, 0.f);
-          T* dst = C + (int64_t)m * ldc + n;
-          if (accumulate) v += Num<T>::to_f(*dst);
-          *dst = Num<T>::from_f(v);
+          if (addend) v += Num<T>::to_f(addend[(int64_t)m * ld_addend + n]);
+          if (mask && !(Num<T>::to_f(mask[(int64_t)m * ld_mask + n]) > 0.f)) v = 0.f;
+          C[(int64_t)m * ldc + n] = Num<T>::from_f(v);
         }
       }
     }
   }
 }
 
-int gemm_generic(const void* a, const void* b, void* c, const void* bias, int64_t M, int64_t N,
-                 int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int64_t ldc,
-                 int relu, int accumulate, int dtype, cudaStream_t st) {
+int gemm_generic(const void* a, const void* b, void* c, const void* bias, const void* addend, int64_t ld_addend,
+                 const void* mask, int64_t ld_mask, int64_t M, int64_t N, int64_t K, int64_t a_sm, int64_t a_sk,
+                 int64_t b_sk, int64_t b_sn, int64_t ldc, int relu, int dtype, cudaStream_t st) {
   dim3 grid((unsigned)ceil_div(N, GB_N), (unsigned)ceil_div(M, GB_M));
   if (grid.y > 65535) return fail(TFB_ERR_UNSUPPORTED, "gemm(generic): M=%lld too large", (long long)M);
   TFB_DISPATCH_16(dtype, T, {
     gemm_generic_kernel<T><<<grid, GB_THREADS, 0, st>>>((const T*)a, (const T*)b, (T*)c, (const T*)bias,
-                                                        (int)M, (int)N, (int)K, a_sm, a_sk, b_sk, b_sn,
-                                                        ldc, relu, accumulate);
+                                                        (const T*)addend, ld_addend, (const T*)mask, ld_mask,
+                                                        (int)M, (int)N, (int)K, a_sm, a_sk, b_sk, b_sn, ldc, relu);
   })
   return launched("gemm_generic");
 }

@@ -33,10 +33,13 @@ template <int BN> struct GemmCfg {
 struct GemmParams {
   void* C;
   const void* bias;
+  const void* addend;  // added after bias/ReLU (the residual stream, or C itself to accumulate); may be null
+  const void* mask;    // result is zeroed where mask <= 0 (a saved ReLU output); may be null
+  float* ws;           // split-K: fp32 (M, N) partial sums, zero on entry; null when splits == 1
   int M, N, K;
-  int64_t ldc;
-  int relu, accumulate;
-  int tiles_m, tiles_n;
+  int64_t ldc, ld_addend, ld_mask;
+  int relu;
+  int tiles_m, tiles_n, splits;
 };
 
 template <typename T, int BN, bool A_MN, bool B_MN>
@@ -79,8 +82,10 @@ __global__ void __launch_bounds__(TB_THREADS, 1) gemm_tc05_kernel(const __grid_c
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  const int num_tiles = *abort_flag ? 0 : p.tiles_m * p.tiles_n;
-  const int kblocks = (p.K + TB_K - 1) / TB_K;
+  // work unit = (output tile, K split); the splits of a tile are adjacent so they run concurrently
+  const int num_tiles = *abort_flag ? 0 : p.tiles_m * p.tiles_n * p.splits;
+  const int kblocks_all = (p.K + TB_K - 1) / TB_K;
+  const int kb_per_split = (kblocks_all + p.splits - 1) / p.splits;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -90,10 +95,13 @@ __global__ void __launch_bounds__(TB_THREADS, 1) gemm_tc05_kernel(const __grid_c
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int unit = blockIdx.x; unit < num_tiles && ok; unit += gridDim.x) {
+        const int tile = unit / p.splits, split = unit % p.splits;
         const int m0 = (tile % p.tiles_m) * TB_M;
         const int n0 = (tile / p.tiles_m) * BN;
-        for (int kb = 0; kb < kblocks; ++kb) {
+        const int kb0 = split * kb_per_split;
+        const int kb1 = min(kb0 + kb_per_split, kblocks_all);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, 0x100 | stage, abort_flag)) { ok = false; break; }
           uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
           uint8_t* sb = sa + Cfg::A_BYTES;
@@ -125,11 +133,14 @@ __global__ void __launch_bounds__(TB_THREADS, 1) gemm_tc05_kernel(const __grid_c
       int buf = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int unit = blockIdx.x; unit < num_tiles && ok; unit += gridDim.x) {
+        const int split = unit % p.splits;
+        const int kb0 = split * kb_per_split;
+        const int kb1 = min(kb0 + kb_per_split, kblocks_all);
         if (!mbar_wait(&acc_empty[buf], acc_phase ^ 1, 0x300 | buf, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < kblocks; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full[stage], phase, 0x200 | stage, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
@@ -141,7 +152,7 @@ __global__ void __launch_bounds__(TB_THREADS, 1) gemm_tc05_kernel(const __grid_c
                                      : smem_desc_sw128(sa + k * 32, 16, 1024);
             const uint64_t bd = B_MN ? smem_desc_sw128(sb + k * 2048, 8192, 1024)
                                      : smem_desc_sw128(sb + k * 32, 16, 1024);
-            tc_mma_ss(d_tmem, ad, bd, idesc, (kb | k) ? 1u : 0u);
+            tc_mma_ss(d_tmem, ad, bd, idesc, ((kb - kb0) | k) ? 1u : 0u);
           }
           tc_commit(&empty[stage]);  // slot reusable once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -157,23 +168,58 @@ __global__ void __launch_bounds__(TB_THREADS, 1) gemm_tc05_kernel(const __grid_c
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     T* C = reinterpret_cast<T*>(p.C);
     const T* bias = reinterpret_cast<const T*>(p.bias);
+    const T* addend = reinterpret_cast<const T*>(p.addend);
+    const T* mask = reinterpret_cast<const T*>(p.mask);
     int buf = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    for (int unit = blockIdx.x; unit < num_tiles && ok; unit += gridDim.x) {
+      const int tile = unit / p.splits;
       const int m0 = (tile % p.tiles_m) * TB_M;
       const int n0 = (tile / p.tiles_m) * BN;
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const bool fused_in = (addend != nullptr || mask != nullptr) && p.splits == 1;
+      // addend / mask vectors of a 32-column chunk are fetched one chunk ahead (the first chunk while
+      // the tile's main loop is still running), so their latency is off the epilogue's critical path
+      uint4 addv[2][4], mskv[2][4];
+      auto prefetch = [&](int c, int slot) {
+        if (!fused_in || !row_ok) return;
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const int col = n0 + c * 32 + v * 8;
+          if (col + 8 <= p.N) {
+            if (addend) addv[slot][v] = *reinterpret_cast<const uint4*>(addend + (int64_t)row * p.ld_addend + col);
+            if (mask) mskv[slot][v] = *reinterpret_cast<const uint4*>(mask + (int64_t)row * p.ld_mask + col);
+          }
+        }
+      };
+      prefetch(0, 0);
       if (!mbar_wait(&acc_full[buf], acc_phase, 0x400 | buf, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      const int row = m0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
-#pragma unroll 1
+#pragma unroll
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
         tmem_ld32(taddr + c * 32, r);
+        if (c + 1 < BN / 32) prefetch(c + 1, (c + 1) & 1);
         tc_wait_ld();
         const int col0 = n0 + c * 32;
-        if (row < p.M && col0 < p.N) {
+        if (row_ok && col0 < p.N) {
+          if (p.splits > 1) {
+            // partial sum of this K range: fp32 adds into the workspace; the finishing kernel applies
+            // bias / ReLU / addend / mask and rounds once (N % 8 == 0 on this path)
+            float* w = p.ws + (int64_t)row * p.N + col0;
+#pragma unroll
+            for (int e = 0; e < 32; e += 4) {
+              if (col0 + e < p.N)
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(w + e), "f"(__uint_as_float(r[e])),
+                             "f"(__uint_as_float(r[e + 1])), "f"(__uint_as_float(r[e + 2])),
+                             "f"(__uint_as_float(r[e + 3]))
+                             : "memory");
+            }
+            continue;
+          }
           T* dst = C + (int64_t)row * p.ldc + col0;
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
@@ -193,11 +239,17 @@ __global__ void __launch_bounds__(TB_THREADS, 1) gemm_tc05_kernel(const __grid_c
 #pragma unroll
                 for (int j = 0; j < 8; ++j) f[j] = fmaxf(f[j], 0.f);
               }
-              if (p.accumulate) {
+              if (addend) {
                 float o[8];
-                unpack8<T>(*reinterpret_cast<const uint4*>(dst + v * 8), o);
+                unpack8<T>(addv[c & 1][v], o);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) f[j] += o[j];
+              }
+              if (mask) {
+                float o[8];
+                unpack8<T>(mskv[c & 1][v], o);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = o[j] > 0.f ? f[j] : 0.f;
               }
               *reinterpret_cast<uint4*>(dst + v * 8) = pack8<T>(f);
             } else {
@@ -205,7 +257,8 @@ __global__ void __launch_bounds__(TB_THREADS, 1) gemm_tc05_kernel(const __grid_c
                 float x = f[j];
                 if (bias) x += Num<T>::to_f(bias[col + j]);
                 if (p.relu) x = fmaxf(x, 0.f);
-                if (p.accumulate) x += Num<T>::to_f(dst[v * 8 + j]);
+                if (addend) x += Num<T>::to_f(addend[(int64_t)row * p.ld_addend + col + j]);
+                if (mask && !(Num<T>::to_f(mask[(int64_t)row * p.ld_mask + col + j]) > 0.f)) x = 0.f;
                 dst[v * 8 + j] = Num<T>::from_f(x);
               }
             }
@@ -232,6 +285,48 @@ __global__ void __launch_bounds__(TB_THREADS, 1) gemm_tc05_kernel(const __grid_c
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// Split-K epilogue: C = mask(act(ws + bias) + addend), rounded once; 8 columns per thread.
+template <typename T>
+__global__ void __launch_bounds__(256) splitk_finish_kernel(const GemmParams p) {
+  const int vpr = p.N / 8;
+  const int64_t total = (int64_t)p.M * vpr;
+  T* C = reinterpret_cast<T*>(p.C);
+  const T* bias = reinterpret_cast<const T*>(p.bias);
+  const T* addend = reinterpret_cast<const T*>(p.addend);
+  const T* mask = reinterpret_cast<const T*>(p.mask);
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = idx / vpr;
+    const int col = (int)(idx % vpr) * 8;
+    const float4 x = *reinterpret_cast<const float4*>(p.ws + row * p.N + col);
+    const float4 y = *reinterpret_cast<const float4*>(p.ws + row * p.N + col + 4);
+    float f[8] = {x.x, x.y, x.z, x.w, y.x, y.y, y.z, y.w};
+    if (bias) {
+      float b[8];
+      unpack8<T>(__ldg(reinterpret_cast<const uint4*>(bias + col)), b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] += b[j];
+    }
+    if (p.relu) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = fmaxf(f[j], 0.f);
+    }
+    if (addend) {
+      float o[8];
+      unpack8<T>(*reinterpret_cast<const uint4*>(addend + row * p.ld_addend + col), o);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] += o[j];
+    }
+    if (mask) {
+      float o[8];
+      unpack8<T>(*reinterpret_cast<const uint4*>(mask + row * p.ld_mask + col), o);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = o[j] > 0.f ? f[j] : 0.f;
+    }
+    *reinterpret_cast<uint4*>(C + row * p.ldc + col) = pack8<T>(f);
   }
 }
 
@@ -293,10 +388,19 @@ static int launch_tc05(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
     if (e != cudaSuccess) return fail(TFB_ERR_LAUNCH, "gemm_tc05: smem attribute: %s", cudaGetErrorString(e));
     attr_set = true;
   }
-  const int tiles = p.tiles_m * p.tiles_n;
-  const int grid = tiles < sm_count() ? tiles : sm_count();
+  const int units = p.tiles_m * p.tiles_n * p.splits;
+  const int grid = units < sm_count() ? units : sm_count();
+  if (p.splits > 1) {
+    cudaError_t e = cudaMemsetAsync(p.ws, 0, (size_t)p.M * p.N * sizeof(float), st);
+    if (e != cudaSuccess) return fail(TFB_ERR_LAUNCH, "gemm_tc05: workspace memset: %s", cudaGetErrorString(e));
+  }
   kern<<<grid, TB_THREADS, Cfg::SMEM_BYTES, st>>>(tmA, tmB, p);
-  return launched("gemm_tc05");
+  int rc = launched("gemm_tc05");
+  if (rc || p.splits == 1) return rc;
+  const int64_t total = (int64_t)p.M * (p.N / 8);
+  const unsigned blocks = (unsigned)(ceil_div(total, 256) < 148 * 8 ? ceil_div(total, 256) : 148 * 8);
+  splitk_finish_kernel<T><<<blocks, 256, 0, st>>>(p);
+  return launched("gemm_splitk_finish");
 }
 
 template <typename T, int BN>
@@ -311,8 +415,11 @@ static int dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& tmA, const CU
 // Whether (ptr, strides) can be described by a TMA tensor map of 16-bit elements.
 static bool tma_ok(const void* ptr, int64_t s_outer) { return aligned16(ptr) && s_outer % 8 == 0 && s_outer > 0; }
 
-bool gemm_tc05_eligible(const void* a, const void* b, const void* c, const void* bias, int64_t M, int64_t N,
-                        int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int64_t ldc) {
+bool gemm_tc05_eligible(const void* a, const void* b, const void* c, const void* bias, const void* addend,
+                        int64_t ld_addend, const void* mask, int64_t ld_mask, int64_t M, int64_t N, int64_t K,
+                        int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int64_t ldc) {
+  if (addend && !(aligned16(addend) && ld_addend % 8 == 0)) return false;
+  if (mask && !(aligned16(mask) && ld_mask % 8 == 0)) return false;
   if (M < 1 || N < 1 || K < 1) return false;
   if (M >= (1LL << 31) || N >= (1LL << 31) || K >= (1LL << 31)) return false;
   const bool a_ok = (a_sk == 1) ? tma_ok(a, a_sm) : (a_sm == 1 && tma_ok(a, a_sk));
@@ -321,9 +428,10 @@ bool gemm_tc05_eligible(const void* a, const void* b, const void* c, const void*
   return a_ok && b_ok && aligned16(c) && ldc % 8 == 0 && (bias == nullptr || aligned16(bias));
 }
 
-int gemm_tc05(const void* a, const void* b, void* c, const void* bias, int64_t M, int64_t N, int64_t K,
-              int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int64_t ldc, int relu, int accumulate,
-              int dtype, cudaStream_t st) {
+int gemm_tc05(const void* a, const void* b, void* c, const void* bias, const void* addend, int64_t ld_addend,
+              const void* mask, int64_t ld_mask, int64_t M, int64_t N, int64_t K, int64_t a_sm, int64_t a_sk,
+              int64_t b_sk, int64_t b_sn, int64_t ldc, int relu, int dtype, void* workspace,
+              int64_t workspace_bytes, cudaStream_t st) {
   const bool a_mn = (a_sk != 1);  // M contiguous
   const bool b_mn = (b_sk != 1);  // N contiguous
   // tile width: fewest "waves x tile cost" over the SMs
@@ -331,7 +439,16 @@ int gemm_tc05(const void* a, const void* b, void* c, const void* bias, int64_t M
   const int sms = sm_count();
   const int64_t cost256 = ceil_div(tm * ceil_div(N, 256), sms) * 256;
   const int64_t cost128 = ceil_div(tm * ceil_div(N, 128), sms) * 128;
-  const int BN = (N <= 128 || cost128 < cost256) ? 128 : 256;
+  // the wide tile moves fewer operand bytes per flop: the narrow one has to win by a clear margin
+  const int BN = (N <= 128 || cost128 * 10 < cost256 * 9) ? 128 : 256;
+  // Split the contraction in two when the output has too few tiles to occupy the machine (weight
+  // gradients: small M x N, contraction over every token).  Two fp32 partials added to a zeroed
+  // workspace give the same bits in either order, so the result stays deterministic.
+  const int64_t tiles = tm * ceil_div(N, BN);
+  int splits = 1;
+  if (workspace && tiles * 10 <= sms * 6 && K >= 2048 && N % 8 == 0 &&
+      workspace_bytes >= (int64_t)M * N * (int64_t)sizeof(float) && aligned16(workspace))
+    splits = 2;
 
   CUtensorMap tmA, tmB;
   int rc;
@@ -346,9 +463,10 @@ int gemm_tc05(const void* a, const void* b, void* c, const void* bias, int64_t M
     if ((rc = encode_tmap_sw128(&tmB, b, dtype, 2, dims, str, box))) return rc;
   }
   GemmParams p;
-  p.C = c; p.bias = bias; p.M = (int)M; p.N = (int)N; p.K = (int)K; p.ldc = ldc;
-  p.relu = relu; p.accumulate = accumulate;
-  p.tiles_m = (int)tm; p.tiles_n = (int)ceil_div(N, BN);
+  p.C = c; p.bias = bias; p.addend = addend; p.mask = mask; p.ws = splits > 1 ? (float*)workspace : nullptr;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K; p.ldc = ldc; p.ld_addend = ld_addend; p.ld_mask = ld_mask;
+  p.relu = relu;
+  p.tiles_m = (int)tm; p.tiles_n = (int)ceil_div(N, BN); p.splits = splits;
   TFB_DISPATCH_16(dtype, T, {
     if (BN == 256) return dispatch_major<T, 256>(a_mn, b_mn, tmA, tmB, p, st);
     return dispatch_major<T, 128>(a_mn, b_mn, tmA, tmB, p, st);

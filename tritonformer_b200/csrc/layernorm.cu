@@ -102,7 +102,7 @@ __global__ void __launch_bounds__(MAXT) ln_bwd_kernel(
     const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ alpha,
     const float* __restrict__ mean, const float* __restrict__ rstd, T* __restrict__ dx,
     float* __restrict__ partials, int64_t rows, int d, int64_t dy_ld, int64_t x_ld,
-    int64_t dx_ld) {
+    int64_t dx_ld, const T* __restrict__ dres, int64_t dres_ld) {
   __shared__ float red[2][32][2 * LN_RB];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nwarp = blockDim.x >> 5;
@@ -119,7 +119,30 @@ __global__ void __launch_bounds__(MAXT) ln_bwd_kernel(
 
   const float inv_d = 1.f / (float)d;
   int buf = 0;
-  for (int64_t r0 = (int64_t)blockIdx.x * LN_RB; r0 < rows; r0 += (int64_t)gridDim.x * LN_RB) {
+  const int64_t stride = (int64_t)gridDim.x * LN_RB;
+  // raw 16-byte vectors of the row group being processed and of the next one (loads for the next
+  // group are in flight while this one goes through its reduction, barrier and stores)
+  uint4 cx[LN_RB], cg[LN_RB], nx[LN_RB], ng[LN_RB];
+  auto fetch = [&](int64_t r0, uint4 (&vx)[LN_RB], uint4 (&vg)[LN_RB]) {
+    if (!VEC) return;
+#pragma unroll
+    for (int r = 0; r < LN_RB; ++r) {
+      const int64_t row = r0 + r;
+      if (row < rows && active) {
+        vx[r] = ld_stream16(x + row * x_ld + c0);
+        vg[r] = ld_stream16(dy + row * dy_ld + c0);
+      }
+    }
+  };
+  fetch((int64_t)blockIdx.x * LN_RB, cx, cg);
+  for (int64_t r0 = (int64_t)blockIdx.x * LN_RB; r0 < rows; r0 += stride) {
+    if (r0 + stride < rows) fetch(r0 + stride, nx, ng);
+    uint4 rv[LN_RB];  // residual-branch gradient, needed only after the reduction
+    if (VEC && dres) {
+#pragma unroll
+      for (int r = 0; r < LN_RB; ++r)
+        if (r0 + r < rows && active) rv[r] = ld_stream16(dres + (r0 + r) * dres_ld + c0);
+    }
     float xh[LN_RB][8], g[LN_RB][8];
     float s[2 * LN_RB];
 #pragma unroll
@@ -131,8 +154,8 @@ __global__ void __launch_bounds__(MAXT) ln_bwd_kernel(
       if (row < rows && active) {
         float xv[8], dv[8];
         if (VEC) {
-          unpack8<T>(ld_stream16(x + row * x_ld + c0), xv);
-          unpack8<T>(ld_stream16(dy + row * dy_ld + c0), dv);
+          unpack8<T>(cx[r], xv);
+          unpack8<T>(cg[r], dv);
         } else {
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
@@ -176,13 +199,26 @@ __global__ void __launch_bounds__(MAXT) ln_bwd_kernel(
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = rs * (g[r][j] - xh[r][j] * s[2 * r] - s[2 * r + 1]);
         if (VEC) {
+          if (dres) {  // gradient arriving through the residual branch that forked at this LayerNorm's input
+            float e[8];
+            unpack8<T>(rv[r], e);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] += e[j];
+          }
           st_stream16(dx + row * dx_ld + c0, pack8<T>(o));
         } else {
 #pragma unroll
           for (int j = 0; j < 8; ++j)
-            if (j < ncol) dx[row * dx_ld + c0 + j] = Num<T>::from_f(o[j]);
+            if (j < ncol)
+              dx[row * dx_ld + c0 + j] =
+                  Num<T>::from_f(o[j] + (dres ? Num<T>::to_f(dres[row * dres_ld + c0 + j]) : 0.f));
         }
       }
+    }
+#pragma unroll
+    for (int r = 0; r < LN_RB; ++r) {
+      cx[r] = nx[r];
+      cg[r] = ng[r];
     }
   }
   if (active) {
@@ -234,11 +270,12 @@ template <typename T>
 static int ln_bwd_launch(const void* dy, const void* x, const void* alpha, const float* mean,
                          const float* rstd, void* dx, void* dalpha, void* dbeta, float* partials,
                          int64_t n_partials, int64_t rows, int d, int64_t dy_ld, int64_t x_ld,
-                         int64_t dx_ld, bool vec, int threads, cudaStream_t st) {
+                         int64_t dx_ld, bool vec, int threads, cudaStream_t st, const void* dres = nullptr,
+                         int64_t dres_ld = 0) {
 #define TFB_LN_BWD(V, MT)                                                                     \
   ln_bwd_kernel<T, V, MT><<<(unsigned)n_partials, threads, 0, st>>>(                          \
       (const T*)dy, (const T*)x, (const T*)alpha, mean, rstd, (T*)dx, partials, rows, d, dy_ld, \
-      x_ld, dx_ld)
+      x_ld, dx_ld, (const T*)dres, dres_ld)
   if (vec && threads <= 256) TFB_LN_BWD(true, 256);
   else if (vec) TFB_LN_BWD(true, 1024);
   else if (threads <= 256) TFB_LN_BWD(false, 256);
@@ -290,25 +327,35 @@ extern "C" int64_t tfb_layernorm_bwd_partials(int64_t rows, int64_t d) {
   return n < 1 ? 1 : n;
 }
 
-extern "C" int tfb_layernorm_bwd(const void* dy, const void* x, const void* alpha,
-                                 const float* mean, const float* rstd, void* dx, void* dalpha,
-                                 void* dbeta, float* partials, int64_t n_partials, int64_t rows,
-                                 int64_t d, int64_t dy_ld, int64_t x_ld, int64_t dx_ld, int dtype,
-                                 void* stream) {
+extern "C" int tfb_layernorm_bwd_res(const void* dy, const void* x, const void* alpha, const float* mean,
+                                     const float* rstd, const void* dres, void* dx, void* dalpha, void* dbeta,
+                                     float* partials, int64_t n_partials, int64_t rows, int64_t d, int64_t dy_ld,
+                                     int64_t x_ld, int64_t dres_ld, int64_t dx_ld, int dtype, void* stream) {
   TFB_REQUIRE(rows > 0 && d > 0, "layernorm_bwd: bad shape rows=%lld d=%lld", (long long)rows,
               (long long)d);
   if (d > 8192) return fail(TFB_ERR_UNSUPPORTED, "layernorm_bwd: d=%lld > 8192", (long long)d);
   TFB_REQUIRE(n_partials == tfb_layernorm_bwd_partials(rows, d),
               "layernorm_bwd: scratch must hold tfb_layernorm_bwd_partials() rows");
-  TFB_REQUIRE(dy_ld >= d && x_ld >= d && dx_ld >= d, "layernorm_bwd: row stride smaller than d");
+  TFB_REQUIRE(dy_ld >= d && x_ld >= d && dx_ld >= d && (!dres || dres_ld >= d),
+              "layernorm_bwd: row stride smaller than d");
   cudaStream_t st = (cudaStream_t)stream;
   const bool vec = (d % 8 == 0) && (x_ld % 8 == 0) && (dy_ld % 8 == 0) && (dx_ld % 8 == 0) &&
-                   aligned16(x) && aligned16(dy) && aligned16(dx);
+                   aligned16(x) && aligned16(dy) && aligned16(dx) &&
+                   (!dres || (aligned16(dres) && dres_ld % 8 == 0));
   const int threads = ln_bwd_threads(d);
   TFB_DISPATCH_16(dtype, T, {
     return ln_bwd_launch<T>(dy, x, alpha, mean, rstd, dx, dalpha, dbeta, partials, n_partials, rows,
-                            (int)d, dy_ld, x_ld, dx_ld, vec, threads, st);
+                            (int)d, dy_ld, x_ld, dx_ld, vec, threads, st, dres, dres_ld);
   })
+}
+
+extern "C" int tfb_layernorm_bwd(const void* dy, const void* x, const void* alpha,
+                                 const float* mean, const float* rstd, void* dx, void* dalpha,
+                                 void* dbeta, float* partials, int64_t n_partials, int64_t rows,
+                                 int64_t d, int64_t dy_ld, int64_t x_ld, int64_t dx_ld, int dtype,
+                                 void* stream) {
+  return tfb_layernorm_bwd_res(dy, x, alpha, mean, rstd, nullptr, dx, dalpha, dbeta, partials, n_partials, rows,
+                               d, dy_ld, x_ld, 0, dx_ld, dtype, stream);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -9,12 +9,16 @@ std::atomic<int> g_force_generic_gemm{0};
 std::atomic<int> g_force_fallback_attn{0};
 std::atomic<int> g_attn_debug{0};
 
-int gemm_generic(const void*, const void*, void*, const void*, int64_t, int64_t, int64_t, int64_t, int64_t,
-                 int64_t, int64_t, int64_t, int, int, int, cudaStream_t);
-int gemm_tc05(const void*, const void*, void*, const void*, int64_t, int64_t, int64_t, int64_t, int64_t,
-              int64_t, int64_t, int64_t, int, int, int, cudaStream_t);
-bool gemm_tc05_eligible(const void*, const void*, const void*, const void*, int64_t, int64_t, int64_t, int64_t,
-                        int64_t, int64_t, int64_t, int64_t);
+int gemm_generic(const void* a, const void* b, void* c, const void* bias, const void* addend, int64_t ld_addend,
+                 const void* mask, int64_t ld_mask, int64_t M, int64_t N, int64_t K, int64_t a_sm, int64_t a_sk,
+                 int64_t b_sk, int64_t b_sn, int64_t ldc, int relu, int dtype, cudaStream_t st);
+int gemm_tc05(const void* a, const void* b, void* c, const void* bias, const void* addend, int64_t ld_addend,
+              const void* mask, int64_t ld_mask, int64_t M, int64_t N, int64_t K, int64_t a_sm, int64_t a_sk,
+              int64_t b_sk, int64_t b_sn, int64_t ldc, int relu, int dtype, void* workspace,
+              int64_t workspace_bytes, cudaStream_t st);
+bool gemm_tc05_eligible(const void* a, const void* b, const void* c, const void* bias, const void* addend,
+                        int64_t ld_addend, const void* mask, int64_t ld_mask, int64_t M, int64_t N, int64_t K,
+                        int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int64_t ldc);
 int gemm_tc05_status(int reset);
 int attn_tc05_status(int reset);
 int attn_bwd_tc05_status(int reset);
@@ -45,9 +49,10 @@ extern "C" void tfb_debug_set(int key, int value) {
   if (key == 2) g_attn_debug.store(value);
 }
 
-extern "C" int tfb_gemm(const void* a, const void* b, void* c, const void* bias, int64_t M, int64_t N,
-                        int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int64_t ldc,
-                        int relu, int accumulate, int dtype, void* stream, int* path) {
+extern "C" int tfb_gemm_fused(const void* a, const void* b, void* c, const void* bias, const void* addend,
+                              int64_t ld_addend, const void* mask, int64_t ld_mask, int64_t M, int64_t N, int64_t K,
+                              int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int64_t ldc, int relu,
+                              int dtype, void* workspace, int64_t workspace_bytes, void* stream, int* path) {
   TFB_REQUIRE(M >= 0 && N >= 0 && K >= 0, "gemm: negative dimension");
   TFB_REQUIRE(M < (1LL << 31) && N < (1LL << 31) && K < (1LL << 31), "gemm: dimension exceeds 2^31");
   TFB_REQUIRE(a_sm == 1 || a_sk == 1, "gemm: A needs a unit stride (a_sm=%lld a_sk=%lld)", (long long)a_sm,
@@ -55,13 +60,26 @@ extern "C" int tfb_gemm(const void* a, const void* b, void* c, const void* bias,
   TFB_REQUIRE(b_sk == 1 || b_sn == 1, "gemm: B needs a unit stride (b_sk=%lld b_sn=%lld)", (long long)b_sk,
               (long long)b_sn);
   TFB_REQUIRE(ldc >= N, "gemm: ldc=%lld smaller than N=%lld", (long long)ldc, (long long)N);
+  TFB_REQUIRE(!addend || ld_addend >= N, "gemm: addend leading dimension smaller than N");
+  TFB_REQUIRE(!mask || ld_mask >= N, "gemm: mask leading dimension smaller than N");
   TFB_REQUIRE(dtype == TFB_F16 || dtype == TFB_BF16, "gemm: dtype %d: expected fp16 or bf16", dtype);
   if (M == 0 || N == 0) return TFB_OK;
   TFB_REQUIRE(K > 0, "gemm: empty contraction");
   cudaStream_t st = (cudaStream_t)stream;
   const bool fast = !g_force_generic_gemm.load() &&
-                    gemm_tc05_eligible(a, b, c, bias, M, N, K, a_sm, a_sk, b_sk, b_sn, ldc);
+                    gemm_tc05_eligible(a, b, c, bias, addend, ld_addend, mask, ld_mask, M, N, K, a_sm, a_sk, b_sk,
+                                       b_sn, ldc);
   if (path) *path = fast ? 1 : 0;
-  if (fast) return gemm_tc05(a, b, c, bias, M, N, K, a_sm, a_sk, b_sk, b_sn, ldc, relu, accumulate, dtype, st);
-  return gemm_generic(a, b, c, bias, M, N, K, a_sm, a_sk, b_sk, b_sn, ldc, relu, accumulate, dtype, st);
+  if (fast)
+    return gemm_tc05(a, b, c, bias, addend, ld_addend, mask, ld_mask, M, N, K, a_sm, a_sk, b_sk, b_sn, ldc, relu,
+                     dtype, workspace, workspace_bytes, st);
+  return gemm_generic(a, b, c, bias, addend, ld_addend, mask, ld_mask, M, N, K, a_sm, a_sk, b_sk, b_sn, ldc, relu,
+                      dtype, st);
+}
+
+extern "C" int tfb_gemm(const void* a, const void* b, void* c, const void* bias, int64_t M, int64_t N,
+                        int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int64_t ldc,
+                        int relu, int accumulate, int dtype, void* stream, int* path) {
+  return tfb_gemm_fused(a, b, c, bias, accumulate ? c : nullptr, ldc, nullptr, 0, M, N, K, a_sm, a_sk, b_sk, b_sn,
+                        ldc, relu, dtype, nullptr, 0, stream, path);
 }

@@ -27,18 +27,46 @@ def _as_rows(x: torch.Tensor) -> torch.Tensor:
 PROFILE = None
 
 
-def gemm(a, a_sm, a_sk, b, b_sk, b_sn, m, n, k, bias=None, relu=False, out=None, accumulate=False):
-    """C[m,n] = act(sum_k A(m,k) B(k,n) + bias) with element strides for A and B."""
+# When True, a weight gradient is added straight into an existing, contiguous `.grad` by the GEMM
+# epilogue (one rounding of accumulator + old value) and the Function reports no gradient for the
+# weight, so autograd launches no separate accumulation kernel.  Off by default because parameter
+# hooks do not fire for gradients delivered this way; the benchmark and the data-parallel buckets
+# turn it on.
+ACCUMULATE_INTO_GRAD = False
+
+_workspaces = {}
+
+
+def _splitk_workspace(device, nbytes):
+    """Per-device fp32 scratch for the split-K path of small-output GEMMs (grown on demand)."""
+    ws = _workspaces.get(device)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 32 << 20), device=device, dtype=torch.uint8)
+        _workspaces[device] = ws
+    return ws
+
+
+def gemm(a, a_sm, a_sk, b, b_sk, b_sn, m, n, k, bias=None, relu=False, out=None, accumulate=False,
+         addend=None, mask=None):
+    """C[m,n] = mask(act(sum_k A(m,k) B(k,n) + bias) + addend) with element strides for A and B.
+
+    `addend` and `mask` are (m, n) tensors with unit inner stride; `accumulate` adds into `out`."""
     if out is None:
         out = torch.empty((m, n), device=a.device, dtype=a.dtype)
+    if accumulate:
+        addend = out
     path = ctypes.c_int(0)
+    ws = _splitk_workspace(a.device, m * n * 4) if (m * n <= (8 << 20) and k >= 2048) else None
     if PROFILE is not None:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-    _lib.check(_lib.lib.tfb_gemm(
+    _lib.check(_lib.lib.tfb_gemm_fused(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), bias.data_ptr() if bias is not None else None,
-        m, n, k, a_sm, a_sk, b_sk, b_sn, out.stride(0), 1 if relu else 0, 1 if accumulate else 0,
-        _lib.dtype_code(a.dtype), _lib.stream_ptr(a.device), ctypes.byref(path)))
+        addend.data_ptr() if addend is not None else None, addend.stride(0) if addend is not None else 0,
+        mask.data_ptr() if mask is not None else None, mask.stride(0) if mask is not None else 0,
+        m, n, k, a_sm, a_sk, b_sk, b_sn, out.stride(0), 1 if relu else 0, _lib.dtype_code(a.dtype),
+        ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+        _lib.stream_ptr(a.device), ctypes.byref(path)))
     if PROFILE is not None:
         e1.record()
         PROFILE.append((2.0 * m * n * k, e0, e1, path.value, (m, n, k)))
@@ -55,30 +83,56 @@ def _check_linear(x, w, bias):
         assert bias.dtype == x.dtype and bias.numel() == w.shape[1], "bias must be (out_features,)"
 
 
-def linear_forward(x, w, bias, relu):
+def linear_forward(x, w, bias, relu, residual=None):
     _check_linear(x, w, bias)
     x2 = _as_rows(x)
     if w.stride(0) != 1 and w.stride(1) != 1:
         w = w.contiguous()
     m, k = x2.shape
     n = w.shape[1]
+    res2 = None
+    if residual is not None:
+        res2 = residual.reshape(-1, n)
+        if res2.stride(1) != 1:
+            res2 = res2.contiguous()
     y = gemm(x2, x2.stride(0), x2.stride(1), w, w.stride(0), w.stride(1), m, n, k,
-             bias=bias.contiguous() if bias is not None else None, relu=relu)
+             bias=bias.contiguous() if bias is not None else None, relu=relu, addend=res2)
     return y.view(*x.shape[:-1], n)
+
+
+def input_grad(dy, w, x_shape, mask=None, addend=None, out=None):
+    """dX = dY Wᵀ (optionally masked by a saved ReLU output, optionally added to `addend`)."""
+    dy2 = _as_rows(dy)
+    m, n = dy2.shape
+    k = w.shape[0]
+    m2 = mask.reshape(m, k) if mask is not None else None
+    a2 = addend.reshape(m, k) if addend is not None else None
+    o2 = out.reshape(m, k) if out is not None else None
+    # B(kk, nn) = W[nn, kk]
+    return gemm(dy2, dy2.stride(0), dy2.stride(1), w, w.stride(1), w.stride(0), m, k, n, mask=m2, addend=a2,
+                out=o2).view(x_shape)
+
+
+def weight_grad(x, dy, w):
+    """dW = Xᵀ dY over every row of the flattened batch.  Returns None when the product was added
+    straight into `w.grad` (see ACCUMULATE_INTO_GRAD)."""
+    x2, dy2 = _as_rows(x), _as_rows(dy)
+    m, k = x2.shape
+    n = dy2.shape[1]
+    into = None
+    if ACCUMULATE_INTO_GRAD and w.grad is not None and w.grad.is_contiguous() and w.grad.dtype == x.dtype \
+            and w.grad.shape == (k, n):
+        into = w.grad
+    # A(mm, kk) = X[kk, mm]
+    dw = gemm(x2, x2.stride(1), x2.stride(0), dy2, dy2.stride(0), dy2.stride(1), k, n, m, out=into,
+              accumulate=into is not None)
+    return None if into is not None else dw
 
 
 def linear_backward(dy, x, w, need_dx=True, need_dw=True):
     """dX = dY Wᵀ, dW = Xᵀ dY (contraction over every row of the flattened batch)."""
-    x2, dy2 = _as_rows(x), _as_rows(dy)
-    m, k = x2.shape
-    n = w.shape[1]
-    dx = dw = None
-    if need_dx:
-        # B(kk, nn) = W[nn, kk]
-        dx = gemm(dy2, dy2.stride(0), dy2.stride(1), w, w.stride(1), w.stride(0), m, k, n).view(x.shape)
-    if need_dw:
-        # A(mm, kk) = X[kk, mm]
-        dw = gemm(x2, x2.stride(1), x2.stride(0), dy2, dy2.stride(0), dy2.stride(1), k, n, m)
+    dx = input_grad(dy, w, x.shape) if need_dx else None
+    dw = weight_grad(x, dy, w) if need_dw else None
     return dx, dw
 
 

@@ -22,6 +22,12 @@ import torch.nn as nn
 from . import fast_causal_attention, fast_causal_attention_with_bias
 from . import nn as tnn
 from .crossentropy import CrossEntropyLossFP32
+from .fused import LayerNormFork, LinearResidual, MLPResidual, QKVProjection
+
+# The layer runs on fused Functions (residual adds, ReLU mask and the q/k/v input gradients folded into
+# kernel epilogues).  Set to False to run the layer module by module through the plain Functions,
+# exactly as the reference composes it; results agree to rounding.
+USE_FUSED_BLOCKS = True
 
 
 @dataclass(frozen=True)
@@ -140,8 +146,24 @@ class TransformerLayer(nn.Module):
         self.mlp = MLPBlock(config, device=device)
 
     def forward(self, hidden_states: torch.Tensor, attn_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-        hidden_states = hidden_states + self.attention(self.input_layernorm(hidden_states), attn_bias)
-        return hidden_states + self.mlp(self.post_attention_layernorm(hidden_states))
+        if not USE_FUSED_BLOCKS or not hidden_states.is_cuda:
+            hidden_states = hidden_states + self.attention(self.input_layernorm(hidden_states), attn_bias)
+            return hidden_states + self.mlp(self.post_attention_layernorm(hidden_states))
+        att, mlp = self.attention, self.mlp
+        ln1, ln2 = self.input_layernorm, self.post_attention_layernorm
+        normed, residual = LayerNormFork.apply(hidden_states, ln1.weight, ln1.bias, ln1.eps)
+        q, k, v = QKVProjection.apply(normed, att.q_proj.weight, att.k_proj.weight, att.v_proj.weight)
+        b, s, d = q.shape
+        q, k, v = att._heads(q), att._heads(k), att._heads(v)
+        if attn_bias is None:
+            ctx = fast_causal_attention.apply(q, k, v)
+        else:
+            ctx = fast_causal_attention_with_bias.apply(q, k, v, attn_bias)
+        ctx = ctx.transpose(1, 2).contiguous().view(b, s, d)
+        hidden_states = LinearResidual.apply(ctx, att.out_proj.weight, None, residual)
+        normed, residual = LayerNormFork.apply(hidden_states, ln2.weight, ln2.bias, ln2.eps)
+        return MLPResidual.apply(normed, mlp.dense_h_to_4h.weight, mlp.dense_h_to_4h.bias,
+                                 mlp.dense_4h_to_h.weight, mlp.dense_4h_to_h.bias, residual)
 
 
 class Transformer(nn.Module):
