@@ -7,8 +7,9 @@
 //   warp 1  : MMA issuer    - one elected lane issues tcgen05.mma (M=128, N=BN, K=16) into one
 //                             of two TMEM accumulator buffers, commits ring slots back
 //   warps 2-5: epilogue     - tcgen05.ld the finished accumulator (each warp its 32 lanes),
-//                             bias / ReLU / accumulate, round once, 16-byte global stores;
-//                             overlaps the next tile's main loop through the second buffer
+//                             bias / ReLU / addend / mask in fp32, round once into a swizzled smem
+//                             box, TMA store (the addend / mask box arrives by TMA load); overlaps
+//                             the next tile's main loop through the second accumulator buffer
 // Either operand may be K-major (contraction index contiguous) or MN-major, so the forward
 // product X·W, the input gradient dY·Wᵀ and the weight gradient Xᵀ·dY (contraction over every
 // token of the batch, i.e. the batch reduction fused into the product) are the same kernel.
@@ -26,7 +27,11 @@ template <int BN> struct GemmCfg {
   static constexpr int B_BYTES = BN * TB_K * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+  static constexpr int EPI_BYTES = 4 * 4096;  // per epilogue warp: one 32-row x 64-column 16-bit box
+  static constexpr int OFF_EPI_C = STAGES * STAGE_BYTES;       // output staging for the TMA store
+  static constexpr int OFF_EPI_X = OFF_EPI_C + EPI_BYTES;      // addend / mask staging filled by TMA
+  static constexpr int OFF_BAR = OFF_EPI_X + EPI_BYTES;
+  static constexpr int SMEM_BYTES = OFF_BAR + 1024 /*align slack*/ + 256 /*barriers*/;
   static constexpr int TMEM_COLS = 2 * BN;
 };
 
@@ -45,18 +50,21 @@ struct GemmParams {
 template <typename T, int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(TB_THREADS, 1) gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA,
                                                                   const __grid_constant__ CUtensorMap tmB,
+                                                                  const __grid_constant__ CUtensorMap tmC,
+                                                                  const __grid_constant__ CUtensorMap tmX,
                                                                   const GemmParams p) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the swizzle pattern is a function of the shared-memory address
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
   uint64_t* full = bars;                    // [STAGES] TMA -> MMA
   uint64_t* empty = bars + STAGES;          // [STAGES] MMA -> TMA
   uint64_t* acc_full = bars + 2 * STAGES;   // [2] MMA -> epilogue
   uint64_t* acc_empty = acc_full + 2;       // [2] epilogue -> MMA
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* x_full = acc_empty + 2;         // [4] addend / mask box of an epilogue warp landed
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(x_full + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -69,6 +77,7 @@ __global__ void __launch_bounds__(TB_THREADS, 1) gemm_tc05_kernel(const __grid_c
       mbar_init(&acc_full[i], 1);
       mbar_init(&acc_empty[i], 4);  // one arrival per epilogue warp
     }
+    for (int i = 0; i < 4; ++i) mbar_init(&x_full[i], 1);
     // an earlier kernel that gave up leaves the status set: then this one does nothing
     *abort_flag = (*(volatile int*)&g_dev_status != 0) ? 1 : 0;
     mbar_fence_init();
@@ -165,102 +174,122 @@ __global__ void __launch_bounds__(TB_THREADS, 1) gemm_tc05_kernel(const __grid_c
     }
   } else {
     // ---------------------------------------------------------------------- epilogue
+    // Each warp owns 32 accumulator rows.  Per 64-column step it reads its TMEM slice, applies
+    // bias / ReLU / addend / mask in fp32, rounds once into a swizzled 32 x 64 box in shared memory
+    // and hands the box to the TMA unit, which writes full 128-byte rows and clips at the matrix
+    // edges.  The addend or mask box of the next step is fetched by TMA while this one is computed.
     const int q = warp & 3;  // TMEM lane quarter this warp may read
-    T* C = reinterpret_cast<T*>(p.C);
+    const int ew = warp - 2; // 0..3: index of this warp's staging boxes and barrier
     const T* bias = reinterpret_cast<const T*>(p.bias);
-    const T* addend = reinterpret_cast<const T*>(p.addend);
-    const T* mask = reinterpret_cast<const T*>(p.mask);
+    uint8_t* stage_c = smem + Cfg::OFF_EPI_C + ew * 4096;
+    uint8_t* stage_x = smem + Cfg::OFF_EPI_X + ew * 4096;
+    // at most one of addend / mask travels through the TMA box; a second one is read directly
+    const bool x_is_addend = p.addend != nullptr;
+    const bool use_x = (p.addend != nullptr || p.mask != nullptr) && p.splits == 1;
+    const T* mask_direct = (p.addend != nullptr && p.mask != nullptr) ? reinterpret_cast<const T*>(p.mask) : nullptr;
+    constexpr int STEPS = BN / 64;
     int buf = 0;
-    uint32_t acc_phase = 0;
+    uint32_t acc_phase = 0, x_phase = 0;
     bool ok = true;
+    if (lane == 0) {
+      tma_prefetch_desc(&tmC);
+      if (use_x) tma_prefetch_desc(&tmX);
+    }
     for (int unit = blockIdx.x; unit < num_tiles && ok; unit += gridDim.x) {
       const int tile = unit / p.splits;
       const int m0 = (tile % p.tiles_m) * TB_M;
       const int n0 = (tile / p.tiles_m) * BN;
-      const int row = m0 + q * 32 + lane;
-      const bool row_ok = row < p.M;
-      const bool fused_in = (addend != nullptr || mask != nullptr) && p.splits == 1;
-      // addend / mask vectors of a 32-column chunk are fetched one chunk ahead (the first chunk while
-      // the tile's main loop is still running), so their latency is off the epilogue's critical path
-      uint4 addv[2][4], mskv[2][4];
-      auto prefetch = [&](int c, int slot) {
-        if (!fused_in || !row_ok) return;
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          const int col = n0 + c * 32 + v * 8;
-          if (col + 8 <= p.N) {
-            if (addend) addv[slot][v] = *reinterpret_cast<const uint4*>(addend + (int64_t)row * p.ld_addend + col);
-            if (mask) mskv[slot][v] = *reinterpret_cast<const uint4*>(mask + (int64_t)row * p.ld_mask + col);
-          }
-        }
-      };
-      prefetch(0, 0);
+      const int row0 = m0 + q * 32;       // first row of this warp's slice
+      const int row = row0 + lane;
+      if (use_x && lane == 0) {           // box of step 0, in flight while the main loop still runs
+        mbar_expect_tx(&x_full[ew], 4096);
+        tma_load_2d(stage_x, &tmX, n0, row0, &x_full[ew]);
+      }
       if (!mbar_wait(&acc_full[buf], acc_phase, 0x400 | buf, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
-#pragma unroll
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(taddr + c * 32, r);
-        if (c + 1 < BN / 32) prefetch(c + 1, (c + 1) & 1);
+#pragma unroll 1
+      for (int st = 0; st < STEPS && ok; ++st) {
+        const int col0 = n0 + st * 64;
+        uint32_t r0[32], r1[32];
+        tmem_ld32(taddr + st * 64, r0);
+        tmem_ld32(taddr + st * 64 + 32, r1);
         tc_wait_ld();
-        const int col0 = n0 + c * 32;
-        if (row_ok && col0 < p.N) {
-          if (p.splits > 1) {
-            // partial sum of this K range: fp32 adds into the workspace; the finishing kernel applies
-            // bias / ReLU / addend / mask and rounds once (N % 8 == 0 on this path)
+        if (p.splits > 1) {
+          // partial sum of this K range: fp32 adds into the workspace; the finishing kernel applies
+          // bias / ReLU / addend / mask and rounds once (N % 8 == 0 on this path)
+          if (row < p.M) {
             float* w = p.ws + (int64_t)row * p.N + col0;
 #pragma unroll
             for (int e = 0; e < 32; e += 4) {
               if (col0 + e < p.N)
-                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(w + e), "f"(__uint_as_float(r[e])),
-                             "f"(__uint_as_float(r[e + 1])), "f"(__uint_as_float(r[e + 2])),
-                             "f"(__uint_as_float(r[e + 3]))
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(w + e), "f"(__uint_as_float(r0[e])),
+                             "f"(__uint_as_float(r0[e + 1])), "f"(__uint_as_float(r0[e + 2])),
+                             "f"(__uint_as_float(r0[e + 3]))
+                             : "memory");
+              if (col0 + 32 + e < p.N)
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(w + 32 + e),
+                             "f"(__uint_as_float(r1[e])), "f"(__uint_as_float(r1[e + 1])),
+                             "f"(__uint_as_float(r1[e + 2])), "f"(__uint_as_float(r1[e + 3]))
                              : "memory");
             }
-            continue;
           }
-          T* dst = C + (int64_t)row * p.ldc + col0;
+          continue;
+        }
+        if (use_x) {
+          if (!mbar_wait(&x_full[ew], x_phase, 0x500 | ew, abort_flag)) { ok = false; break; }
+          x_phase ^= 1;
+        }
+        // the staging box of the previous step must have been read by the TMA unit
+        if (lane == 0) tma_store_wait_read();
+        __syncwarp();
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            const int col = col0 + v * 8;
-            if (col >= p.N) break;
-            float f[8];
+        for (int v = 0; v < 8; ++v) {  // 16-byte chunks (8 columns) of this thread's row
+          const int col = col0 + v * 8;
+          float f[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
+          for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v < 4 ? r0[v * 8 + j] : r1[(v - 4) * 8 + j]);
+          if (bias && col < p.N) {
             if (col + 8 <= p.N) {
-              if (bias) {
-                float b[8];
-                unpack8<T>(__ldg(reinterpret_cast<const uint4*>(bias + col)), b);
+              float b[8];
+              unpack8<T>(__ldg(reinterpret_cast<const uint4*>(bias + col)), b);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) f[j] += b[j];
-              }
-              if (p.relu) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) f[j] = fmaxf(f[j], 0.f);
-              }
-              if (addend) {
-                float o[8];
-                unpack8<T>(addv[c & 1][v], o);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) f[j] += o[j];
-              }
-              if (mask) {
-                float o[8];
-                unpack8<T>(mskv[c & 1][v], o);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) f[j] = o[j] > 0.f ? f[j] : 0.f;
-              }
-              *reinterpret_cast<uint4*>(dst + v * 8) = pack8<T>(f);
+              for (int j = 0; j < 8; ++j) f[j] += b[j];
             } else {
-              for (int j = 0; j < 8 && col + j < p.N; ++j) {
-                float x = f[j];
-                if (bias) x += Num<T>::to_f(bias[col + j]);
-                if (p.relu) x = fmaxf(x, 0.f);
-                if (addend) x += Num<T>::to_f(addend[(int64_t)row * p.ld_addend + col + j]);
-                if (mask && !(Num<T>::to_f(mask[(int64_t)row * p.ld_mask + col + j]) > 0.f)) x = 0.f;
-                dst[v * 8 + j] = Num<T>::from_f(x);
-              }
+              for (int j = 0; j < 8 && col + j < p.N; ++j) f[j] += Num<T>::to_f(bias[col + j]);
+            }
+          }
+          if (p.relu) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = fmaxf(f[j], 0.f);
+          }
+          const uint32_t soff = lane * 128 + ((v ^ (lane & 7)) << 4);
+          if (use_x) {
+            float o[8];
+            unpack8<T>(*reinterpret_cast<const uint4*>(stage_x + soff), o);
+            if (x_is_addend) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) f[j] += o[j];
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) f[j] = o[j] > 0.f ? f[j] : 0.f;
+            }
+          }
+          if (mask_direct && row < p.M) {
+            for (int j = 0; j < 8 && col + j < p.N; ++j)
+              if (!(Num<T>::to_f(mask_direct[(int64_t)row * p.ld_mask + col + j]) > 0.f)) f[j] = 0.f;
+          }
+          *reinterpret_cast<uint4*>(stage_c + soff) = pack8<T>(f);
+        }
+        fence_proxy_async_smem();  // staged output visible to the TMA unit; addend box reads are done
+        __syncwarp();
+        if (lane == 0) {
+          if (col0 < p.N && row0 < p.M) tma_store_2d(&tmC, stage_c, col0, row0);
+          tma_store_commit();
+          if (use_x) {  // next box: the next step of this tile, or nothing (step 0 of the next tile is issued above)
+            if (st + 1 < STEPS) {
+              mbar_expect_tx(&x_full[ew], 4096);
+              tma_load_2d(stage_x, &tmX, col0 + 64, row0, &x_full[ew]);
             }
           }
         }
@@ -271,6 +300,7 @@ __global__ void __launch_bounds__(TB_THREADS, 1) gemm_tc05_kernel(const __grid_c
       buf ^= 1;
       if (buf == 0) acc_phase ^= 1;
     }
+    if (lane == 0) tma_store_wait_all();  // global writes of this warp are complete before the CTA exits
   }
 
   // Unwind: every role has left its loop (normally or through a bounded wait).
@@ -379,7 +409,8 @@ static int sm_count() {
 }
 
 template <typename T, int BN, bool A_MN, bool B_MN>
-static int launch_tc05(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t st) {
+static int launch_tc05(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmX,
+                       const GemmParams& p, cudaStream_t st) {
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_tc05_kernel<T, BN, A_MN, B_MN>;
   static bool attr_set = false;  // benign race: the call is idempotent
@@ -394,7 +425,7 @@ static int launch_tc05(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
     cudaError_t e = cudaMemsetAsync(p.ws, 0, (size_t)p.M * p.N * sizeof(float), st);
     if (e != cudaSuccess) return fail(TFB_ERR_LAUNCH, "gemm_tc05: workspace memset: %s", cudaGetErrorString(e));
   }
-  kern<<<grid, TB_THREADS, Cfg::SMEM_BYTES, st>>>(tmA, tmB, p);
+  kern<<<grid, TB_THREADS, Cfg::SMEM_BYTES, st>>>(tmA, tmB, tmC, tmX, p);
   int rc = launched("gemm_tc05");
   if (rc || p.splits == 1) return rc;
   const int64_t total = (int64_t)p.M * (p.N / 8);
@@ -405,11 +436,11 @@ static int launch_tc05(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
 
 template <typename T, int BN>
 static int dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& tmA, const CUtensorMap& tmB,
-                          const GemmParams& p, cudaStream_t st) {
-  if (a_mn && b_mn) return launch_tc05<T, BN, true, true>(tmA, tmB, p, st);
-  if (a_mn) return launch_tc05<T, BN, true, false>(tmA, tmB, p, st);
-  if (b_mn) return launch_tc05<T, BN, false, true>(tmA, tmB, p, st);
-  return launch_tc05<T, BN, false, false>(tmA, tmB, p, st);
+                          const CUtensorMap& tmC, const CUtensorMap& tmX, const GemmParams& p, cudaStream_t st) {
+  if (a_mn && b_mn) return launch_tc05<T, BN, true, true>(tmA, tmB, tmC, tmX, p, st);
+  if (a_mn) return launch_tc05<T, BN, true, false>(tmA, tmB, tmC, tmX, p, st);
+  if (b_mn) return launch_tc05<T, BN, false, true>(tmA, tmB, tmC, tmX, p, st);
+  return launch_tc05<T, BN, false, false>(tmA, tmB, tmC, tmX, p, st);
 }
 
 // Whether (ptr, strides) can be described by a TMA tensor map of 16-bit elements.
@@ -450,8 +481,18 @@ int gemm_tc05(const void* a, const void* b, void* c, const void* bias, const voi
       workspace_bytes >= (int64_t)M * N * (int64_t)sizeof(float) && aligned16(workspace))
     splits = 2;
 
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmC, tmX;
   int rc;
+  {
+    // output and addend/mask: (N inner, M outer), boxes of 64 columns x 32 rows
+    uint64_t dims[2] = {(uint64_t)N, (uint64_t)M}, str[1] = {(uint64_t)ldc * 2};
+    uint32_t box[2] = {64, 32};
+    if ((rc = encode_tmap_sw128(&tmC, c, dtype, 2, dims, str, box))) return rc;
+    const void* xp = addend ? addend : mask;
+    str[0] = (uint64_t)(addend ? ld_addend : ld_mask) * 2;
+    if (xp) { if ((rc = encode_tmap_sw128(&tmX, xp, dtype, 2, dims, str, box))) return rc; }
+    else tmX = tmC;
+  }
   {
     uint64_t dims[2], str[1];
     uint32_t box[2];
@@ -468,8 +509,8 @@ int gemm_tc05(const void* a, const void* b, void* c, const void* bias, const voi
   p.relu = relu;
   p.tiles_m = (int)tm; p.tiles_n = (int)ceil_div(N, BN); p.splits = splits;
   TFB_DISPATCH_16(dtype, T, {
-    if (BN == 256) return dispatch_major<T, 256>(a_mn, b_mn, tmA, tmB, p, st);
-    return dispatch_major<T, 128>(a_mn, b_mn, tmA, tmB, p, st);
+    if (BN == 256) return dispatch_major<T, 256>(a_mn, b_mn, tmA, tmB, tmC, tmX, p, st);
+    return dispatch_major<T, 128>(a_mn, b_mn, tmA, tmB, tmC, tmX, p, st);
   })
 }
 
