@@ -43,7 +43,10 @@ template <int HD> struct FbCfg {
   static constexpr int OFF_P = OFF_DO + QSTAGES * TILE_BYTES;        // Pᵀ  128 x 128 x 2 B
   static constexpr int OFF_DS = OFF_P + 32768;                       // dSᵀ 128 x 128 x 2 B
   static constexpr int OFF_STAT = OFF_DS + 32768;                    // 2 x (lse2[128], delta[128]) fp32
-  static constexpr int OFF_BAR = OFF_STAT + 2048;
+  // dQ_i staging for the TMA reduction (head_dim 64 only: it does not fit next to 128-wide tiles)
+  static constexpr bool DQ_TMA = (HD == 64);
+  static constexpr int OFF_DQ = OFF_STAT + 2048;                     // 4 drain warps x 2 boxes of 32 rows x 128 B
+  static constexpr int OFF_BAR = OFF_DQ + (DQ_TMA ? 32768 : 0);
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
   static constexpr int COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 256 + HD;
   // dQ_i has columns of its own when they fit (hd 64); otherwise it reuses the Sᵀ columns
@@ -96,6 +99,7 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
                                                                       const __grid_constant__ CUtensorMap tmK,
                                                                       const __grid_constant__ CUtensorMap tmV,
                                                                       const __grid_constant__ CUtensorMap tmDO,
+                                                                      const __grid_constant__ CUtensorMap tmDQ,
                                                                       const FbParams p) {
   using Cfg = FbCfg<HD>;
   constexpr int QS = Cfg::QSTAGES;
@@ -298,18 +302,19 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
         long long t3 = 0, t4 = 0;
         if (ok) {
           tc_fence_after();
+          const bool plain = !BIAS && !diag;  // no bias and not the diagonal tile: scale, subtract, 2^x
 #pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            const int col0 = half * 64 + c * 32;  // first query column of this chunk
-            uint32_t sv_[32], dv_[32];
+          for (int c = 0; c < 4; ++c) {         // 16-column steps keep the live register set small
+            const int col0 = half * 64 + c * 16;
+            uint32_t sv_[16], dv_[16];
             PROF_T(tl0);
-            tmem_ld32(lane_addr + Cfg::COL_S + col0, sv_);
-            tmem_ld32(lane_addr + Cfg::COL_DP + col0, dv_);
+            tmem_ld16(lane_addr + Cfg::COL_S + col0, sv_);
+            tmem_ld16(lane_addr + Cfg::COL_DP + col0, dv_);
             tc_wait_ld();
             PROF_T(tl1);
             PROF_ADD(14, tl0, tl1);
 #pragma unroll
-            for (int e4 = 0; e4 < 8; ++e4) {
+            for (int e4 = 0; e4 < 4; ++e4) {
               const float4 l4 = *reinterpret_cast<const float4*>(s_lse2 + col0 + e4 * 4);
               const float4 d4 = *reinterpret_cast<const float4*>(s_delta + col0 + e4 * 4);
               const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
@@ -318,20 +323,20 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
 #pragma unroll
               for (int k = 0; k < 4; ++k) {
                 const int e = e4 * 4 + k;
-                if (!BIAS && !diag) {
-                  pe[k] = ex2_approx_b(fmaf(__uint_as_float(sv_[e]), c2, -lv[k]));
+                float x = fmaf(__uint_as_float(sv_[e]), c2, -lv[k]);
+                if (plain) {
+                  pe[k] = ex2_approx_b(x);
                 } else {
                   const int i = i0 + col0 + e;
-                  float x = fmaf(__uint_as_float(sv_[e]), c2, -lv[k]);
                   if (BIAS) x += alibi_term_b(p.bias_mode, slope, max(i - j, 0)) * kLog2eB;
                   pe[k] = (j > i) ? 0.f : ex2_approx_b(x);
                 }
                 de[k] = pe[k] * (__uint_as_float(dv_[e]) - dl[k]);
               }
-              pk[c * 16 + e4 * 2] = pack2<T>(pe[0], pe[1]);
-              pk[c * 16 + e4 * 2 + 1] = pack2<T>(pe[2], pe[3]);
-              dk_[c * 16 + e4 * 2] = pack2<T>(de[0], de[1]);
-              dk_[c * 16 + e4 * 2 + 1] = pack2<T>(de[2], de[3]);
+              pk[c * 8 + e4 * 2] = pack2<T>(pe[0], pe[1]);
+              pk[c * 8 + e4 * 2 + 1] = pack2<T>(pe[2], pe[3]);
+              dk_[c * 8 + e4 * 2] = pack2<T>(de[0], de[1]);
+              dk_[c * 8 + e4 * 2 + 1] = pack2<T>(de[2], de[3]);
             }
           }
           // Pᵀ / dSᵀ of the previous tile are still being read by its gradient products
@@ -387,11 +392,16 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
     }
   } else if (!dead) {
     // ---------------------------------------------------------------------------- dQ drain
-    // warps 10-13: lanes are query rows here; each warp adds its 32 rows of dQ_i to the fp32 accumulator
+    // warps 10-13: lanes are query rows here; each warp adds its 32 rows of dQ_i to the fp32 accumulator.
+    // head_dim 64: the rows go through swizzled shared-memory boxes and the TMA unit performs the
+    // reduction (cp.reduce.async.bulk.tensor), which keeps the load/store path free for the compute
+    // warps; head_dim 128: vector red.global.add.
     const int qd = warp & 3;
     const int r = qd * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
     const bool prof = (p.debug & 2) && warp == 10 && lane == 0;
+    uint8_t* stage = smem + Cfg::OFF_DQ + (warp - 10) * 8192;
+    if (Cfg::DQ_TMA && lane == 0) tma_prefetch_desc(&tmDQ);
     for (int it = 0; it < iters; ++it) {
       const int i0 = (kt + it) * FB_T;
       PROF_T(a0);
@@ -399,26 +409,56 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
       PROF_T(a1);
       PROF_ADD(10, a0, a1);
       tc_fence_after();
-      float* dq_row = p.dq_acc + ((int64_t)bh * p.T + i0 + r) * HD;
-#pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld32(lane_addr + Cfg::COL_DQ + c * 32, v);
+      if (Cfg::DQ_TMA) {
+        uint32_t v0[32], v1[32];
+        tmem_ld32(lane_addr + Cfg::COL_DQ, v0);
+        tmem_ld32(lane_addr + Cfg::COL_DQ + 32, v1);
         tc_wait_ld();
-        if (!(p.debug & 1))
+        // TMEM is drained: the tensor core may overwrite dQ while the rows travel on
+        tc_fence_before();
+        if (lane == 0) tma_store_wait_read();  // previous boxes have been read by the TMA unit
+        __syncwarp();
+        if (lane == 0) mbar_arrive(dq_free);
+        if (!(p.debug & 1)) {
 #pragma unroll
-          for (int e = 0; e < 32; e += 4)
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + c * 32 + e),
-                         "f"(__uint_as_float(v[e])), "f"(__uint_as_float(v[e + 1])),
-                         "f"(__uint_as_float(v[e + 2])), "f"(__uint_as_float(v[e + 3]))
-                         : "memory");
+          for (int j = 0; j < 8; ++j) {  // 16-byte chunks (4 floats) of this row in each of the two boxes
+            const uint32_t off = lane * 128 + ((j ^ (lane & 7)) << 4);
+            *reinterpret_cast<uint4*>(stage + off) = make_uint4(v0[4 * j], v0[4 * j + 1], v0[4 * j + 2], v0[4 * j + 3]);
+            *reinterpret_cast<uint4*>(stage + 4096 + off) =
+                make_uint4(v1[4 * j], v1[4 * j + 1], v1[4 * j + 2], v1[4 * j + 3]);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const int row0 = (int)((int64_t)bh * p.T) + i0 + qd * 32;
+            tma_reduce_add_2d(&tmDQ, stage, 0, row0);
+            tma_reduce_add_2d(&tmDQ, stage + 4096, 32, row0);
+            tma_store_commit();
+          }
+        }
+      } else {
+        float* dq_row = p.dq_acc + ((int64_t)bh * p.T + i0 + r) * HD;
+#pragma unroll 1
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld32(lane_addr + Cfg::COL_DQ + c * 32, v);
+          tc_wait_ld();
+          if (!(p.debug & 1))
+#pragma unroll
+            for (int e = 0; e < 32; e += 4)
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + c * 32 + e),
+                           "f"(__uint_as_float(v[e])), "f"(__uint_as_float(v[e + 1])),
+                           "f"(__uint_as_float(v[e + 2])), "f"(__uint_as_float(v[e + 3]))
+                           : "memory");
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(dq_free);
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(dq_free);
       PROF_T(a2);
       PROF_ADD(11, a1, a2);
     }
+    if (Cfg::DQ_TMA && lane == 0) tma_store_wait_all();  // every reduction has reached global memory
   }
 
   tc_fence_before();
@@ -485,7 +525,14 @@ static int bwd_tc05_launch(const AttnArgs& a, int dtype, cudaStream_t st) {
   const size_t acc_bytes = (size_t)a.B * a.H * a.T * HD * sizeof(float);
   cudaError_t e = cudaMemsetAsync(a.dq_acc, 0, acc_bytes, st);
   if (e != cudaSuccess) return fail(TFB_ERR_LAUNCH, "attention_bwd(tcgen05): memset: %s", cudaGetErrorString(e));
-  CUtensorMap tq, tk, tv, tdo;
+  CUtensorMap tq, tk, tv, tdo, tdq;
+  {
+    // fp32 dQ accumulator as a (HD, B*H*T) matrix, boxes of 32 floats x 32 rows
+    const uint64_t dims[2] = {(uint64_t)HD, (uint64_t)a.B * a.H * a.T};
+    const uint64_t str[1] = {(uint64_t)HD * 4};
+    const uint32_t box[2] = {32, 32};
+    if ((rc = encode_tmap_sw128(&tdq, a.dq_acc, TFB_F32, 2, dims, str, box))) return rc;
+  }
   if ((rc = encode_bhtd(&tq, a.q, a.sq, a.B, a.H, a.T, HD, dtype))) return rc;
   if ((rc = encode_bhtd(&tk, a.k, a.sk, a.B, a.H, a.T, HD, dtype))) return rc;
   if ((rc = encode_bhtd(&tv, a.v, a.sv, a.B, a.H, a.T, HD, dtype))) return rc;
@@ -505,8 +552,8 @@ static int bwd_tc05_launch(const AttnArgs& a, int dtype, cudaStream_t st) {
     attr_set = true;
   }
   dim3 grid(a.T / FB_T, a.B * a.H);
-  if (a.bias_mode) attn_bwd_tc05_kernel<T, HD, true><<<grid, FB_THREADS, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
-  else attn_bwd_tc05_kernel<T, HD, false><<<grid, FB_THREADS, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
+  if (a.bias_mode) attn_bwd_tc05_kernel<T, HD, true><<<grid, FB_THREADS, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, tdo, tdq, p);
+  else attn_bwd_tc05_kernel<T, HD, false><<<grid, FB_THREADS, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, tdo, tdq, p);
   if ((rc = launched("attention_bwd(tcgen05)"))) return rc;
   const int64_t nvec = (int64_t)a.B * a.H * a.T * HD / 8;
   const unsigned blocks = (unsigned)(ceil_div(nvec, 256) < 148 * 8 ? ceil_div(nvec, 256) : 148 * 8);

@@ -388,7 +388,9 @@ int encode_tmap_sw128(CUtensorMap* out, const void* base, int dtype, int rank, c
     es[i] = 1;
     if (i + 1 < rank) gstr[i] = strides_bytes[i];
   }
-  const CUtensorMapDataType dt = dtype == TFB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUtensorMapDataType dt = dtype == TFB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                 : dtype == TFB_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                                    : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUresult r = enc(out, dt, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, bx, es,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);

@@ -42,14 +42,18 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One probe of the barrier.  The thread may be parked by the hardware for up to kSuspendNs while
+// the phase is incomplete (it is woken as soon as the phase completes), so a waiting warp does not
+// burn the issue slots of the warps that share its scheduler.
+constexpr uint32_t kSuspendNs = 200000;
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendNs)
       : "memory");
   return ok != 0;
 }
@@ -96,6 +100,12 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
 // Tiled store smem -> global (clipped at the tensor's edges), tracked by the thread's bulk group.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* smem_src, int c0, int c1) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(m),
+               "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
+               : "memory");
+}
+// Tiled reduction smem -> global: global[tile] += smem[tile] (element type of the tensor map).
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* m, const void* smem_src, int c0, int c1) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(m),
                "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
                : "memory");
 }
@@ -215,7 +225,7 @@ __device__ __forceinline__ bool elect_one() {
 }
 
 // ---- host: tensor maps ------------------------------------------------------------------
-// Encodes a tiled map over a tensor of 16-bit elements with 128-byte swizzle.
+// Encodes a tiled map with 128-byte swizzle over a tensor of fp16 / bf16 / fp32 elements (dtype code).
 // dims[0] is the contiguous dimension; strides_bytes[i] is the byte stride of dims[i+1].
 int encode_tmap_sw128(CUtensorMap* out, const void* base, int dtype, int rank, const uint64_t* dims,
                       const uint64_t* strides_bytes, const uint32_t* box);
