@@ -180,8 +180,23 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
       constexpr uint32_t idesc_s = instr_desc_f16(128, 128, fmt, 0, 0);   // Sᵀ, dPᵀ : both K-major
       constexpr uint32_t idesc_kv = instr_desc_f16(128, HD, fmt, 0, 1);   // dV, dK  : A K-major, B MN-major
       constexpr uint32_t idesc_q = instr_desc_f16(128, HD, fmt, 1, 1);    // dQ      : both MN-major
-      const uint32_t sk = smem_u32(smem + Cfg::OFF_K), sv = smem_u32(smem + Cfg::OFF_V);
-      const uint32_t sp = smem_u32(smem + Cfg::OFF_P), sds = smem_u32(smem + Cfg::OFF_DS);
+      // operand descriptors of every buffer in both roles, built once; each MMA only advances the
+      // start address (K-major: lbo unused, 8-row groups 1024 B apart; MN-major: 64-element chunks
+      // one 16 KB panel apart, 8-row groups 1024 B apart)
+      const uint64_t dk_k = smem_desc_sw128(smem_u32(smem + Cfg::OFF_K), 16, 1024);
+      const uint64_t dk_mn = smem_desc_sw128(smem_u32(smem + Cfg::OFF_K), 16384, 1024);
+      const uint64_t dv_k = smem_desc_sw128(smem_u32(smem + Cfg::OFF_V), 16, 1024);
+      const uint64_t dp_k = smem_desc_sw128(smem_u32(smem + Cfg::OFF_P), 16, 1024);
+      const uint64_t dds_k = smem_desc_sw128(smem_u32(smem + Cfg::OFF_DS), 16, 1024);
+      const uint64_t dds_mn = smem_desc_sw128(smem_u32(smem + Cfg::OFF_DS), 16384, 1024);
+      uint64_t dq_k[QS], dq_mn[QS], ddo_k[QS], ddo_mn[QS];
+#pragma unroll
+      for (int i = 0; i < QS; ++i) {
+        dq_k[i] = smem_desc_sw128(smem_u32(smem + Cfg::OFF_Q + i * Cfg::TILE_BYTES), 16, 1024);
+        dq_mn[i] = smem_desc_sw128(smem_u32(smem + Cfg::OFF_Q + i * Cfg::TILE_BYTES), 16384, 1024);
+        ddo_k[i] = smem_desc_sw128(smem_u32(smem + Cfg::OFF_DO + i * Cfg::TILE_BYTES), 16, 1024);
+        ddo_mn[i] = smem_desc_sw128(smem_u32(smem + Cfg::OFF_DO + i * Cfg::TILE_BYTES), 16384, 1024);
+      }
       const bool prof = (p.debug & 2) != 0;
       PROF_T(tm_start);
       bool ok = mbar_wait(kv_full, 0, 0x2200, abort_flag);
@@ -193,19 +208,16 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
         PROF_T(a1);
         PROF_ADD(7, a0, a1);
         tc_fence_after();
-        const uint32_t sq = smem_u32(smem + Cfg::OFF_Q + st * Cfg::TILE_BYTES);
-        const uint32_t sdo = smem_u32(smem + Cfg::OFF_DO + st * Cfg::TILE_BYTES);
+        const uint64_t q_k = dq_k[st], do_k = ddo_k[st];
 #pragma unroll
         for (int s = 0; s < HD / 16; ++s) {
           const uint32_t off = (s / 4) * 16384 + (s % 4) * 32;
-          tc_mma_ss(tmem_base + Cfg::COL_S, smem_desc_sw128(sk + off, 16, 1024), smem_desc_sw128(sq + off, 16, 1024),
-                    idesc_s, s ? 1u : 0u);
+          tc_mma_ss(tmem_base + Cfg::COL_S, desc_advance(dk_k, off), desc_advance(q_k, off), idesc_s, s ? 1u : 0u);
         }
 #pragma unroll
         for (int s = 0; s < HD / 16; ++s) {
           const uint32_t off = (s / 4) * 16384 + (s % 4) * 32;
-          tc_mma_ss(tmem_base + Cfg::COL_DP, smem_desc_sw128(sv + off, 16, 1024), smem_desc_sw128(sdo + off, 16, 1024),
-                    idesc_s, s ? 1u : 0u);
+          tc_mma_ss(tmem_base + Cfg::COL_DP, desc_advance(dv_k, off), desc_advance(do_k, off), idesc_s, s ? 1u : 0u);
         }
         tc_commit(s_full);
         return true;
@@ -213,8 +225,7 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
       // dV += Pᵀ dO_i, dK += dSᵀ Q_i, dQ_i = dS K
       auto issue_grads = [&](int it) -> bool {
         const int st = it % QS;
-        const uint32_t sq = smem_u32(smem + Cfg::OFF_Q + st * Cfg::TILE_BYTES);
-        const uint32_t sdo = smem_u32(smem + Cfg::OFF_DO + st * Cfg::TILE_BYTES);
+        const uint64_t q_mn = dq_mn[st], do_mn = ddo_mn[st];
         // the dQ columns still hold the previous tile's dQ until the drain warps are done with it
         PROF_T(a0);
         if (it > 0 && !mbar_wait(dq_free, (it - 1) & 1, 0x2400, abort_flag)) return false;
@@ -225,16 +236,16 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
         for (int s = 0; s < FB_T / 16; ++s) {  // contraction over the 128 queries of this tile
           const uint32_t koff = (s / 4) * 16384 + (s % 4) * 32;  // K-major A: 16 queries = 32 B along the row
           const uint32_t moff = s * 2048;                         // MN-major B: 16 query rows of 128 B
-          tc_mma_ss(tmem_base + Cfg::COL_DV, smem_desc_sw128(sp + koff, 16, 1024),
-                    smem_desc_sw128(sdo + moff, 16384, 1024), idesc_kv, (it | s) ? 1u : 0u);
-          tc_mma_ss(tmem_base + Cfg::COL_DK, smem_desc_sw128(sds + koff, 16, 1024),
-                    smem_desc_sw128(sq + moff, 16384, 1024), idesc_kv, (it | s) ? 1u : 0u);
+          tc_mma_ss(tmem_base + Cfg::COL_DV, desc_advance(dp_k, koff), desc_advance(do_mn, moff), idesc_kv,
+                    (it | s) ? 1u : 0u);
+          tc_mma_ss(tmem_base + Cfg::COL_DK, desc_advance(dds_k, koff), desc_advance(q_mn, moff), idesc_kv,
+                    (it | s) ? 1u : 0u);
         }
 #pragma unroll
         for (int s = 0; s < FB_T / 16; ++s) {  // contraction over the 128 keys of this CTA
           const uint32_t moff = s * 2048;      // 16 key rows of 128 B in dSᵀ and in K
-          tc_mma_ss(tmem_base + Cfg::COL_DQ, smem_desc_sw128(sds + moff, 16384, 1024),
-                    smem_desc_sw128(sk + moff, 16384, 1024), idesc_q, s ? 1u : 0u);
+          tc_mma_ss(tmem_base + Cfg::COL_DQ, desc_advance(dds_mn, moff), desc_advance(dk_mn, moff), idesc_q,
+                    s ? 1u : 0u);
         }
         tc_commit(&q_empty[st]);
         tc_commit(dq_full);

@@ -150,6 +150,14 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo
   return d;
 }
 
+// Descriptor of the same layout `byte_off` bytes further on (the start-address field is the low 14
+// bits in 16-byte units; operands live below 256 KB, so the sum never leaves the field).  One 32-bit
+// add per MMA instead of rebuilding the descriptor keeps the single issuing thread off the critical path.
+__device__ __forceinline__ uint64_t desc_advance(uint64_t d, uint32_t byte_off) {
+  const uint32_t lo = (uint32_t)d + (byte_off >> 4);
+  return (d & 0xFFFFFFFF00000000ull) | lo;
+}
+
 // Instruction descriptor for kind::f16 with fp32 accumulation.
 // fmt: 0 = fp16, 1 = bf16.  major: 0 = K-major, 1 = MN-major.
 __host__ __device__ constexpr uint32_t instr_desc_f16(int m, int n, int fmt, int a_mn, int b_mn) {
