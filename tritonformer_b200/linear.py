@@ -22,9 +22,32 @@ def _as_rows(x: torch.Tensor) -> torch.Tensor:
     return x2
 
 
-# When set to a list, every GEMM call appends (flops, start_event, end_event): used by the
-# benchmark to time the kernel family live on the launching stream.
+# When set to a list, every GEMM call appends a description of itself (shape, operand strides,
+# epilogue options): the benchmark replays that list to time the kernel family on its own.
 PROFILE = None
+
+
+def replay(calls, device):
+    """Re-issues the recorded GEMM calls on scratch operands of the same shapes and strides."""
+    cache = {}
+
+    def buf(key, numel, dtype):
+        t = cache.get((key, dtype))
+        if t is None or t.numel() < numel:
+            t = torch.randn(numel, device=device).to(dtype) * 0.05
+            cache[(key, dtype)] = t
+        return t
+
+    for c in calls:
+        m, n, k, dt = c["m"], c["n"], c["k"], c["dtype"]
+        a = buf("a", m * k, dt)
+        b = buf("b", k * n, dt)
+        out = buf("c", m * n, dt)[: m * n].view(m, n)
+        addend = out if c["accumulate"] else (buf("x", m * n, dt)[: m * n].view(m, n) if c["addend"] else None)
+        mask = buf("m", m * n, dt)[: m * n].view(m, n) if c["mask"] else None
+        bias = buf("bias", n, dt)[:n] if c["bias"] else None
+        gemm(a, c["a"][0], c["a"][1], b, c["b"][0], c["b"][1], m, n, k, bias=bias, relu=c["relu"], out=out,
+             addend=addend, mask=mask)
 
 
 # When True, a weight gradient is added straight into an existing, contiguous `.grad` by the GEMM
@@ -57,9 +80,6 @@ def gemm(a, a_sm, a_sk, b, b_sk, b_sn, m, n, k, bias=None, relu=False, out=None,
         addend = out
     path = ctypes.c_int(0)
     ws = _splitk_workspace(a.device, m * n * 4) if (m * n <= (8 << 20) and k >= 2048) else None
-    if PROFILE is not None:
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
     _lib.check(_lib.lib.tfb_gemm_fused(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), bias.data_ptr() if bias is not None else None,
         addend.data_ptr() if addend is not None else None, addend.stride(0) if addend is not None else 0,
@@ -68,8 +88,9 @@ def gemm(a, a_sm, a_sk, b, b_sk, b_sn, m, n, k, bias=None, relu=False, out=None,
         ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
         _lib.stream_ptr(a.device), ctypes.byref(path)))
     if PROFILE is not None:
-        e1.record()
-        PROFILE.append((2.0 * m * n * k, e0, e1, path.value, (m, n, k)))
+        PROFILE.append({"m": m, "n": n, "k": k, "a": (a_sm, a_sk), "b": (b_sk, b_sn), "bias": bias is not None,
+                        "relu": bool(relu), "addend": addend is not None, "accumulate": addend is out,
+                        "mask": mask is not None, "dtype": a.dtype, "path": path.value})
     return out
 
 
