@@ -233,6 +233,118 @@ __global__ void __launch_bounds__(MAXT) ln_bwd_kernel(
   }
 }
 
+// Backward for rows of at most 1024 elements: one warp per row, no block-wide barrier in the row
+// loop.  A lane owns the 16-byte vectors lane, lane+32, ... of the row (like the forward kernel), so
+// the two row reductions are warp shuffles, and it keeps the dalpha / dbeta sums of its columns in
+// registers across all the rows its warp visits.  The next row's vectors are loaded before the
+// current row is reduced.  At the end the warps of a CTA fold their sums in shared memory and the CTA
+// writes one partial row.
+template <typename T, int NV>
+__global__ void __launch_bounds__(256, 1) ln_bwd_warp_kernel(
+    const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ alpha,
+    const float* __restrict__ mean, const float* __restrict__ rstd, T* __restrict__ dx,
+    float* __restrict__ partials, int64_t rows, int d, int64_t dy_ld, int64_t x_ld, int64_t dx_ld,
+    const T* __restrict__ dres, int64_t dres_ld) {
+  extern __shared__ float fold[];  // [2][d]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nvec = d >> 3;
+  for (int c = threadIdx.x; c < 2 * d; c += blockDim.x) fold[c] = 0.f;
+  __syncthreads();
+
+  float a[NV][8], acc_a[NV][8], acc_b[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = i * 32 + lane;
+    if (c < nvec) unpack8<T>(__ldg(reinterpret_cast<const uint4*>(alpha) + c), a[i]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc_a[i][j] = acc_b[i][j] = 0.f;
+  }
+  const float inv_d = 1.f / (float)d;
+  const int64_t stride = (int64_t)gridDim.x * (blockDim.x >> 5);
+  int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
+
+  uint4 cx[NV], cg[NV], cr[NV], nx[NV], ng[NV], nr[NV];
+  auto fetch = [&](int64_t r, uint4 (&vx)[NV], uint4 (&vg)[NV], uint4 (&vr)[NV]) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = i * 32 + lane;
+      if (c < nvec) {
+        vx[i] = ld_stream16(reinterpret_cast<const uint4*>(x + r * x_ld) + c);
+        vg[i] = ld_stream16(reinterpret_cast<const uint4*>(dy + r * dy_ld) + c);
+        if (dres) vr[i] = ld_stream16(reinterpret_cast<const uint4*>(dres + r * dres_ld) + c);
+      }
+    }
+  };
+  if (row < rows) fetch(row, cx, cg, cr);
+  for (; row < rows; row += stride) {
+    const bool more = row + stride < rows;
+    if (more) fetch(row + stride, nx, ng, nr);
+    const float mu = __ldg(mean + row), rs = __ldg(rstd + row);
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      if (i * 32 + lane < nvec) {
+        float xv[8], dv[8];
+        unpack8<T>(cx[i], xv);
+        unpack8<T>(cg[i], dv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float h = (xv[j] - mu) * rs;
+          const float gg = dv[j] * a[i][j];
+          acc_a[i][j] += dv[j] * h;
+          acc_b[i][j] += dv[j];
+          s1 += gg * h;
+          s2 += gg;
+        }
+      }
+    }
+    s1 = warp_sum(s1) * inv_d;
+    s2 = warp_sum(s2) * inv_d;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = i * 32 + lane;
+      if (c < nvec) {
+        // the normalised value and the scaled gradient are recomputed from the packed vectors rather
+        // than kept across the reduction: two multiplies each instead of 16 live registers per vector
+        float xv[8], dv[8], o[8];
+        unpack8<T>(cx[i], xv);
+        unpack8<T>(cg[i], dv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rs * (dv[j] * a[i][j] - (xv[j] - mu) * rs * s1 - s2);
+        if (dres) {
+          float e[8];
+          unpack8<T>(cr[i], e);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += e[j];
+        }
+        st_stream16(reinterpret_cast<uint4*>(dx + row * dx_ld) + c, pack8<T>(o));
+      }
+    }
+    if (more) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        cx[i] = nx[i];
+        cg[i] = ng[i];
+        cr[i] = nr[i];
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = i * 32 + lane;
+    if (c < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        atomicAdd(&fold[c * 8 + j], acc_a[i][j]);
+        atomicAdd(&fold[d + c * 8 + j], acc_b[i][j]);
+      }
+    }
+  }
+  __syncthreads();
+  float* pa = partials + (int64_t)blockIdx.x * 2 * d;
+  for (int c = threadIdx.x; c < 2 * d; c += blockDim.x) pa[c] = fold[c];
+}
+
 // out0[c] (c < split) / out1[c - split] = sum over n rows of partials[r, c]; ncols total.
 template <typename T>
 __global__ void __launch_bounds__(256) finalize_partials_kernel(
@@ -276,7 +388,15 @@ static int ln_bwd_launch(const void* dy, const void* x, const void* alpha, const
   ln_bwd_kernel<T, V, MT><<<(unsigned)n_partials, threads, 0, st>>>(                          \
       (const T*)dy, (const T*)x, (const T*)alpha, mean, rstd, (T*)dx, partials, rows, d, dy_ld, \
       x_ld, dx_ld, (const T*)dres, dres_ld)
-  if (vec && threads <= 256) TFB_LN_BWD(true, 256);
+  if (vec && d <= 1024 && aligned16(alpha)) {
+    const size_t sm = (size_t)2 * d * sizeof(float);
+    const T *gp = (const T*)dy, *xp = (const T*)x, *ap = (const T*)alpha, *rp = (const T*)dres;
+    T* op = (T*)dx;
+    const unsigned grid = (unsigned)n_partials;
+    if (d <= 256) ln_bwd_warp_kernel<T, 1><<<grid, 256, sm, st>>>(gp, xp, ap, mean, rstd, op, partials, rows, d, dy_ld, x_ld, dx_ld, rp, dres_ld);
+    else if (d <= 512) ln_bwd_warp_kernel<T, 2><<<grid, 256, sm, st>>>(gp, xp, ap, mean, rstd, op, partials, rows, d, dy_ld, x_ld, dx_ld, rp, dres_ld);
+    else ln_bwd_warp_kernel<T, 4><<<grid, 256, sm, st>>>(gp, xp, ap, mean, rstd, op, partials, rows, d, dy_ld, x_ld, dx_ld, rp, dres_ld);
+  } else if (vec && threads <= 256) TFB_LN_BWD(true, 256);
   else if (vec) TFB_LN_BWD(true, 1024);
   else if (threads <= 256) TFB_LN_BWD(false, 256);
   else TFB_LN_BWD(false, 1024);
@@ -321,8 +441,8 @@ extern "C" int tfb_layernorm_fwd(const void* x, const void* alpha, const void* b
 
 extern "C" int64_t tfb_layernorm_bwd_partials(int64_t rows, int64_t d) {
   (void)d;
-  int64_t n = ceil_div(rows, LN_RB);
-  const int64_t cap = 148 * 4;
+  int64_t n = ceil_div(rows, 16);
+  const int64_t cap = 148 * 2;  // two CTAs per SM
   if (n > cap) n = cap;
   return n < 1 ? 1 : n;
 }
@@ -413,7 +533,7 @@ extern "C" int tfb_layernorm_bwd_static(const void* dy, const void* x, const voi
   float* scratch = nullptr;
   int rc = static_scratch_for_current_device(&scratch);
   if (rc) return rc;
-  int64_t n = ceil_div(rows, LN_RB);
+  int64_t n = ceil_div(rows, 16);
   if (n > kStaticRows) n = kStaticRows;
   // Every one of the n partial rows is rewritten in full by the first kernel before the second
   // reads it, so nothing in the array has to be cleared between calls.
