@@ -182,7 +182,7 @@ def build_model(cfg, dtype, device, seed=1234):
 def run_b200_arm(args):
     import tritonformer_b200._lib as L
     from tritonformer_b200 import linear as tlinear
-    from tritonformer_b200.dp import GradBuckets, broadcast_parameters
+    from tritonformer_b200.dp import GradBuckets, OverlappedReducer, broadcast_parameters
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -191,7 +191,9 @@ def run_b200_arm(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        from datetime import timedelta
+        # short timeout: a rank that is missing from a collective ends the run instead of stalling it
+        dist.init_process_group("nccl", device_id=dev, timeout=timedelta(seconds=90))
 
     cfg, B, T, dtype = make_config(args.config)
     model = build_model(cfg, dtype, dev)
@@ -207,10 +209,16 @@ def run_b200_arm(args):
     static_ids.copy_(host_tokens[0])
     static_loss = torch.zeros((), device=dev, dtype=torch.float32)
 
+    # N > 1: each gradient bucket is all-reduced from a hook as soon as backward has produced it, on a
+    # side stream, so the collectives overlap the rest of backward (and are captured with the step)
+    reducer = OverlappedReducer(buckets, list(model.layer_list)) if (world > 1 and not args.no_overlap) else None
+
     def step(ids):
         with torch.autocast("cuda", dtype=dtype):
             _, loss = model(ids, ids)
         (loss * loss_scale).backward()
+        if reducer is not None:
+            reducer.finish()
         return loss.detach()
 
     # eager warm-up (also fills every per-shape cache before graph capture)
@@ -241,7 +249,8 @@ def run_b200_arm(args):
             graph.replay()
         else:
             static_loss.copy_(step(static_ids))
-        buckets.all_reduce_mean()
+        if reducer is None:
+            buckets.all_reduce_mean()
 
     def barrier():
         if world > 1:
@@ -289,7 +298,11 @@ def run_b200_arm(args):
         peaks = measured_peaks()
         recs = []
         tlinear.PROFILE = recs
+        if reducer is not None:
+            reducer.enabled = False  # this step runs on rank 0 only: no collectives
         step(static_ids)
+        if reducer is not None:
+            reducer.enabled = True
         tlinear.PROFILE = None
         torch.cuda.synchronize()
         gflop = sum(2.0 * r["m"] * r["n"] * r["k"] for r in recs)
@@ -320,6 +333,8 @@ def run_b200_arm(args):
                                    f"H{cfg.num_attention_heads} ffn{cfg.ffn_dim} V{cfg.vocab_size} ctx{T} batch{B}/GPU",
                        "global_batch": world * B, "seq_len": T, "parallelism": f"dp{world}",
                        "cuda_graph": graph is not None, "loss_scale": loss_scale,
+                       "allreduce": ("overlapped with backward" if reducer is not None else "after backward")
+                       if world > 1 else None,
                        "l2": "working set per step (>= 0.8 GB of weights plus activations) exceeds the 126 MB L2"},
             "tflops_per_gpu": tflops_gpu,
             "frac_of_measured_bf16_peak": tflops_gpu / measured_peaks()["tflops"],
@@ -338,7 +353,13 @@ def run_b200_arm(args):
         }
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # Every rank waits for rank 0's extra measurements, then the processes leave without tearing the
+        # communicator down: the captured graph still references NCCL kernels, and destroying the
+        # process group underneath it has been seen to block at exit.
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 # ------------------------------------------------------------------ per-kernel micro-benchmarks
@@ -490,6 +511,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-overlap", action="store_true",
+                    help="N > 1: all-reduce the gradient buckets after the step instead of during backward")
     ap.add_argument("--kernel", default=None,
                     choices=["all", "gemm", "attn", "layernorm", "crossentropy", "softmax", "relu"],
                     help="run the isolated-kernel micro-benchmarks instead of the model step")

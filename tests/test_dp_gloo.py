@@ -7,7 +7,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from tritonformer_b200.dp import GradBuckets, broadcast_parameters, shard_batch
+from tritonformer_b200.dp import GradBuckets, OverlappedReducer, broadcast_parameters, shard_batch
 
 
 def _free_port():
@@ -26,11 +26,22 @@ def _worker(rank, world, port, mode, out):
         torch.manual_seed(rank)  # replicas start different on purpose
         model = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.ReLU(), torch.nn.Linear(32, 4))
         broadcast_parameters(model, 0)
-        buckets = GradBuckets(model.parameters(), bucket_bytes=1024)
+        buckets = GradBuckets(model.parameters(), bucket_bytes=600 if mode == "overlap" else 1024)
         assert len(buckets.buckets) >= 2
         gen = torch.Generator().manual_seed(7)
         data = torch.randn((8, 16), generator=gen)
         x = shard_batch(data, rank, world)
+        reducer = None
+        if mode == "overlap":  # buckets are reduced from hooks while backward is still running
+            reducer = OverlappedReducer(buckets, [model[0], model[2]])
+            assert reducer.ready_at[0] >= 1 and min(reducer.ready_at) == 0
+            model(x).square().mean().backward()
+            assert any(reducer.launched), "no bucket was reduced during backward"
+            reducer.finish()
+            buckets.check_views()
+            flat = torch.cat([p.grad.reshape(-1) for p in model.parameters()])
+            out.put((rank, "ok", flat))
+            return
         for _ in range(2):  # gradients accumulate in place across steps
             model(x).square().mean().backward()
         buckets.check_views()
@@ -40,7 +51,8 @@ def _worker(rank, world, port, mode, out):
         flat = torch.cat([p.grad.reshape(-1) for p in model.parameters()])
         out.put((rank, "ok", flat))
     except Exception as e:  # noqa: BLE001
-        out.put((rank, "error", repr(e)))
+        import traceback
+        out.put((rank, "error", repr(e) + "\n" + traceback.format_exc()))
     finally:
         try:
             dist.destroy_process_group()
@@ -73,6 +85,20 @@ def test_bucketed_allreduce_matches_single_process():
     for shard in (data[:4], data[4:]):
         for _ in range(2):
             (model(shard).square().mean() / 2).backward()
+    want = torch.cat([p.grad.reshape(-1) for p in model.parameters()])
+    assert torch.allclose(res[0][1], want, atol=1e-6)
+
+
+def test_overlapped_reduction_gives_the_same_mean():
+    res = _run("overlap")
+    assert res[0][0] == "ok" and res[1][0] == "ok", res
+    assert torch.allclose(res[0][1], res[1][1])
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.ReLU(), torch.nn.Linear(32, 4))
+    gen = torch.Generator().manual_seed(7)
+    data = torch.randn((8, 16), generator=gen)
+    for shard in (data[:4], data[4:]):
+        (model(shard).square().mean() / 2).backward()
     want = torch.cat([p.grad.reshape(-1) for p in model.parameters()])
     assert torch.allclose(res[0][1], want, atol=1e-6)
 

@@ -17,6 +17,7 @@ class GradBuckets:
     def __init__(self, params, bucket_bytes: int = 256 << 20):
         self.params = [p for p in params if p.requires_grad]
         self.buckets: List[torch.Tensor] = []
+        self.members: List[list] = []  # parameters of each bucket
         self._views = []
         groups, cur, cur_bytes = [], [], 0
         for p in reversed(self.params):  # backward produces gradients roughly in reverse order
@@ -38,6 +39,7 @@ class GradBuckets:
                 self._views.append((p, view))
                 off += -(-p.numel() // 8) * 8
             self.buckets.append(flat)
+            self.members.append(list(group))
 
     def zero(self):
         for b in self.buckets:
@@ -49,22 +51,102 @@ class GradBuckets:
             if p.grad is None or p.grad.data_ptr() != view.data_ptr():
                 raise RuntimeError("a parameter gradient left its bucket (set_to_none or replaced)")
 
-    def all_reduce_mean(self, group=None, async_op: bool = False):
+    @staticmethod
+    def reduce_bucket(b, group=None):
+        """Mean of one flat bucket over the ranks of `group` (NCCL averages in the collective)."""
+        if dist.get_backend(group) == "nccl":
+            dist.all_reduce(b, op=dist.ReduceOp.AVG, group=group)
+        else:
+            dist.all_reduce(b, op=dist.ReduceOp.SUM, group=group)
+            b.div_(dist.get_world_size(group))
+
+    def all_reduce_mean(self, group=None):
         """Average every bucket over the ranks of `group`."""
         if not dist.is_initialized() or dist.get_world_size(group) == 1:
-            return []
-        world = dist.get_world_size(group)
-        avg = dist.get_backend(group) == "nccl"
-        works = []
+            return
         for b in self.buckets:
-            if avg:
-                works.append(dist.all_reduce(b, op=dist.ReduceOp.AVG, group=group, async_op=async_op))
-            else:
-                w = dist.all_reduce(b, op=dist.ReduceOp.SUM, group=group, async_op=async_op)
-                if async_op:
-                    w.wait()
-                b.div_(world)
-        return works if async_op else []
+            self.reduce_bucket(b, group)
+
+
+class OverlappedReducer:
+    """Starts each bucket's all-reduce as soon as the backward pass has produced all of its gradients.
+
+    `stages` are the modules of the model in forward order (the transformer layers).  A hook on the
+    input of stage i fires when the gradient with respect to that input exists, i.e. when every kernel
+    that writes a gradient of stages i, i+1, ... has been enqueued; every bucket made only of such
+    parameters is then reduced on a side stream (after an event on the compute stream), overlapping
+    the rest of the backward pass.  `finish()` reduces what is left (the embeddings) and makes the
+    compute stream wait for the collectives.  On CUDA the whole pattern is stream-ordered and can be
+    captured in a CUDA graph together with the step.
+    """
+
+    def __init__(self, buckets: GradBuckets, stages, group=None):
+        self.buckets, self.group = buckets, group
+        stage_of = {}
+        for i, m in enumerate(stages):
+            for p in m.parameters():
+                stage_of[id(p)] = i
+        # a bucket is ready once the backward pass has gone below its earliest stage; parameters that
+        # belong to no stage and sit before the stages (embeddings) make their bucket wait for finish()
+        n = len(stages)
+        order = {id(p): j for j, p in enumerate(buckets.params)}        # registration (forward) order
+        first_stage_param = min((order[id(p)] for m in stages for p in m.parameters() if id(p) in order), default=0)
+        self.ready_at = []
+        for members in buckets.members:
+            at = n
+            for p in members:
+                if id(p) in stage_of:
+                    at = min(at, stage_of[id(p)])
+                elif order[id(p)] < first_stage_param:
+                    at = -1            # used before the stages (embeddings): gradient arrives last
+                # else: used after the stages (final norm, head): gradient arrives first, no constraint
+            self.ready_at.append(at)
+        self.launched = [False] * len(buckets.buckets)
+        self.enabled = True  # set False around a step that only some ranks run (no collectives then)
+        self.side = torch.cuda.Stream() if buckets.buckets and buckets.buckets[0].is_cuda else None
+        self._handles = [m.register_forward_pre_hook(self._make_pre_hook(i)) for i, m in enumerate(stages)]
+
+    def _make_pre_hook(self, i):
+        def pre_hook(module, args):
+            x = args[0] if args else None
+            # A hook on a non-leaf input runs just before the node that produced it is executed in
+            # backward; by then the gradient accumulators of every later parameter have run (they have
+            # the highest priority in the autograd queue).  A leaf input gives no such ordering against
+            # this stage's own parameters, so its stage is left to finish().
+            if isinstance(x, torch.Tensor) and x.requires_grad and not x.is_leaf:
+                x.register_hook(lambda g: self._stage_done(i))
+        return pre_hook
+
+    def _reduce(self, k):
+        b = self.buckets.buckets[k]
+        self.launched[k] = True
+        if self.side is not None:
+            self.side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.side):
+                self.buckets.reduce_bucket(b, self.group)
+        else:
+            self.buckets.reduce_bucket(b, self.group)
+
+    def _stage_done(self, i):
+        if not self.enabled or not dist.is_initialized() or dist.get_world_size(self.group) == 1:
+            return
+        for k, at in enumerate(self.ready_at):
+            if not self.launched[k] and at >= i:
+                self._reduce(k)
+
+    def finish(self):
+        """Call after backward(): reduces the remaining buckets and joins the side stream."""
+        if self.enabled and dist.is_initialized() and dist.get_world_size(self.group) > 1:
+            for k in range(len(self.launched)):
+                if not self.launched[k]:
+                    self._reduce(k)
+            if self.side is not None:
+                torch.cuda.current_stream().wait_stream(self.side)
+        self.launched = [False] * len(self.launched)
+
+    def remove(self):
+        for h in self._handles:
+            h.remove()
 
 
 def broadcast_parameters(module: torch.nn.Module, src: int = 0, group=None):
