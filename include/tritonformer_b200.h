@@ -158,8 +158,10 @@ int tfb_gemm(const void* a, const void* b, void* c, const void* bias,
  *   C[m,n] = mask( act( sum_k A(m,k) B(k,n) + bias[n] ) + addend[m,n] )
  * addend (may be NULL; may be C itself to accumulate) has leading dimension ld_addend; mask (may be
  * NULL) zeroes the result wherever mask[m,n] <= 0 (pass a saved ReLU output to get the ReLU
- * gradient).  workspace (may be NULL) is fp32 scratch of at least M*N*4 bytes: when given and the
- * output has too few tiles to fill the GPU, the contraction is split in two (deterministic).   */
+ * gradient).  workspace (may be NULL) is fp32 scratch of at least M*N*4 bytes that is ZERO-FILLED on
+ * entry; it is returned zero-filled, so one buffer cleared once serves every call on a stream.  When
+ * given and the output has too few tiles to fill the GPU, the contraction is split in two
+ * (deterministic).                                                                           */
 int tfb_gemm_fused(const void* a, const void* b, void* c, const void* bias,
                    const void* addend, int64_t ld_addend, const void* mask, int64_t ld_mask,
                    int64_t M, int64_t N, int64_t K,

@@ -318,7 +318,8 @@ __global__ void __launch_bounds__(TB_THREADS, 1) gemm_tc05_kernel(const __grid_c
   }
 }
 
-// Split-K epilogue: C = mask(act(ws + bias) + addend), rounded once; 8 columns per thread.
+// Split-K epilogue: C = mask(act(ws + bias) + addend), rounded once; 8 columns per thread.  The
+// workspace is zero on entry to the GEMM (caller's contract) and is returned zero-filled.
 template <typename T>
 __global__ void __launch_bounds__(256) splitk_finish_kernel(const GemmParams p) {
   const int vpr = p.N / 8;
@@ -331,8 +332,12 @@ __global__ void __launch_bounds__(256) splitk_finish_kernel(const GemmParams p) 
        idx += (int64_t)gridDim.x * blockDim.x) {
     const int64_t row = idx / vpr;
     const int col = (int)(idx % vpr) * 8;
-    const float4 x = *reinterpret_cast<const float4*>(p.ws + row * p.N + col);
-    const float4 y = *reinterpret_cast<const float4*>(p.ws + row * p.N + col + 4);
+    float4* w4 = reinterpret_cast<float4*>(p.ws + row * p.N + col);
+    const float4 x = w4[0];
+    const float4 y = w4[1];
+    // leave the workspace zero-filled for the next split-K product (saves a memset per call)
+    w4[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+    w4[1] = make_float4(0.f, 0.f, 0.f, 0.f);
     float f[8] = {x.x, x.y, x.z, x.w, y.x, y.y, y.z, y.w};
     if (bias) {
       float b[8];
@@ -423,10 +428,6 @@ static int launch_tc05(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
   }
   const int units = p.tiles_m * p.tiles_n * p.splits;
   const int grid = units < sm_count() ? units : sm_count();
-  if (p.splits > 1) {
-    cudaError_t e = cudaMemsetAsync(p.ws, 0, (size_t)p.M * p.N * sizeof(float), st);
-    if (e != cudaSuccess) return fail(TFB_ERR_LAUNCH, "gemm_tc05: workspace memset: %s", cudaGetErrorString(e));
-  }
   kern<<<grid, TB_THREADS, Cfg::SMEM_BYTES, st>>>(tmA, tmB, tmC, tmX, p);
   int rc = launched("gemm_tc05");
   if (rc || p.splits == 1) return rc;

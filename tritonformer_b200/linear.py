@@ -61,10 +61,12 @@ _workspaces = {}
 
 
 def _splitk_workspace(device, nbytes):
-    """Per-device fp32 scratch for the split-K path of small-output GEMMs (grown on demand)."""
+    """Per-device fp32 scratch for the split-K path of small-output GEMMs (grown on demand).
+
+    The library expects it zero-filled and hands it back zero-filled, so it is cleared only here."""
     ws = _workspaces.get(device)
     if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(max(nbytes, 32 << 20), device=device, dtype=torch.uint8)
+        ws = torch.zeros(max(nbytes, 32 << 20), device=device, dtype=torch.uint8)
         _workspaces[device] = ws
     return ws
 
