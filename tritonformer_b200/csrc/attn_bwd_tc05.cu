@@ -554,14 +554,11 @@ static int bwd_tc05_launch(const AttnArgs& a, int dtype, cudaStream_t st) {
   p.sdv_b = a.sdv.b; p.sdv_h = a.sdv.h; p.sdv_t = a.sdv.t;
   p.H = a.H; p.T = a.T; p.scale = a.scale; p.bias_mode = a.bias_mode; p.slopes = a.slopes;
   p.debug = g_attn_debug.load();
-  static bool attr_set = false;
-  if (!attr_set) {
-    e = cudaFuncSetAttribute(attn_bwd_tc05_kernel<T, HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(attn_bwd_tc05_kernel<T, HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
-    if (e != cudaSuccess) return fail(TFB_ERR_LAUNCH, "attention_bwd(tcgen05): smem attribute: %s", cudaGetErrorString(e));
-    attr_set = true;
-  }
+  static std::atomic<uint64_t> done_plain{0}, done_bias{0};
+  if ((rc = ensure_dynamic_smem(attn_bwd_tc05_kernel<T, HD, false>, Cfg::SMEM_BYTES, done_plain, "attention_bwd(tcgen05)")))
+    return rc;
+  if ((rc = ensure_dynamic_smem(attn_bwd_tc05_kernel<T, HD, true>, Cfg::SMEM_BYTES, done_bias, "attention_bwd(tcgen05)")))
+    return rc;
   dim3 grid(a.T / FB_T, a.B * a.H);
   if (a.bias_mode) attn_bwd_tc05_kernel<T, HD, true><<<grid, FB_THREADS, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, tdo, tdq, p);
   else attn_bwd_tc05_kernel<T, HD, false><<<grid, FB_THREADS, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, tdo, tdq, p);

@@ -371,16 +371,11 @@ static int fwd2_launch(const AttnArgs& a, int dtype, cudaStream_t st) {
   F2Params p;
   p.out = a.out; p.lse = a.lse; p.so_b = a.so.b; p.so_h = a.so.h; p.so_t = a.so.t;
   p.H = a.H; p.T = a.T; p.scale = a.scale; p.bias_mode = a.bias_mode; p.slopes = a.slopes;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd2_tc05_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         F2_SMEM_BYTES);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(attn_fwd2_tc05_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               F2_SMEM_BYTES);
-    if (e != cudaSuccess) return fail(TFB_ERR_LAUNCH, "attention_fwd(tcgen05): smem attribute: %s", cudaGetErrorString(e));
-    attr_set = true;
-  }
+  static std::atomic<uint64_t> done_plain{0}, done_bias{0};
+  if ((rc = ensure_dynamic_smem(attn_fwd2_tc05_kernel<T, false>, F2_SMEM_BYTES, done_plain, "attention_fwd(tcgen05)")))
+    return rc;
+  if ((rc = ensure_dynamic_smem(attn_fwd2_tc05_kernel<T, true>, F2_SMEM_BYTES, done_bias, "attention_fwd(tcgen05)")))
+    return rc;
   const int nq = a.T / F2_TILE;
   dim3 grid((nq + 1) / 2, a.B * a.H);
   if (a.bias_mode) attn_fwd2_tc05_kernel<T, true><<<grid, F2_THREADS, F2_SMEM_BYTES, st>>>(tq, tk, tv, p);

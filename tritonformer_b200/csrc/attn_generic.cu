@@ -518,24 +518,16 @@ static int bwd_launch(const AttnArgs& a, cudaStream_t st) {
   {
     auto kern = attn_bwd_kv_kernel<T, HD>;
     const int bytes = (int)sizeof(BwdKvSmem<T, HD>);
-    static bool attr_set = false;  // benign race: the call is idempotent
-    if (!attr_set) {
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-      if (e != cudaSuccess) return fail(TFB_ERR_LAUNCH, "attention_bwd: smem attribute: %s", cudaGetErrorString(e));
-      attr_set = true;
-    }
+    static std::atomic<uint64_t> attr_done{0};
+    if ((rc = ensure_dynamic_smem(kern, bytes, attr_done, "attention_bwd"))) return rc;
     kern<<<grid, AT_THREADS, bytes, st>>>(a);
     if ((rc = launched("attention_bwd_kv(generic)"))) return rc;
   }
   {
     auto kern = attn_bwd_q_kernel<T, HD>;
     const int bytes = (int)sizeof(BwdQSmem<T, HD>);
-    static bool attr_set = false;
-    if (!attr_set) {
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-      if (e != cudaSuccess) return fail(TFB_ERR_LAUNCH, "attention_bwd: smem attribute: %s", cudaGetErrorString(e));
-      attr_set = true;
-    }
+    static std::atomic<uint64_t> attr_done{0};
+    if ((rc = ensure_dynamic_smem(kern, bytes, attr_done, "attention_bwd"))) return rc;
     kern<<<grid, AT_THREADS, bytes, st>>>(a);
     if ((rc = launched("attention_bwd_q(generic)"))) return rc;
   }

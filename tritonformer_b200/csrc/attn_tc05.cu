@@ -321,12 +321,8 @@ static int fwd_tc05_launch(const AttnArgs& a, int dtype, cudaStream_t st) {
   p.out = a.out; p.lse = a.lse; p.so_b = a.so.b; p.so_h = a.so.h; p.so_t = a.so.t;
   p.H = a.H; p.T = a.T; p.scale = a.scale; p.bias_mode = a.bias_mode; p.slopes = a.slopes;
   auto kern = attn_fwd_tc05_kernel<T, HD>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
-    if (e != cudaSuccess) return fail(TFB_ERR_LAUNCH, "attention_fwd(tcgen05): smem attribute: %s", cudaGetErrorString(e));
-    attr_set = true;
-  }
+  static std::atomic<uint64_t> attr_done{0};
+  if ((rc = ensure_dynamic_smem(kern, Cfg::SMEM_BYTES, attr_done, "attention_fwd(tcgen05)"))) return rc;
   dim3 grid(a.T / FA_M, a.B * a.H);
   kern<<<grid, FA_THREADS, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, p);
   return launched("attention_fwd(tcgen05)");

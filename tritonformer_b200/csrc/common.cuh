@@ -32,6 +32,20 @@ inline int launched(const char* what) {
   return TFB_OK;
 }
 
+// Raises a kernel's dynamic shared-memory limit once per device (the attribute is per device; `done`
+// holds one bit per device ordinal).  Idempotent, so a race between two threads is harmless.
+template <typename F>
+inline int ensure_dynamic_smem(F func, int bytes, std::atomic<uint64_t>& done, const char* what) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  const uint64_t bit = 1ull << dev;
+  if (done.load(std::memory_order_acquire) & bit) return TFB_OK;
+  cudaError_t e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) return fail(TFB_ERR_LAUNCH, "%s: shared-memory attribute: %s", what, cudaGetErrorString(e));
+  done.fetch_or(bit, std::memory_order_release);
+  return TFB_OK;
+}
+
 #define TFB_REQUIRE(cond, ...)                         \
   do {                                                 \
     if (!(cond)) return ::tfb::fail(TFB_ERR_ARG, __VA_ARGS__); \

@@ -420,12 +420,8 @@ static int launch_tc05(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
                        const GemmParams& p, cudaStream_t st) {
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_tc05_kernel<T, BN, A_MN, B_MN>;
-  static bool attr_set = false;  // benign race: the call is idempotent
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
-    if (e != cudaSuccess) return fail(TFB_ERR_LAUNCH, "gemm_tc05: smem attribute: %s", cudaGetErrorString(e));
-    attr_set = true;
-  }
+  static std::atomic<uint64_t> attr_done{0};
+  if (int rc0 = ensure_dynamic_smem(kern, Cfg::SMEM_BYTES, attr_done, "gemm_tc05")) return rc0;
   const int units = p.tiles_m * p.tiles_n * p.splits;
   const int grid = units < sm_count() ? units : sm_count();
   kern<<<grid, TB_THREADS, Cfg::SMEM_BYTES, st>>>(tmA, tmB, tmC, tmX, p);
