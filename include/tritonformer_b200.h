@@ -47,7 +47,9 @@ int64_t tfb_launch_count(void);
 int tfb_device_status(int reset);
 /* Test switches.  key 0: value 1 sends every GEMM to the generic-stride kernel.
  *                key 1: value 1 sends every attention call to the mma.sync kernels.
- *                key 2: bit 0 skips the dQ accumulation, bit 1 turns the timing counters on. */
+ *                key 2: bit 0 skips the dQ accumulation, bit 1 turns the timing counters on.
+ *                key 3: value 1 launches every kernel fully serialised (no programmatic
+ *                       dependent launch: a kernel's set-up no longer overlaps its predecessor's tail). */
 void tfb_debug_set(int key, int value);
 /* Timing counters of the attention backward kernel (16 cycle sums, filled while tfb_debug_set(2, 2)
  * is in effect); copies and clears them.  Synchronises the device.                        */
@@ -158,10 +160,13 @@ int tfb_gemm(const void* a, const void* b, void* c, const void* bias,
  *   C[m,n] = mask( act( sum_k A(m,k) B(k,n) + bias[n] ) + addend[m,n] )
  * addend (may be NULL; may be C itself to accumulate) has leading dimension ld_addend; mask (may be
  * NULL) zeroes the result wherever mask[m,n] <= 0 (pass a saved ReLU output to get the ReLU
- * gradient).  workspace (may be NULL) is fp32 scratch of at least M*N*4 bytes that is ZERO-FILLED on
- * entry; it is returned zero-filled, so one buffer cleared once serves every call on a stream.  When
- * given and the output has too few tiles to fill the GPU, the contraction is split in two
- * (deterministic).                                                                           */
+ * gradient).  workspace (may be NULL) is scratch of at least tfb_gemm_workspace_bytes() bytes, 16-byte
+ * aligned, whose first 8192 bytes are ZERO on entry; they are zero again when the kernel has finished,
+ * so one buffer cleared once serves every call on a stream (calls that share a workspace must be
+ * stream-ordered).  With a workspace, when the output tiles do not fill whole waves of SMs, the
+ * contraction of some tiles is shared between SMs ("stream-K": fp32 partial tiles, summed in a fixed
+ * order, so the result does not depend on timing).                                                 */
+int64_t tfb_gemm_workspace_bytes(void);
 int tfb_gemm_fused(const void* a, const void* b, void* c, const void* bias,
                    const void* addend, int64_t ld_addend, const void* mask, int64_t ld_mask,
                    int64_t M, int64_t N, int64_t K,

@@ -108,23 +108,53 @@ def test_mlp_residual(bias):
         assert norm_rel(b1.grad, b1r.grad) < 1e-3 and norm_rel(b2.grad, b2r.grad) < 1e-3
 
 
-@pytest.mark.parametrize("shape", [(1024, 1024, 8192), (256, 1024, 4096), (1000, 264, 2048)])
-def test_split_k_gemm_matches_fp32_and_is_deterministic(shape):
-    """Small outputs with a long contraction (the weight-gradient shape) take the two-way split-K path."""
-    from tritonformer_b200 import linear as lin
+STREAM_K_SHAPES = [
+    (1024, 1024, 8192),    # 32 tiles: every tile shared by four or five SMs
+    (256, 1024, 4096),     # 8 tiles
+    (1000, 264, 2048),     # ragged M and N, 16 tiles
+    (8192, 1024, 1024),    # 256 tiles on 148 SMs: one wave plus a remainder, each tile on at most two SMs
+    (4100, 1544, 704),     # 231 tiles, ragged in M, N and K
+    (128, 136, 1024),      # two tiles, few k-blocks
+    (128, 64, 64),         # a single tile and k-block: nothing to share
+]
+
+
+@pytest.mark.parametrize("shape", STREAM_K_SHAPES)
+@pytest.mark.parametrize("layout", ["weight_grad", "forward"])
+def test_stream_k_gemm_matches_fp32_and_is_deterministic(shape, layout):
+    """Tile counts that do not fill whole waves of SMs share the contraction of some tiles between SMs through
+    fp32 partial tiles in the workspace.  The result must match fp32, must not depend on timing, must agree with
+    the same kernel run without a workspace (whole tiles only), and the arrival counters must be zero again."""
+    import ctypes
+    from tritonformer_b200 import _lib, linear as lin
     m, n, k = shape
     torch.manual_seed(4)
-    xt = _r(k, m)                      # A(m, k) = xt[k, m]  (MN-major)
-    dy = _r(k, n, scale=k ** -0.5)
-    old = _r(m, n)
-    want = xt.float().t() @ dy.float()
-    got1 = lin.gemm(xt, 1, m, dy, n, 1, m, n, k)
-    got2 = lin.gemm(xt, 1, m, dy, n, 1, m, n, k)
+    if layout == "weight_grad":
+        a = _r(k, m)                       # A(m, k) = a[k, m]  (MN-major)
+        a_sm, a_sk, a32 = 1, m, a.float().t()
+    else:
+        a = _r(m, k)
+        a_sm, a_sk, a32 = k, 1, a.float()
+    b = _r(k, n, scale=k ** -0.5)
+    bias, old, mask = _r(n), _r(m, n), _r(m, n)
+    want = a32 @ b.float()
+    got1 = lin.gemm(a, a_sm, a_sk, b, n, 1, m, n, k)
+    got2 = lin.gemm(a, a_sm, a_sk, b, n, 1, m, n, k)
     assert torch.equal(got1, got2)
     assert norm_rel(got1, want) < 1e-3
+    plain = torch.empty_like(got1)
+    _lib.check(_lib.lib.tfb_gemm(a.data_ptr(), b.data_ptr(), plain.data_ptr(), None, m, n, k, a_sm, a_sk, n, 1, n,
+                                 0, 0, _lib.dtype_code(a.dtype), _lib.stream_ptr(a.device), None))
+    assert_close(got1, plain, 2e-3, "with and without workspace", rtol=2e-3)
     acc = old.clone()
-    lin.gemm(xt, 1, m, dy, n, 1, m, n, k, out=acc, accumulate=True)
+    lin.gemm(a, a_sm, a_sk, b, n, 1, m, n, k, out=acc, accumulate=True)
     assert norm_rel(acc, want + old.float()) < 1e-3
+    full = lin.gemm(a, a_sm, a_sk, b, n, 1, m, n, k, bias=bias, relu=True, addend=old, mask=mask)
+    assert_close(full, (torch.relu(want + bias.float()) + old.float()) * (mask > 0), 1e-2, "epilogue", rtol=2e-3)
+    ws = lin._gemm_workspace(a.device, _lib.stream_ptr(a.device))
+    torch.cuda.synchronize()
+    assert int(ws[:8192].count_nonzero()) == 0
+    assert _lib.lib.tfb_device_status(0) == 0
 
 
 @pytest.mark.parametrize("shape", [(512, 384, 320), (130, 72, 100)])

@@ -176,6 +176,60 @@ def test_gradients_accumulated_into_existing_grad_buffers():
         assert norm_rel(p.grad.float(), 2.0 * once[n]) < 2e-3, n
 
 
+@pytest.mark.parametrize("graph", [False, True])
+def test_overlapped_launches_match_serialised_launches(graph):
+    """Kernels are launched so that their set-up may overlap the previous kernel's tail; every kernel waits
+    for its predecessor before it touches global memory, so the results equal those of fully serialised launches
+    (up to the order of the fp32 dQ accumulation, which differs from run to run anyway), eagerly and when
+    the step is replayed from a CUDA graph."""
+    from tritonformer_b200 import _lib
+    from tritonformer_b200.transformer import Transformer
+    cfg = _cfg(vocab_size=2048, hidden_size=512, max_position_embeddings=512, num_attention_heads=8, head_dim=64,
+               ffn_dim=2048, num_hidden_layers=3, use_linear_bias=True, attn_bias=True)
+    torch.manual_seed(3)
+    model = Transformer(cfg, device="cuda")
+    with torch.no_grad():
+        model.logits_out.weight.normal_(0.0, 0.02)
+    ids = torch.randint(0, 2048, (4, 512), device="cuda")
+    out = {}
+
+    def step():
+        model.zero_grad(set_to_none=False)
+        with torch.autocast("cuda", dtype=torch.float16):
+            _, loss = model(ids, ids)
+        (loss * 1024.0).backward()
+        out["loss"] = loss.detach()
+
+    def run():
+        step()  # allocates .grad
+        if graph:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step()
+            torch.cuda.current_stream().wait_stream(side)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                step()
+            for _ in range(3):
+                g.replay()
+        else:
+            step()
+        torch.cuda.synchronize()
+        return out["loss"].clone(), [p.grad.detach().clone() for p in model.parameters()]
+
+    loss_a, grads_a = run()
+    _lib.lib.tfb_debug_set(3, 1)
+    try:
+        loss_b, grads_b = run()
+    finally:
+        _lib.lib.tfb_debug_set(3, 0)
+    assert _lib.lib.tfb_device_status(0) == 0
+    assert abs(loss_a.item() - loss_b.item()) < 1e-5
+    for (n, _), a, b in zip(model.named_parameters(), grads_a, grads_b):
+        assert norm_rel(a.float(), b.float()) < 1e-3, n
+
+
 def test_small_model_fp16_bias_alibi_hd32():
     cfg = _cfg(vocab_size=1000, hidden_size=192, max_position_embeddings=256, num_attention_heads=6, head_dim=32,
                ffn_dim=768, num_hidden_layers=2, use_linear_bias=True, attn_bias=True)

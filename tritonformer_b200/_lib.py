@@ -39,6 +39,7 @@ _SIGNATURES = {
     "tfb_colsum_partials": (_i64, [_i64, _i64]),
     "tfb_colsum": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp]),
     "tfb_gemm": (_i32, [_vp, _vp, _vp, _vp] + [_i64] * 8 + [_i32, _i32, _i32, _vp, _pi32]),
+    "tfb_gemm_workspace_bytes": (_i64, []),
     "tfb_gemm_fused": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64] + [_i64] * 8 + [_i32, _i32, _vp, _i64, _vp, _pi32]),
     "tfb_attention_fwd": (_i32, [_vp] * 5 + [_i64] * 4 + [_pi64] * 4 + [_vp, _i32, _vp, _i64, _i64, _i32, _vp, _pi32]),
     "tfb_attention_bwd_scratch_bytes": (_i64, [_i64] * 4),
@@ -66,6 +67,10 @@ if os.environ.get("TFB_FORCE_GENERIC_GEMM") == "1":  # test switch, see tfb_debu
     lib.tfb_debug_set(0, 1)
 if os.environ.get("TFB_FORCE_GENERIC_ATTN") == "1":
     lib.tfb_debug_set(1, 1)
+if os.environ.get("TFB_SERIALISED_LAUNCHES") == "1":  # no programmatic dependent launch
+    lib.tfb_debug_set(3, 1)
+if os.environ.get("TFB_GEMM_SWITCHES"):  # bit 0: whole tiles only, bit 5 (32): no CTA-pair kernel
+    lib.tfb_debug_set(4, int(os.environ["TFB_GEMM_SWITCHES"]))
 
 
 def dtype_code(t: torch.dtype) -> int:

@@ -134,13 +134,16 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
     mbar_init(pds_full, 8);
     mbar_init(dq_full, 1);
     mbar_init(dq_free, 4);
-    *abort_flag = (*(volatile int*)&g_dev_status != 0) ? 1 : 0;
     mbar_fence_init();
   }
   if (warp == 1) {
     __syncwarp();
     tmem_alloc(tmem_holder, 512);
   }
+  // set-up above is CTA-local and may overlap the previous kernel's tail; global memory comes after
+  grid_dependency_wait();
+  allow_dependents();
+  if (threadIdx.x == 0) *abort_flag = (*(volatile int*)&g_dev_status != 0) ? 1 : 0;
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -490,6 +493,8 @@ template <typename T>
 __global__ void __launch_bounds__(256) attn_dq_convert_kernel(const float* __restrict__ acc, T* __restrict__ dq,
                                                               int64_t sb, int64_t sh, int64_t st, int H, int T_,
                                                               int hd, float scale, int64_t nvec) {
+  grid_dependency_wait();
+  allow_dependents();
   const int vpr = hd / 8;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < nvec;
        idx += (int64_t)gridDim.x * blockDim.x) {
@@ -532,10 +537,11 @@ template <typename T, int HD>
 static int bwd_tc05_launch(const AttnArgs& a, int dtype, cudaStream_t st) {
   using Cfg = FbCfg<HD>;
   int rc;
-  if ((rc = attn_delta(a, HD, dtype, st))) return rc;
+  // clear the accumulator first, so that the main kernel directly follows a kernel in the stream
   const size_t acc_bytes = (size_t)a.B * a.H * a.T * HD * sizeof(float);
   cudaError_t e = cudaMemsetAsync(a.dq_acc, 0, acc_bytes, st);
   if (e != cudaSuccess) return fail(TFB_ERR_LAUNCH, "attention_bwd(tcgen05): memset: %s", cudaGetErrorString(e));
+  if ((rc = attn_delta(a, HD, dtype, st))) return rc;
   CUtensorMap tq, tk, tv, tdo, tdq;
   {
     // fp32 dQ accumulator as a (HD, B*H*T) matrix, boxes of 32 floats x 32 rows
@@ -560,13 +566,15 @@ static int bwd_tc05_launch(const AttnArgs& a, int dtype, cudaStream_t st) {
   if ((rc = ensure_dynamic_smem(attn_bwd_tc05_kernel<T, HD, true>, Cfg::SMEM_BYTES, done_bias, "attention_bwd(tcgen05)")))
     return rc;
   dim3 grid(a.T / FB_T, a.B * a.H);
-  if (a.bias_mode) attn_bwd_tc05_kernel<T, HD, true><<<grid, FB_THREADS, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, tdo, tdq, p);
-  else attn_bwd_tc05_kernel<T, HD, false><<<grid, FB_THREADS, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, tdo, tdq, p);
+  if (a.bias_mode)
+    launch_overlapped(attn_bwd_tc05_kernel<T, HD, true>, grid, dim3(FB_THREADS), Cfg::SMEM_BYTES, st, tq, tk, tv, tdo, tdq, p);
+  else
+    launch_overlapped(attn_bwd_tc05_kernel<T, HD, false>, grid, dim3(FB_THREADS), Cfg::SMEM_BYTES, st, tq, tk, tv, tdo, tdq, p);
   if ((rc = launched("attention_bwd(tcgen05)"))) return rc;
   const int64_t nvec = (int64_t)a.B * a.H * a.T * HD / 8;
   const unsigned blocks = (unsigned)(ceil_div(nvec, 256) < 148 * 8 ? ceil_div(nvec, 256) : 148 * 8);
-  attn_dq_convert_kernel<T><<<blocks, 256, 0, st>>>(a.dq_acc, (T*)a.dq, a.sdq.b, a.sdq.h, a.sdq.t, a.H, a.T, HD,
-                                                    a.scale, nvec);
+  launch_overlapped(attn_dq_convert_kernel<T>, dim3(blocks), dim3(256), 0, st, a.dq_acc, (T*)a.dq, a.sdq.b, a.sdq.h,
+                    a.sdq.t, a.H, a.T, HD, a.scale, nvec);
   return launched("attention_dq_convert");
 }
 

@@ -101,13 +101,16 @@ __global__ void __launch_bounds__(F2_THREADS, 1) attn_fwd2_tc05_kernel(const __g
       mbar_init(&p_full[i], 4);
       mbar_init(&pv_done[i], 1);
     }
-    *abort_flag = (*(volatile int*)&g_dev_status != 0) ? 1 : 0;
     mbar_fence_init();
   }
   if (warp == 1) {
     __syncwarp();
     tmem_alloc(tmem_holder, 512);
   }
+  // set-up above is CTA-local and may overlap the previous kernel's tail; global memory comes after
+  grid_dependency_wait();
+  allow_dependents();
+  if (threadIdx.x == 0) *abort_flag = (*(volatile int*)&g_dev_status != 0) ? 1 : 0;
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -378,8 +381,8 @@ static int fwd2_launch(const AttnArgs& a, int dtype, cudaStream_t st) {
     return rc;
   const int nq = a.T / F2_TILE;
   dim3 grid((nq + 1) / 2, a.B * a.H);
-  if (a.bias_mode) attn_fwd2_tc05_kernel<T, true><<<grid, F2_THREADS, F2_SMEM_BYTES, st>>>(tq, tk, tv, p);
-  else attn_fwd2_tc05_kernel<T, false><<<grid, F2_THREADS, F2_SMEM_BYTES, st>>>(tq, tk, tv, p);
+  if (a.bias_mode) launch_overlapped(attn_fwd2_tc05_kernel<T, true>, grid, dim3(F2_THREADS), F2_SMEM_BYTES, st, tq, tk, tv, p);
+  else launch_overlapped(attn_fwd2_tc05_kernel<T, false>, grid, dim3(F2_THREADS), F2_SMEM_BYTES, st, tq, tk, tv, p);
   return launched("attention_fwd(tcgen05, two tiles)");
 }
 

@@ -224,6 +224,8 @@ __global__ void __launch_bounds__(AT_THREADS) attn_fwd_kernel(const AttnArgs a) 
 // delta[b,h,i] = sum_d dO[i,d] * O[i,d]; hd/8 lanes per row, one 16-byte load of each operand per lane
 template <typename T, int HD>
 __global__ void __launch_bounds__(256) attn_delta_kernel(const AttnArgs a) {
+  grid_dependency_wait();
+  allow_dependents();
   constexpr int LPR = HD / 8;          // lanes per row
   constexpr int RPW = 32 / LPR;        // rows per warp
   const int lane = threadIdx.x & 31;
@@ -537,9 +539,9 @@ static int bwd_launch(const AttnArgs& a, cudaStream_t st) {
 int attn_delta(const AttnArgs& a, int hd, int dtype, cudaStream_t st) {
   const int64_t rows = (int64_t)a.B * a.H * a.T;
   TFB_DISPATCH_16(dtype, T, {
-    if (hd == 32) attn_delta_kernel<T, 32><<<(unsigned)ceil_div(rows, 8 * 8), 256, 0, st>>>(a);
-    else if (hd == 64) attn_delta_kernel<T, 64><<<(unsigned)ceil_div(rows, 8 * 4), 256, 0, st>>>(a);
-    else attn_delta_kernel<T, 128><<<(unsigned)ceil_div(rows, 8 * 2), 256, 0, st>>>(a);
+    if (hd == 32) launch_overlapped(attn_delta_kernel<T, 32>, dim3((unsigned)ceil_div(rows, 8 * 8)), dim3(256), 0, st, a);
+    else if (hd == 64) launch_overlapped(attn_delta_kernel<T, 64>, dim3((unsigned)ceil_div(rows, 8 * 4)), dim3(256), 0, st, a);
+    else launch_overlapped(attn_delta_kernel<T, 128>, dim3((unsigned)ceil_div(rows, 8 * 2)), dim3(256), 0, st, a);
   })
   return launched("attention_delta");
 }

@@ -90,13 +90,16 @@ __global__ void __launch_bounds__(FA_THREADS, 1) attn_fwd_tc05_kernel(const __gr
     }
     mbar_init(p_full, 4);
     mbar_init(pv_done, 1);
-    *abort_flag = (*(volatile int*)&g_dev_status != 0) ? 1 : 0;
     mbar_fence_init();
   }
   if (warp == 1) {
     __syncwarp();
     tmem_alloc(tmem_holder, Cfg::TMEM_COLS);
   }
+  // set-up above is CTA-local and may overlap the previous kernel's tail; global memory comes after
+  grid_dependency_wait();
+  allow_dependents();
+  if (threadIdx.x == 0) *abort_flag = (*(volatile int*)&g_dev_status != 0) ? 1 : 0;
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -324,7 +327,7 @@ static int fwd_tc05_launch(const AttnArgs& a, int dtype, cudaStream_t st) {
   static std::atomic<uint64_t> attr_done{0};
   if ((rc = ensure_dynamic_smem(kern, Cfg::SMEM_BYTES, attr_done, "attention_fwd(tcgen05)"))) return rc;
   dim3 grid(a.T / FA_M, a.B * a.H);
-  kern<<<grid, FA_THREADS, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, p);
+  launch_overlapped(kern, grid, dim3(FA_THREADS), Cfg::SMEM_BYTES, st, tq, tk, tv, p);
   return launched("attention_fwd(tcgen05)");
 }
 

@@ -46,6 +46,37 @@ inline int ensure_dynamic_smem(F func, int bytes, std::atomic<uint64_t>& done, c
   return TFB_OK;
 }
 
+// ---- programmatic dependent launch ----------------------------------------------------
+// Kernels launched through launch_overlapped() may become resident while the previous kernel of
+// the stream is still draining: their set-up (barrier init, TMEM allocation, tensor-map prefetch)
+// overlaps its tail.  Every such kernel calls grid_dependency_wait() before its first access to
+// global memory (the wait returns once the previous grid has completed and its writes are visible)
+// and then allow_dependents(), which lets the following kernel do the same with respect to it.
+// A kernel launched the plain way treats both calls as no-ops.  tfb_debug_set(3, 1) turns the
+// launch attribute off.
+extern std::atomic<int> g_plain_launch;
+
+template <typename... KArgs, typename... Args>
+inline void launch_overlapped(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_plain_launch.load(std::memory_order_relaxed) ? 0 : 1;
+  (void)cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);  // error read by launched()
+}
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void allow_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
+
 #define TFB_REQUIRE(cond, ...)                         \
   do {                                                 \
     if (!(cond)) return ::tfb::fail(TFB_ERR_ARG, __VA_ARGS__); \

@@ -25,6 +25,8 @@ template <typename T, bool VEC>
 __global__ void __launch_bounds__(CE_THREADS) ce_fwd_kernel(
     const T* __restrict__ logits, const int64_t* __restrict__ labels, T* __restrict__ loss,
     float* __restrict__ loss_f32, float* __restrict__ lse, int vocab, int64_t ld) {
+  grid_dependency_wait();
+  allow_dependents();
   __shared__ float sm_m[CE_THREADS / 32], sm_s[CE_THREADS / 32];
   const int64_t row = blockIdx.x;
   const T* xr = logits + row * ld;
@@ -85,6 +87,8 @@ __global__ void __launch_bounds__(CE_THREADS) ce_bwd_kernel(
     const T* __restrict__ logits, const int64_t* __restrict__ labels, const float* __restrict__ lse,
     const T* __restrict__ grad, int64_t grad_stride, T* __restrict__ dlogits, int vocab, int64_t ld,
     int64_t dld) {
+  grid_dependency_wait();
+  allow_dependents();
   const int64_t row = blockIdx.x;
   const T* xr = logits + row * ld;
   T* dr = dlogits + row * dld;
@@ -133,11 +137,9 @@ extern "C" int tfb_cross_entropy_fwd(const void* logits, const int64_t* labels, 
   const bool vec = vocab % 8 == 0 && logits_ld % 8 == 0 && aligned16(logits);
   TFB_DISPATCH_16(dtype, T, {
     if (vec)
-      ce_fwd_kernel<T, true><<<(unsigned)rows, CE_THREADS, 0, st>>>(
-          (const T*)logits, labels, (T*)loss, loss_f32, lse, (int)vocab, logits_ld);
+      launch_overlapped(ce_fwd_kernel<T, true>, dim3((unsigned)rows), dim3(CE_THREADS), 0, st, (const T*)logits, labels, (T*)loss, loss_f32, lse, (int)vocab, logits_ld);
     else
-      ce_fwd_kernel<T, false><<<(unsigned)rows, CE_THREADS, 0, st>>>(
-          (const T*)logits, labels, (T*)loss, loss_f32, lse, (int)vocab, logits_ld);
+      launch_overlapped(ce_fwd_kernel<T, false>, dim3((unsigned)rows), dim3(CE_THREADS), 0, st, (const T*)logits, labels, (T*)loss, loss_f32, lse, (int)vocab, logits_ld);
   })
   return launched("cross_entropy_fwd");
 }
@@ -154,12 +156,10 @@ extern "C" int tfb_cross_entropy_bwd(const void* logits, const int64_t* labels, 
                    aligned16(dlogits);
   TFB_DISPATCH_16(dtype, T, {
     if (vec)
-      ce_bwd_kernel<T, true><<<(unsigned)rows, CE_THREADS, 0, st>>>(
-          (const T*)logits, labels, lse, (const T*)grad, grad_stride, (T*)dlogits, (int)vocab,
+      launch_overlapped(ce_bwd_kernel<T, true>, dim3((unsigned)rows), dim3(CE_THREADS), 0, st, (const T*)logits, labels, lse, (const T*)grad, grad_stride, (T*)dlogits, (int)vocab,
           logits_ld, dlogits_ld);
     else
-      ce_bwd_kernel<T, false><<<(unsigned)rows, CE_THREADS, 0, st>>>(
-          (const T*)logits, labels, lse, (const T*)grad, grad_stride, (T*)dlogits, (int)vocab,
+      launch_overlapped(ce_bwd_kernel<T, false>, dim3((unsigned)rows), dim3(CE_THREADS), 0, st, (const T*)logits, labels, lse, (const T*)grad, grad_stride, (T*)dlogits, (int)vocab,
           logits_ld, dlogits_ld);
   })
   return launched("cross_entropy_bwd");

@@ -10,6 +10,8 @@ template <typename T>
 __global__ void __launch_bounds__(256) relu_bwd_vec_kernel(const uint4* __restrict__ dy,
                                                            const uint4* __restrict__ act,
                                                            uint4* __restrict__ dz, int64_t nvec) {
+  grid_dependency_wait();
+  allow_dependents();
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
     float g[8], a[8];
@@ -24,6 +26,8 @@ __global__ void __launch_bounds__(256) relu_bwd_vec_kernel(const uint4* __restri
 template <typename T>
 __global__ void __launch_bounds__(256) relu_bwd_scalar_kernel(const T* __restrict__ dy, const T* __restrict__ act,
                                                               T* __restrict__ dz, int64_t n) {
+  grid_dependency_wait();
+  allow_dependents();
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
     dz[i] = Num<T>::to_f(act[i]) > 0.f ? dy[i] : Num<T>::from_f(0.f);
@@ -33,6 +37,8 @@ __global__ void __launch_bounds__(256) relu_bwd_scalar_kernel(const T* __restric
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) colsum_kernel(const T* __restrict__ x, float* __restrict__ partials,
                                                      int64_t rows, int cols, int64_t ld) {
+  grid_dependency_wait();
+  allow_dependents();
   __shared__ float sm[8][32][9];
   const int cl = threadIdx.x & 31, rl = threadIdx.x >> 5;
   const int c0 = (blockIdx.x * 32 + cl) * 8;
@@ -82,10 +88,10 @@ extern "C" int tfb_relu_bwd(const void* dy, const void* act, void* dz, int64_t n
     if (vec) {
       const int64_t nvec = n / 8;
       const unsigned grid = (unsigned)(ceil_div(nvec, 256) < 148 * 16 ? ceil_div(nvec, 256) : 148 * 16);
-      relu_bwd_vec_kernel<T><<<grid, 256, 0, st>>>((const uint4*)dy, (const uint4*)act, (uint4*)dz, nvec);
+      launch_overlapped(relu_bwd_vec_kernel<T>, dim3(grid), dim3(256), 0, st, (const uint4*)dy, (const uint4*)act, (uint4*)dz, nvec);
     } else {
       const unsigned grid = (unsigned)(ceil_div(n, 256) < 148 * 16 ? ceil_div(n, 256) : 148 * 16);
-      relu_bwd_scalar_kernel<T><<<grid, 256, 0, st>>>((const T*)dy, (const T*)act, (T*)dz, n);
+      launch_overlapped(relu_bwd_scalar_kernel<T>, dim3(grid), dim3(256), 0, st, (const T*)dy, (const T*)act, (T*)dz, n);
     }
   })
   return launched("relu_bwd");
@@ -110,8 +116,8 @@ extern "C" int tfb_colsum(const void* x, void* out, float* partials, int64_t n_p
   const bool vec = cols % 8 == 0 && x_ld % 8 == 0 && aligned16(x);
   dim3 grid((unsigned)ceil_div(cols, 256), (unsigned)n_partials);
   TFB_DISPATCH_16(dtype, T, {
-    if (vec) colsum_kernel<T, true><<<grid, 256, 0, st>>>((const T*)x, partials, rows, (int)cols, x_ld);
-    else colsum_kernel<T, false><<<grid, 256, 0, st>>>((const T*)x, partials, rows, (int)cols, x_ld);
+    if (vec) launch_overlapped(colsum_kernel<T, true>, dim3(grid), dim3(256), 0, st, (const T*)x, partials, rows, (int)cols, x_ld);
+    else launch_overlapped(colsum_kernel<T, false>, dim3(grid), dim3(256), 0, st, (const T*)x, partials, rows, (int)cols, x_ld);
     int rc = launched("colsum");
     if (rc) return rc;
     return finalize_partials<T>(partials, n_partials, (int)cols, (int)cols, out, out, st);

@@ -10,13 +10,26 @@
 //                             bias / ReLU / addend / mask in fp32, round once into a swizzled smem
 //                             box, TMA store (the addend / mask box arrives by TMA load); overlaps
 //                             the next tile's main loop through the second accumulator buffer
+// Work split ("stream-K"): when there are fewer tiles than SMs, the tiles are cut along K into one
+// equal, contiguous range of k-blocks per CTA (the scheduler also handles a split region followed by
+// whole tiles).  A CTA whose range starts inside a tile writes that fp32 partial tile to its
+// own workspace slot and raises the tile's flags; the CTA that owns the tile's first k-blocks (its
+// last piece of the range, so the others are long done) adds the partials in CTA order and runs the
+// epilogue.  The sum order is fixed, so results do not depend on timing.
 // Either operand may be K-major (contraction index contiguous) or MN-major, so the forward
 // product X·W, the input gradient dY·Wᵀ and the weight gradient Xᵀ·dY (contraction over every
 // token of the batch, i.e. the batch reduction fused into the product) are the same kernel.
-#include "tc05.cuh"
+#include "gemm_sched.cuh"
 #include <type_traits>
 
 namespace tfb {
+
+extern std::atomic<int> g_gemm_debug;
+int64_t gemm_pair_tiles(int64_t M, int64_t N);
+int gemm_pair_tc05(const void* a, const void* b, void* c, const void* bias, const void* addend, int64_t ld_addend,
+                   const void* mask, int64_t ld_mask, int64_t M, int64_t N, int64_t K, int64_t a_sm, int64_t a_sk,
+                   int64_t b_sk, int64_t b_sn, int64_t ldc, int relu, int dtype, int sms, void* workspace,
+                   cudaStream_t st);
 
 constexpr int TB_M = 128;
 constexpr int TB_K = 64;  // 64 sixteen-bit elements = one 128-byte swizzle row
@@ -40,11 +53,14 @@ struct GemmParams {
   const void* bias;
   const void* addend;  // added after bias/ReLU (the residual stream, or C itself to accumulate); may be null
   const void* mask;    // result is zeroed where mask <= 0 (a saved ReLU output); may be null
-  float* ws;           // split-K: fp32 (M, N) partial sums, zero on entry; null when splits == 1
+  int* flags;          // stream-K: 4 arrival counters per split tile (one per epilogue warp), zero between kernels
+  float* partials;     // stream-K: one fp32 128 x BN slot per CTA
   int M, N, K;
   int64_t ldc, ld_addend, ld_mask;
   int relu;
-  int tiles_m, tiles_n, splits;
+  int tiles_m, tiles_n;
+  int sk_tiles;        // tiles [0, sk_tiles) are split along K over all CTAs; 0 = whole tiles only
+  int debug;           // timing experiments (tfb_debug_set key 4): bit 1 skips the partial reads, bit 2 the partial writes
 };
 
 template <typename T, int BN, bool A_MN, bool B_MN>
@@ -78,38 +94,39 @@ __global__ void __launch_bounds__(TB_THREADS, 1) gemm_tc05_kernel(const __grid_c
       mbar_init(&acc_empty[i], 4);  // one arrival per epilogue warp
     }
     for (int i = 0; i < 4; ++i) mbar_init(&x_full[i], 1);
-    // an earlier kernel that gave up leaves the status set: then this one does nothing
-    *abort_flag = (*(volatile int*)&g_dev_status != 0) ? 1 : 0;
     mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
   }
   if (warp == 1) {
     __syncwarp();
     tmem_alloc(tmem_holder, Cfg::TMEM_COLS);
   }
+  // everything above touches only this CTA's shared memory, TMEM and kernel parameters, so it may
+  // run while the previous kernel of the stream is still finishing; global memory comes after this
+  grid_dependency_wait();
+  allow_dependents();
+  // an earlier kernel that gave up leaves the status set: then this one does nothing
+  if (threadIdx.x == 0) *abort_flag = (*(volatile int*)&g_dev_status != 0) ? 1 : 0;
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  // work unit = (output tile, K split); the splits of a tile are adjacent so they run concurrently
-  const int num_tiles = *abort_flag ? 0 : p.tiles_m * p.tiles_n * p.splits;
   const int kblocks_all = (p.K + TB_K - 1) / TB_K;
-  const int kb_per_split = (kblocks_all + p.splits - 1) / p.splits;
+  const bool dead = *abort_flag != 0;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      tma_prefetch_desc(&tmA);
-      tma_prefetch_desc(&tmB);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int unit = blockIdx.x; unit < num_tiles && ok; unit += gridDim.x) {
-        const int tile = unit / p.splits, split = unit % p.splits;
+      Segments segs(kblocks_all, p.tiles_m * p.tiles_n, p.sk_tiles, (int)gridDim.x, (int)blockIdx.x, dead);
+      int tile, kb0, kb1;
+      while (ok && segs.next(tile, kb0, kb1)) {
         const int m0 = (tile % p.tiles_m) * TB_M;
         const int n0 = (tile / p.tiles_m) * BN;
-        const int kb0 = split * kb_per_split;
-        const int kb1 = min(kb0 + kb_per_split, kblocks_all);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, 0x100 | stage, abort_flag)) { ok = false; break; }
           uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
@@ -142,10 +159,9 @@ __global__ void __launch_bounds__(TB_THREADS, 1) gemm_tc05_kernel(const __grid_c
       int buf = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int unit = blockIdx.x; unit < num_tiles && ok; unit += gridDim.x) {
-        const int split = unit % p.splits;
-        const int kb0 = split * kb_per_split;
-        const int kb1 = min(kb0 + kb_per_split, kblocks_all);
+      Segments segs(kblocks_all, p.tiles_m * p.tiles_n, p.sk_tiles, (int)gridDim.x, (int)blockIdx.x, dead);
+      int tile, kb0, kb1;
+      while (ok && segs.next(tile, kb0, kb1)) {
         if (!mbar_wait(&acc_empty[buf], acc_phase ^ 1, 0x300 | buf, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
@@ -185,7 +201,7 @@ __global__ void __launch_bounds__(TB_THREADS, 1) gemm_tc05_kernel(const __grid_c
     uint8_t* stage_x = smem + Cfg::OFF_EPI_X + ew * 4096;
     // at most one of addend / mask travels through the TMA box; a second one is read directly
     const bool x_is_addend = p.addend != nullptr;
-    const bool use_x = (p.addend != nullptr || p.mask != nullptr) && p.splits == 1;
+    const bool use_x = (p.addend != nullptr || p.mask != nullptr);
     const T* mask_direct = (p.addend != nullptr && p.mask != nullptr) ? reinterpret_cast<const T*>(p.mask) : nullptr;
     constexpr int STEPS = BN / 64;
     int buf = 0;
@@ -195,19 +211,65 @@ __global__ void __launch_bounds__(TB_THREADS, 1) gemm_tc05_kernel(const __grid_c
       tma_prefetch_desc(&tmC);
       if (use_x) tma_prefetch_desc(&tmX);
     }
-    for (int unit = blockIdx.x; unit < num_tiles && ok; unit += gridDim.x) {
-      const int tile = unit / p.splits;
+    Segments segs(kblocks_all, p.tiles_m * p.tiles_n, p.sk_tiles, (int)gridDim.x, (int)blockIdx.x, dead);
+    int tile, kb0, kb1;
+    while (ok && segs.next(tile, kb0, kb1)) {
       const int m0 = (tile % p.tiles_m) * TB_M;
       const int n0 = (tile / p.tiles_m) * BN;
       const int row0 = m0 + q * 32;       // first row of this warp's slice
       const int row = row0 + lane;
-      if (use_x && lane == 0) {           // box of step 0, in flight while the main loop still runs
+      const bool contributes = kb0 > 0;                      // a later part of a split tile
+      const bool finishes = kb0 == 0 && kb1 < kblocks_all;   // first part of a split tile: owns its epilogue
+      if (use_x && !contributes && lane == 0) {  // box of step 0, in flight while the main loop still runs
         mbar_expect_tx(&x_full[ew], 4096);
         tma_load_2d(stage_x, &tmX, n0, row0, &x_full[ew]);
       }
       if (!mbar_wait(&acc_full[buf], acc_phase, 0x400 | buf, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
+      if (contributes) {
+        // fp32 partial of this warp's 32 rows into this CTA's slot, then one arrival on the tile's counter
+        // slot layout [column group of 4][row]: the 32 lanes of a warp touch 512 contiguous bytes
+        float4* slot = reinterpret_cast<float4*>(p.partials + (int64_t)blockIdx.x * TB_M * BN) + q * 32 + lane;
+#pragma unroll 1
+        for (int st = 0; st < ((p.debug & 4) ? 0 : STEPS); ++st) {
+          uint32_t r0[32], r1[32];
+          tmem_ld32(taddr + st * 64, r0);
+          tmem_ld32(taddr + st * 64 + 32, r1);
+          tc_wait_ld();
+          float4* dst = slot + st * 16 * TB_M;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            __stcg(dst + e * TB_M, make_float4(__uint_as_float(r0[4 * e]), __uint_as_float(r0[4 * e + 1]),
+                                        __uint_as_float(r0[4 * e + 2]), __uint_as_float(r0[4 * e + 3])));
+            __stcg(dst + (8 + e) * TB_M, make_float4(__uint_as_float(r1[4 * e]), __uint_as_float(r1[4 * e + 1]),
+                                            __uint_as_float(r1[4 * e + 2]), __uint_as_float(r1[4 * e + 3])));
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence();  // the warp's partial rows are visible before the arrival
+          atomicAdd(p.flags + tile * 4 + q, 1);
+          mbar_arrive(&acc_empty[buf]);
+        }
+        buf ^= 1;
+        if (buf == 0) acc_phase ^= 1;
+        continue;
+      }
+      int n_parts = 0;  // partial tiles to add: the CTAs after this one whose ranges reach into the tile
+      if (finishes) {
+        n_parts = partials_expected(tile, kblocks_all, p.sk_tiles, (int)gridDim.x, (int)blockIdx.x);
+        int* flag = p.flags + tile * 4 + q;
+        int fine = 1;
+        if (lane == 0) {
+          fine = flag_wait(flag, n_parts, 0x600 | q, abort_flag) ? 1 : 0;
+          if (fine) *flag = 0;  // this warp is the counter's only reader: hand it back cleared
+        }
+        fine = __shfl_sync(0xffffffffu, fine, 0);
+        __syncwarp();  // lane 0's acquire orders the whole warp's reads of the partial tiles
+        if (!fine) { ok = false; break; }
+      }
 #pragma unroll 1
       for (int st = 0; st < STEPS && ok; ++st) {
         const int col0 = n0 + st * 64;
@@ -215,26 +277,24 @@ __global__ void __launch_bounds__(TB_THREADS, 1) gemm_tc05_kernel(const __grid_c
         tmem_ld32(taddr + st * 64, r0);
         tmem_ld32(taddr + st * 64 + 32, r1);
         tc_wait_ld();
-        if (p.splits > 1) {
-          // partial sum of this K range: fp32 adds into the workspace; the finishing kernel applies
-          // bias / ReLU / addend / mask and rounds once (N % 8 == 0 on this path)
-          if (row < p.M) {
-            float* w = p.ws + (int64_t)row * p.N + col0;
+        for (int c = 1; c <= ((p.debug & 2) ? 0 : n_parts); ++c) {
+          // all sixteen loads of this thread's 64 columns are issued before the first add
+          const float4* src = reinterpret_cast<const float4*>(p.partials + (int64_t)(blockIdx.x + c) * TB_M * BN) +
+                              st * 16 * TB_M + q * 32 + lane;
+          float4 v[16];
 #pragma unroll
-            for (int e = 0; e < 32; e += 4) {
-              if (col0 + e < p.N)
-                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(w + e), "f"(__uint_as_float(r0[e])),
-                             "f"(__uint_as_float(r0[e + 1])), "f"(__uint_as_float(r0[e + 2])),
-                             "f"(__uint_as_float(r0[e + 3]))
-                             : "memory");
-              if (col0 + 32 + e < p.N)
-                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(w + 32 + e),
-                             "f"(__uint_as_float(r1[e])), "f"(__uint_as_float(r1[e + 1])),
-                             "f"(__uint_as_float(r1[e + 2])), "f"(__uint_as_float(r1[e + 3]))
-                             : "memory");
-            }
+          for (int e = 0; e < 16; ++e) v[e] = __ldcg(src + e * TB_M);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            r0[4 * e] = __float_as_uint(__uint_as_float(r0[4 * e]) + v[e].x);
+            r0[4 * e + 1] = __float_as_uint(__uint_as_float(r0[4 * e + 1]) + v[e].y);
+            r0[4 * e + 2] = __float_as_uint(__uint_as_float(r0[4 * e + 2]) + v[e].z);
+            r0[4 * e + 3] = __float_as_uint(__uint_as_float(r0[4 * e + 3]) + v[e].w);
+            r1[4 * e] = __float_as_uint(__uint_as_float(r1[4 * e]) + v[8 + e].x);
+            r1[4 * e + 1] = __float_as_uint(__uint_as_float(r1[4 * e + 1]) + v[8 + e].y);
+            r1[4 * e + 2] = __float_as_uint(__uint_as_float(r1[4 * e + 2]) + v[8 + e].z);
+            r1[4 * e + 3] = __float_as_uint(__uint_as_float(r1[4 * e + 3]) + v[8 + e].w);
           }
-          continue;
         }
         if (use_x) {
           if (!mbar_wait(&x_full[ew], x_phase, 0x500 | ew, abort_flag)) { ok = false; break; }
@@ -318,53 +378,6 @@ __global__ void __launch_bounds__(TB_THREADS, 1) gemm_tc05_kernel(const __grid_c
   }
 }
 
-// Split-K epilogue: C = mask(act(ws + bias) + addend), rounded once; 8 columns per thread.  The
-// workspace is zero on entry to the GEMM (caller's contract) and is returned zero-filled.
-template <typename T>
-__global__ void __launch_bounds__(256) splitk_finish_kernel(const GemmParams p) {
-  const int vpr = p.N / 8;
-  const int64_t total = (int64_t)p.M * vpr;
-  T* C = reinterpret_cast<T*>(p.C);
-  const T* bias = reinterpret_cast<const T*>(p.bias);
-  const T* addend = reinterpret_cast<const T*>(p.addend);
-  const T* mask = reinterpret_cast<const T*>(p.mask);
-  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
-       idx += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t row = idx / vpr;
-    const int col = (int)(idx % vpr) * 8;
-    float4* w4 = reinterpret_cast<float4*>(p.ws + row * p.N + col);
-    const float4 x = w4[0];
-    const float4 y = w4[1];
-    // leave the workspace zero-filled for the next split-K product (saves a memset per call)
-    w4[0] = make_float4(0.f, 0.f, 0.f, 0.f);
-    w4[1] = make_float4(0.f, 0.f, 0.f, 0.f);
-    float f[8] = {x.x, x.y, x.z, x.w, y.x, y.y, y.z, y.w};
-    if (bias) {
-      float b[8];
-      unpack8<T>(__ldg(reinterpret_cast<const uint4*>(bias + col)), b);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) f[j] += b[j];
-    }
-    if (p.relu) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) f[j] = fmaxf(f[j], 0.f);
-    }
-    if (addend) {
-      float o[8];
-      unpack8<T>(*reinterpret_cast<const uint4*>(addend + row * p.ld_addend + col), o);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) f[j] += o[j];
-    }
-    if (mask) {
-      float o[8];
-      unpack8<T>(*reinterpret_cast<const uint4*>(mask + row * p.ld_mask + col), o);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) f[j] = o[j] > 0.f ? f[j] : 0.f;
-    }
-    *reinterpret_cast<uint4*>(C + row * p.ldc + col) = pack8<T>(f);
-  }
-}
-
 // ------------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -415,31 +428,28 @@ static int sm_count() {
   return n;
 }
 
+// Arrival counters plus one fp32 128 x 256 partial tile per SM.
+int64_t gemm_tc05_workspace_bytes() { return kFlagBytes + (int64_t)sm_count() * TB_M * 256 * (int64_t)sizeof(float); }
+
 template <typename T, int BN, bool A_MN, bool B_MN>
 static int launch_tc05(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmX,
-                       const GemmParams& p, cudaStream_t st) {
+                       const GemmParams& p, int grid, cudaStream_t st) {
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_tc05_kernel<T, BN, A_MN, B_MN>;
   static std::atomic<uint64_t> attr_done{0};
   if (int rc0 = ensure_dynamic_smem(kern, Cfg::SMEM_BYTES, attr_done, "gemm_tc05")) return rc0;
-  const int units = p.tiles_m * p.tiles_n * p.splits;
-  const int grid = units < sm_count() ? units : sm_count();
-  kern<<<grid, TB_THREADS, Cfg::SMEM_BYTES, st>>>(tmA, tmB, tmC, tmX, p);
-  int rc = launched("gemm_tc05");
-  if (rc || p.splits == 1) return rc;
-  const int64_t total = (int64_t)p.M * (p.N / 8);
-  const unsigned blocks = (unsigned)(ceil_div(total, 256) < 148 * 8 ? ceil_div(total, 256) : 148 * 8);
-  splitk_finish_kernel<T><<<blocks, 256, 0, st>>>(p);
-  return launched("gemm_splitk_finish");
+  launch_overlapped(kern, dim3(grid), dim3(TB_THREADS), Cfg::SMEM_BYTES, st, tmA, tmB, tmC, tmX, p);
+  return launched("gemm_tc05");
 }
 
 template <typename T, int BN>
 static int dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& tmA, const CUtensorMap& tmB,
-                          const CUtensorMap& tmC, const CUtensorMap& tmX, const GemmParams& p, cudaStream_t st) {
-  if (a_mn && b_mn) return launch_tc05<T, BN, true, true>(tmA, tmB, tmC, tmX, p, st);
-  if (a_mn) return launch_tc05<T, BN, true, false>(tmA, tmB, tmC, tmX, p, st);
-  if (b_mn) return launch_tc05<T, BN, false, true>(tmA, tmB, tmC, tmX, p, st);
-  return launch_tc05<T, BN, false, false>(tmA, tmB, tmC, tmX, p, st);
+                          const CUtensorMap& tmC, const CUtensorMap& tmX, const GemmParams& p, int grid,
+                          cudaStream_t st) {
+  if (a_mn && b_mn) return launch_tc05<T, BN, true, true>(tmA, tmB, tmC, tmX, p, grid, st);
+  if (a_mn) return launch_tc05<T, BN, true, false>(tmA, tmB, tmC, tmX, p, grid, st);
+  if (b_mn) return launch_tc05<T, BN, false, true>(tmA, tmB, tmC, tmX, p, grid, st);
+  return launch_tc05<T, BN, false, false>(tmA, tmB, tmC, tmX, p, grid, st);
 }
 
 // Whether (ptr, strides) can be described by a TMA tensor map of 16-bit elements.
@@ -464,21 +474,43 @@ int gemm_tc05(const void* a, const void* b, void* c, const void* bias, const voi
               int64_t workspace_bytes, cudaStream_t st) {
   const bool a_mn = (a_sk != 1);  // M contiguous
   const bool b_mn = (b_sk != 1);  // N contiguous
-  // tile width: fewest "waves x tile cost" over the SMs
   const int64_t tm = ceil_div(M, TB_M);
   const int sms = sm_count();
+  const int64_t kblocks = ceil_div(K, TB_K);
+  const int dbg = g_gemm_debug.load();
+  const bool can_split = !(dbg & 1) && workspace != nullptr && aligned16(workspace) &&
+                         workspace_bytes >= gemm_tc05_workspace_bytes();
+  // Outputs of at least 256 x 256 that can occupy the pairs of SMs run on CTA pairs (a third less
+  // operand traffic per flop): either a 256 x 256 tile for every pair, or a tile for at least every
+  // second pair and enough k-blocks to share.
+  {
+    const int64_t pt = gemm_pair_tiles(M, N);
+    if (!(dbg & 32) && M >= 256 && N >= 256 &&
+        (pt >= sms / 2 || (can_split && pt * 2 >= sms / 2 && pt * kblocks >= (int64_t)(sms / 2) * 8)))
+      return gemm_pair_tc05(a, b, c, bias, addend, ld_addend, mask, ld_mask, M, N, K, a_sm, a_sk, b_sk, b_sn, ldc,
+                            relu, dtype, sms, can_split ? workspace : nullptr, st);
+  }
+  // Tile width: fewest "waves x tile cost" over the SMs; the wide tile moves fewer operand bytes per
+  // flop, so the narrow one has to win by a clear margin.
   const int64_t cost256 = ceil_div(tm * ceil_div(N, 256), sms) * 256;
   const int64_t cost128 = ceil_div(tm * ceil_div(N, 128), sms) * 128;
-  // the wide tile moves fewer operand bytes per flop: the narrow one has to win by a clear margin
-  const int BN = (N <= 128 || cost128 * 10 < cost256 * 9) ? 128 : 256;
-  // Split the contraction in two when the output has too few tiles to occupy the machine (weight
-  // gradients: small M x N, contraction over every token).  Two fp32 partials added to a zeroed
-  // workspace give the same bits in either order, so the result stays deterministic.
+  int BN = (N <= 128 || cost128 * 10 < cost256 * 9) ? 128 : 256;
+  // Outputs with fewer tiles than SMs (weight gradients: small M x N, contraction over every token)
+  // share the K range of each tile between CTAs.  This pays only here: with more tiles than SMs the
+  // kernel is bound by operand traffic rather than by idle SMs in the last wave (measured), and the
+  // partial tiles would add to that traffic.  Very small outputs take the narrow tile so that a tile
+  // has fewer partials to add.
+  if (can_split && N > 128 && tm * ceil_div(N, 256) < sms) BN = (tm * ceil_div(N, 256) * 3 <= sms) ? 128 : 256;
   const int64_t tiles = tm * ceil_div(N, BN);
-  int splits = 1;
-  if (workspace && tiles * 10 <= sms * 6 && K >= 2048 && N % 8 == 0 &&
-      workspace_bytes >= (int64_t)M * N * (int64_t)sizeof(float) && aligned16(workspace))
-    splits = 2;
+  int64_t grid = tiles < sms ? tiles : sms;
+  int64_t sk_tiles = 0;
+  if (can_split && tiles < sms) {
+    // as many CTAs as leave each at least 8 k-blocks and each tile at most about 8 parts
+    int64_t g = tiles * kblocks / 8;
+    if (g > sms) g = sms;
+    if (g > tiles * 8) g = tiles * 8;
+    if (g * 4 >= tiles * 5 && tiles * 16 <= kFlagBytes) { grid = g; sk_tiles = tiles; }
+  }
 
   CUtensorMap tmA, tmB, tmC, tmX;
   int rc;
@@ -503,13 +535,15 @@ int gemm_tc05(const void* a, const void* b, void* c, const void* bias, const voi
     if ((rc = encode_tmap_sw128(&tmB, b, dtype, 2, dims, str, box))) return rc;
   }
   GemmParams p;
-  p.C = c; p.bias = bias; p.addend = addend; p.mask = mask; p.ws = splits > 1 ? (float*)workspace : nullptr;
+  p.C = c; p.bias = bias; p.addend = addend; p.mask = mask;
+  p.flags = sk_tiles ? reinterpret_cast<int*>(workspace) : nullptr;
+  p.partials = sk_tiles ? reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + kFlagBytes) : nullptr;
   p.M = (int)M; p.N = (int)N; p.K = (int)K; p.ldc = ldc; p.ld_addend = ld_addend; p.ld_mask = ld_mask;
   p.relu = relu;
-  p.tiles_m = (int)tm; p.tiles_n = (int)ceil_div(N, BN); p.splits = splits;
+  p.tiles_m = (int)tm; p.tiles_n = (int)ceil_div(N, BN); p.sk_tiles = (int)sk_tiles; p.debug = dbg;
   TFB_DISPATCH_16(dtype, T, {
-    if (BN == 256) return dispatch_major<T, 256>(a_mn, b_mn, tmA, tmB, tmC, tmX, p, st);
-    return dispatch_major<T, 128>(a_mn, b_mn, tmA, tmB, tmC, tmX, p, st);
+    if (BN == 256) return dispatch_major<T, 256>(a_mn, b_mn, tmA, tmB, tmC, tmX, p, (int)grid, st);
+    return dispatch_major<T, 128>(a_mn, b_mn, tmA, tmB, tmC, tmX, p, (int)grid, st);
   })
 }
 

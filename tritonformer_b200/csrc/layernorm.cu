@@ -15,6 +15,8 @@ __global__ void __launch_bounds__(128) ln_fwd_vec_kernel(
     const T* __restrict__ x, const T* __restrict__ alpha, const T* __restrict__ beta,
     T* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd,
     int64_t rows, int d, int64_t x_ld, int64_t y_ld, float eps) {
+  grid_dependency_wait();
+  allow_dependents();
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -71,6 +73,8 @@ __global__ void __launch_bounds__(128) ln_fwd_generic_kernel(
     const T* __restrict__ x, const T* __restrict__ alpha, const T* __restrict__ beta,
     T* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd,
     int64_t rows, int d, int64_t x_ld, int64_t y_ld, float eps) {
+  grid_dependency_wait();
+  allow_dependents();
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -103,6 +107,8 @@ __global__ void __launch_bounds__(MAXT) ln_bwd_kernel(
     const float* __restrict__ mean, const float* __restrict__ rstd, T* __restrict__ dx,
     float* __restrict__ partials, int64_t rows, int d, int64_t dy_ld, int64_t x_ld,
     int64_t dx_ld, const T* __restrict__ dres, int64_t dres_ld) {
+  grid_dependency_wait();
+  allow_dependents();
   __shared__ float red[2][32][2 * LN_RB];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nwarp = blockDim.x >> 5;
@@ -245,6 +251,8 @@ __global__ void __launch_bounds__(256, 1) ln_bwd_warp_kernel(
     const float* __restrict__ mean, const float* __restrict__ rstd, T* __restrict__ dx,
     float* __restrict__ partials, int64_t rows, int d, int64_t dy_ld, int64_t x_ld, int64_t dx_ld,
     const T* __restrict__ dres, int64_t dres_ld) {
+  grid_dependency_wait();
+  allow_dependents();
   extern __shared__ float fold[];  // [2][d]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nvec = d >> 3;
@@ -350,6 +358,8 @@ template <typename T>
 __global__ void __launch_bounds__(256) finalize_partials_kernel(
     const float* __restrict__ partials, int64_t n, int ncols, int split, T* __restrict__ out0,
     T* __restrict__ out1) {
+  grid_dependency_wait();
+  allow_dependents();
   __shared__ float sm[8][33];
   const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + cx;
@@ -369,8 +379,7 @@ __global__ void __launch_bounds__(256) finalize_partials_kernel(
 template <typename T>
 int finalize_partials(const float* partials, int64_t n, int ncols, int split, void* out0,
                       void* out1, cudaStream_t st) {
-  finalize_partials_kernel<T><<<(unsigned)ceil_div(ncols, 32), 256, 0, st>>>(
-      partials, n, ncols, split, (T*)out0, (T*)out1);
+  launch_overlapped(finalize_partials_kernel<T>, dim3((unsigned)ceil_div(ncols, 32)), dim3(256), 0, st, partials, n, ncols, split, (T*)out0, (T*)out1);
   return launched("finalize_partials");
 }
 template int finalize_partials<__half>(const float*, int64_t, int, int, void*, void*, cudaStream_t);
@@ -385,7 +394,7 @@ static int ln_bwd_launch(const void* dy, const void* x, const void* alpha, const
                          int64_t dx_ld, bool vec, int threads, cudaStream_t st, const void* dres = nullptr,
                          int64_t dres_ld = 0) {
 #define TFB_LN_BWD(V, MT)                                                                     \
-  ln_bwd_kernel<T, V, MT><<<(unsigned)n_partials, threads, 0, st>>>(                          \
+  launch_overlapped(ln_bwd_kernel<T, V, MT>, dim3((unsigned)n_partials), dim3(threads), 0, st, \
       (const T*)dy, (const T*)x, (const T*)alpha, mean, rstd, (T*)dx, partials, rows, d, dy_ld, \
       x_ld, dx_ld, (const T*)dres, dres_ld)
   if (vec && d <= 1024 && aligned16(alpha)) {
@@ -393,9 +402,9 @@ static int ln_bwd_launch(const void* dy, const void* x, const void* alpha, const
     const T *gp = (const T*)dy, *xp = (const T*)x, *ap = (const T*)alpha, *rp = (const T*)dres;
     T* op = (T*)dx;
     const unsigned grid = (unsigned)n_partials;
-    if (d <= 256) ln_bwd_warp_kernel<T, 1><<<grid, 256, sm, st>>>(gp, xp, ap, mean, rstd, op, partials, rows, d, dy_ld, x_ld, dx_ld, rp, dres_ld);
-    else if (d <= 512) ln_bwd_warp_kernel<T, 2><<<grid, 256, sm, st>>>(gp, xp, ap, mean, rstd, op, partials, rows, d, dy_ld, x_ld, dx_ld, rp, dres_ld);
-    else ln_bwd_warp_kernel<T, 4><<<grid, 256, sm, st>>>(gp, xp, ap, mean, rstd, op, partials, rows, d, dy_ld, x_ld, dx_ld, rp, dres_ld);
+    if (d <= 256) launch_overlapped(ln_bwd_warp_kernel<T, 1>, dim3(grid), dim3(256), sm, st, gp, xp, ap, mean, rstd, op, partials, rows, d, dy_ld, x_ld, dx_ld, rp, dres_ld);
+    else if (d <= 512) launch_overlapped(ln_bwd_warp_kernel<T, 2>, dim3(grid), dim3(256), sm, st, gp, xp, ap, mean, rstd, op, partials, rows, d, dy_ld, x_ld, dx_ld, rp, dres_ld);
+    else launch_overlapped(ln_bwd_warp_kernel<T, 4>, dim3(grid), dim3(256), sm, st, gp, xp, ap, mean, rstd, op, partials, rows, d, dy_ld, x_ld, dx_ld, rp, dres_ld);
   } else if (vec && threads <= 256) TFB_LN_BWD(true, 256);
   else if (vec) TFB_LN_BWD(true, 1024);
   else if (threads <= 256) TFB_LN_BWD(false, 256);
@@ -425,15 +434,15 @@ extern "C" int tfb_layernorm_fwd(const void* x, const void* alpha, const void* b
     const T *xp = (const T*)x, *ap = (const T*)alpha, *bp = (const T*)beta;
     T* yp = (T*)y;
     if (!vec) {
-      ln_fwd_generic_kernel<T><<<grid, 128, 0, st>>>(xp, ap, bp, yp, mean, rstd, rows, (int)d, x_ld, y_ld, eps);
+      launch_overlapped(ln_fwd_generic_kernel<T>, dim3(grid), dim3(128), 0, st, xp, ap, bp, yp, mean, rstd, rows, (int)d, x_ld, y_ld, eps);
     } else if (d <= 256) {
-      ln_fwd_vec_kernel<T, 1><<<grid, 128, 0, st>>>(xp, ap, bp, yp, mean, rstd, rows, (int)d, x_ld, y_ld, eps);
+      launch_overlapped(ln_fwd_vec_kernel<T, 1>, dim3(grid), dim3(128), 0, st, xp, ap, bp, yp, mean, rstd, rows, (int)d, x_ld, y_ld, eps);
     } else if (d <= 512) {
-      ln_fwd_vec_kernel<T, 2><<<grid, 128, 0, st>>>(xp, ap, bp, yp, mean, rstd, rows, (int)d, x_ld, y_ld, eps);
+      launch_overlapped(ln_fwd_vec_kernel<T, 2>, dim3(grid), dim3(128), 0, st, xp, ap, bp, yp, mean, rstd, rows, (int)d, x_ld, y_ld, eps);
     } else if (d <= 1024) {
-      ln_fwd_vec_kernel<T, 4><<<grid, 128, 0, st>>>(xp, ap, bp, yp, mean, rstd, rows, (int)d, x_ld, y_ld, eps);
+      launch_overlapped(ln_fwd_vec_kernel<T, 4>, dim3(grid), dim3(128), 0, st, xp, ap, bp, yp, mean, rstd, rows, (int)d, x_ld, y_ld, eps);
     } else {
-      ln_fwd_vec_kernel<T, 8><<<grid, 128, 0, st>>>(xp, ap, bp, yp, mean, rstd, rows, (int)d, x_ld, y_ld, eps);
+      launch_overlapped(ln_fwd_vec_kernel<T, 8>, dim3(grid), dim3(128), 0, st, xp, ap, bp, yp, mean, rstd, rows, (int)d, x_ld, y_ld, eps);
     }
   })
   return launched("layernorm_fwd");

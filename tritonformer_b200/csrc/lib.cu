@@ -8,6 +8,8 @@ std::atomic<int64_t> g_launches{0};
 std::atomic<int> g_force_generic_gemm{0};
 std::atomic<int> g_force_fallback_attn{0};
 std::atomic<int> g_attn_debug{0};
+std::atomic<int> g_plain_launch{0};
+std::atomic<int> g_gemm_debug{0};
 
 int gemm_generic(const void* a, const void* b, void* c, const void* bias, const void* addend, int64_t ld_addend,
                  const void* mask, int64_t ld_mask, int64_t M, int64_t N, int64_t K, int64_t a_sm, int64_t a_sk,
@@ -20,10 +22,14 @@ bool gemm_tc05_eligible(const void* a, const void* b, const void* c, const void*
                         int64_t ld_addend, const void* mask, int64_t ld_mask, int64_t M, int64_t N, int64_t K,
                         int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int64_t ldc);
 int gemm_tc05_status(int reset);
+int gemm_pair_tc05_status(int reset);
+int64_t gemm_tc05_workspace_bytes();
 int attn_tc05_status(int reset);
 int attn_bwd_tc05_status(int reset);
 int attn_fwd2_tc05_status(int reset);
 int attn_bwd_tc05_counters(unsigned long long* out);
+int gemm_pair_counters(int cta, unsigned long long* out);
+std::atomic<int> g_counter_select{-1};
 }  // namespace tfb
 
 using namespace tfb;
@@ -38,16 +44,25 @@ extern "C" int tfb_device_status(int reset) {
   const int b = attn_tc05_status(reset);
   const int c = attn_bwd_tc05_status(reset);
   const int d = attn_fwd2_tc05_status(reset);
-  return a ? a : (b ? b : (c ? c : d));
+  const int e = gemm_pair_tc05_status(reset);
+  return a ? a : (b ? b : (c ? c : (d ? d : e)));
 }
 
-extern "C" int tfb_debug_counters(unsigned long long* out16) { return attn_bwd_tc05_counters(out16); }
+extern "C" int tfb_debug_counters(unsigned long long* out16) {
+  const int sel = g_counter_select.load();
+  return sel >= 0 ? gemm_pair_counters(sel, out16) : attn_bwd_tc05_counters(out16);
+}
 
 extern "C" void tfb_debug_set(int key, int value) {
   if (key == 0) g_force_generic_gemm.store(value);
   if (key == 1) g_force_fallback_attn.store(value);
   if (key == 2) g_attn_debug.store(value);
+  if (key == 3) g_plain_launch.store(value);
+  if (key == 4) g_gemm_debug.store(value);
+  if (key == 5) g_counter_select.store(value);
 }
+
+extern "C" int64_t tfb_gemm_workspace_bytes(void) { return gemm_tc05_workspace_bytes(); }
 
 extern "C" int tfb_gemm_fused(const void* a, const void* b, void* c, const void* bias, const void* addend,
                               int64_t ld_addend, const void* mask, int64_t ld_mask, int64_t M, int64_t N, int64_t K,

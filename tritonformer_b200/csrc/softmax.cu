@@ -40,6 +40,8 @@ template <typename T, int NV>
 __global__ void __launch_bounds__(128) softmax_fwd_vec_kernel(const T* __restrict__ x, T* __restrict__ y,
                                                               int64_t rows, int cols, int64_t x_ld,
                                                               int64_t y_ld) {
+  grid_dependency_wait();
+  allow_dependents();
   constexpr int W = Vec16<T>::N;
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -86,6 +88,8 @@ template <typename T>
 __global__ void __launch_bounds__(128) softmax_fwd_generic_kernel(const T* __restrict__ x, T* __restrict__ y,
                                                                   int64_t rows, int cols, int64_t x_ld,
                                                                   int64_t y_ld) {
+  grid_dependency_wait();
+  allow_dependents();
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -106,6 +110,8 @@ template <typename T, int NV>
 __global__ void __launch_bounds__(128) softmax_bwd_vec_kernel(const T* __restrict__ dy, const T* __restrict__ y,
                                                               T* __restrict__ dx, int64_t rows, int cols,
                                                               int64_t dy_ld, int64_t y_ld, int64_t dx_ld) {
+  grid_dependency_wait();
+  allow_dependents();
   constexpr int W = Vec16<T>::N;
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -140,6 +146,8 @@ __global__ void __launch_bounds__(128) softmax_bwd_generic_kernel(const T* __res
                                                                   const T* __restrict__ y, T* __restrict__ dx,
                                                                   int64_t rows, int cols, int64_t dy_ld,
                                                                   int64_t y_ld, int64_t dx_ld) {
+  grid_dependency_wait();
+  allow_dependents();
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -163,11 +171,11 @@ static int softmax_fwd_launch(const void* x, void* y, int64_t rows, int64_t cols
   const T* xp = (const T*)x;
   T* yp = (T*)y;
   const int nv = (int)ceil_div(cols, 32 * W);
-  if (!vec) softmax_fwd_generic_kernel<T><<<grid, 128, 0, st>>>(xp, yp, rows, (int)cols, x_ld, y_ld);
-  else if (nv <= 1) softmax_fwd_vec_kernel<T, 1><<<grid, 128, 0, st>>>(xp, yp, rows, (int)cols, x_ld, y_ld);
-  else if (nv <= 2) softmax_fwd_vec_kernel<T, 2><<<grid, 128, 0, st>>>(xp, yp, rows, (int)cols, x_ld, y_ld);
-  else if (nv <= 4) softmax_fwd_vec_kernel<T, 4><<<grid, 128, 0, st>>>(xp, yp, rows, (int)cols, x_ld, y_ld);
-  else softmax_fwd_vec_kernel<T, 8><<<grid, 128, 0, st>>>(xp, yp, rows, (int)cols, x_ld, y_ld);
+  if (!vec) launch_overlapped(softmax_fwd_generic_kernel<T>, dim3(grid), dim3(128), 0, st, xp, yp, rows, (int)cols, x_ld, y_ld);
+  else if (nv <= 1) launch_overlapped(softmax_fwd_vec_kernel<T, 1>, dim3(grid), dim3(128), 0, st, xp, yp, rows, (int)cols, x_ld, y_ld);
+  else if (nv <= 2) launch_overlapped(softmax_fwd_vec_kernel<T, 2>, dim3(grid), dim3(128), 0, st, xp, yp, rows, (int)cols, x_ld, y_ld);
+  else if (nv <= 4) launch_overlapped(softmax_fwd_vec_kernel<T, 4>, dim3(grid), dim3(128), 0, st, xp, yp, rows, (int)cols, x_ld, y_ld);
+  else launch_overlapped(softmax_fwd_vec_kernel<T, 8>, dim3(grid), dim3(128), 0, st, xp, yp, rows, (int)cols, x_ld, y_ld);
   return launched("softmax_fwd");
 }
 
@@ -181,10 +189,10 @@ static int softmax_bwd_launch(const void* dy, const void* y, void* dx, int64_t r
   const T *gp = (const T*)dy, *pp = (const T*)y;
   T* op = (T*)dx;
   const int nv = (int)ceil_div(cols, 32 * W);
-  if (!vec) softmax_bwd_generic_kernel<T><<<grid, 128, 0, st>>>(gp, pp, op, rows, (int)cols, dy_ld, y_ld, dx_ld);
-  else if (nv <= 1) softmax_bwd_vec_kernel<T, 1><<<grid, 128, 0, st>>>(gp, pp, op, rows, (int)cols, dy_ld, y_ld, dx_ld);
-  else if (nv <= 2) softmax_bwd_vec_kernel<T, 2><<<grid, 128, 0, st>>>(gp, pp, op, rows, (int)cols, dy_ld, y_ld, dx_ld);
-  else softmax_bwd_vec_kernel<T, 4><<<grid, 128, 0, st>>>(gp, pp, op, rows, (int)cols, dy_ld, y_ld, dx_ld);
+  if (!vec) launch_overlapped(softmax_bwd_generic_kernel<T>, dim3(grid), dim3(128), 0, st, gp, pp, op, rows, (int)cols, dy_ld, y_ld, dx_ld);
+  else if (nv <= 1) launch_overlapped(softmax_bwd_vec_kernel<T, 1>, dim3(grid), dim3(128), 0, st, gp, pp, op, rows, (int)cols, dy_ld, y_ld, dx_ld);
+  else if (nv <= 2) launch_overlapped(softmax_bwd_vec_kernel<T, 2>, dim3(grid), dim3(128), 0, st, gp, pp, op, rows, (int)cols, dy_ld, y_ld, dx_ld);
+  else launch_overlapped(softmax_bwd_vec_kernel<T, 4>, dim3(grid), dim3(128), 0, st, gp, pp, op, rows, (int)cols, dy_ld, y_ld, dx_ld);
   return launched("softmax_bwd");
 }
 

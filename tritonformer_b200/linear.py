@@ -60,14 +60,15 @@ ACCUMULATE_INTO_GRAD = False
 _workspaces = {}
 
 
-def _splitk_workspace(device, nbytes):
-    """Per-device fp32 scratch for the split-K path of small-output GEMMs (grown on demand).
-
-    The library expects it zero-filled and hands it back zero-filled, so it is cleared only here."""
-    ws = _workspaces.get(device)
-    if ws is None or ws.numel() < nbytes:
-        ws = torch.zeros(max(nbytes, 32 << 20), device=device, dtype=torch.uint8)
-        _workspaces[device] = ws
+def _gemm_workspace(device, stream):
+    """Scratch the GEMM uses to share the contraction of a tile between SMs: arrival counters (kept zero by
+    the kernels, so cleared only here) and one fp32 partial tile per SM.  One per device and stream, since calls
+    that share it must be stream-ordered."""
+    key = (device, stream)
+    ws = _workspaces.get(key)
+    if ws is None:
+        ws = torch.zeros(int(_lib.lib.tfb_gemm_workspace_bytes()), device=device, dtype=torch.uint8)
+        _workspaces[key] = ws
     return ws
 
 
@@ -81,14 +82,14 @@ def gemm(a, a_sm, a_sk, b, b_sk, b_sn, m, n, k, bias=None, relu=False, out=None,
     if accumulate:
         addend = out
     path = ctypes.c_int(0)
-    ws = _splitk_workspace(a.device, m * n * 4) if (m * n <= (8 << 20) and k >= 2048) else None
+    stream = _lib.stream_ptr(a.device)
+    ws = _gemm_workspace(a.device, stream)
     _lib.check(_lib.lib.tfb_gemm_fused(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), bias.data_ptr() if bias is not None else None,
         addend.data_ptr() if addend is not None else None, addend.stride(0) if addend is not None else 0,
         mask.data_ptr() if mask is not None else None, mask.stride(0) if mask is not None else 0,
         m, n, k, a_sm, a_sk, b_sk, b_sn, out.stride(0), 1 if relu else 0, _lib.dtype_code(a.dtype),
-        ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
-        _lib.stream_ptr(a.device), ctypes.byref(path)))
+        ws.data_ptr(), ws.numel(), stream, ctypes.byref(path)))
     if PROFILE is not None:
         PROFILE.append({"m": m, "n": n, "k": k, "a": (a_sm, a_sk), "b": (b_sk, b_sn), "bias": bias is not None,
                         "relu": bool(relu), "addend": addend is not None, "accumulate": addend is out,
