@@ -116,14 +116,16 @@ STREAM_K_SHAPES = [
     (4100, 1544, 704),     # 231 tiles, ragged in M, N and K
     (128, 136, 1024),      # two tiles, few k-blocks
     (128, 64, 64),         # a single tile and k-block: nothing to share
+    (1024, 3072, 4096),    # 48 tiles of 256 x 256 for 74 pairs of SMs: CTA-pair kernel, K shared between pairs
+    (2300, 2056, 1088),    # 81 ragged pair tiles: CTA-pair kernel, whole tiles
 ]
 
 
 @pytest.mark.parametrize("shape", STREAM_K_SHAPES)
-@pytest.mark.parametrize("layout", ["weight_grad", "forward"])
+@pytest.mark.parametrize("layout", ["weight_grad", "forward", "input_grad"])
 def test_stream_k_gemm_matches_fp32_and_is_deterministic(shape, layout):
-    """Tile counts that do not fill whole waves of SMs share the contraction of some tiles between SMs through
-    fp32 partial tiles in the workspace.  The result must match fp32, must not depend on timing, must agree with
+    """Outputs with fewer tiles than SMs (or pairs of SMs) share the contraction of their tiles between SMs through
+    fp32 partial tiles in the workspace; large outputs run on the CTA-pair kernel.  The result must match fp32, must not depend on timing, must agree with
     the same kernel run without a workspace (whole tiles only), and the arrival counters must be zero again."""
     import ctypes
     from tritonformer_b200 import _lib, linear as lin
@@ -135,21 +137,26 @@ def test_stream_k_gemm_matches_fp32_and_is_deterministic(shape, layout):
     else:
         a = _r(m, k)
         a_sm, a_sk, a32 = k, 1, a.float()
-    b = _r(k, n, scale=k ** -0.5)
+    if layout == "input_grad":
+        b = _r(n, k, scale=k ** -0.5)      # B(k, n) = b[n, k]  (K-major, a weight read transposed)
+        b_sk, b_sn, b32 = 1, k, b.float().t()
+    else:
+        b = _r(k, n, scale=k ** -0.5)
+        b_sk, b_sn, b32 = n, 1, b.float()
     bias, old, mask = _r(n), _r(m, n), _r(m, n)
-    want = a32 @ b.float()
-    got1 = lin.gemm(a, a_sm, a_sk, b, n, 1, m, n, k)
-    got2 = lin.gemm(a, a_sm, a_sk, b, n, 1, m, n, k)
+    want = a32 @ b32
+    got1 = lin.gemm(a, a_sm, a_sk, b, b_sk, b_sn, m, n, k)
+    got2 = lin.gemm(a, a_sm, a_sk, b, b_sk, b_sn, m, n, k)
     assert torch.equal(got1, got2)
     assert norm_rel(got1, want) < 1e-3
     plain = torch.empty_like(got1)
-    _lib.check(_lib.lib.tfb_gemm(a.data_ptr(), b.data_ptr(), plain.data_ptr(), None, m, n, k, a_sm, a_sk, n, 1, n,
-                                 0, 0, _lib.dtype_code(a.dtype), _lib.stream_ptr(a.device), None))
+    _lib.check(_lib.lib.tfb_gemm(a.data_ptr(), b.data_ptr(), plain.data_ptr(), None, m, n, k, a_sm, a_sk, b_sk, b_sn,
+                                 n, 0, 0, _lib.dtype_code(a.dtype), _lib.stream_ptr(a.device), None))
     assert_close(got1, plain, 2e-3, "with and without workspace", rtol=2e-3)
     acc = old.clone()
-    lin.gemm(a, a_sm, a_sk, b, n, 1, m, n, k, out=acc, accumulate=True)
+    lin.gemm(a, a_sm, a_sk, b, b_sk, b_sn, m, n, k, out=acc, accumulate=True)
     assert norm_rel(acc, want + old.float()) < 1e-3
-    full = lin.gemm(a, a_sm, a_sk, b, n, 1, m, n, k, bias=bias, relu=True, addend=old, mask=mask)
+    full = lin.gemm(a, a_sm, a_sk, b, b_sk, b_sn, m, n, k, bias=bias, relu=True, addend=old, mask=mask)
     assert_close(full, (torch.relu(want + bias.float()) + old.float()) * (mask > 0), 1e-2, "epilogue", rtol=2e-3)
     ws = lin._gemm_workspace(a.device, _lib.stream_ptr(a.device))
     torch.cuda.synchronize()

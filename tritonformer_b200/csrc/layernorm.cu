@@ -239,121 +239,172 @@ __global__ void __launch_bounds__(MAXT) ln_bwd_kernel(
   }
 }
 
-// Backward for rows of at most 1024 elements: one warp per row, no block-wide barrier in the row
-// loop.  A lane owns the 16-byte vectors lane, lane+32, ... of the row (like the forward kernel), so
-// the two row reductions are warp shuffles, and it keeps the dalpha / dbeta sums of its columns in
-// registers across all the rows its warp visits.  The next row's vectors are loaded before the
-// current row is reduced.  At the end the warps of a CTA fold their sums in shared memory and the CTA
-// writes one partial row.
-template <typename T, int NV>
-__global__ void __launch_bounds__(256, 1) ln_bwd_warp_kernel(
+// Backward for vectorisable rows of at most 2048 elements: G warps share a row, a lane owns ONE
+// 16-byte vector of it, so a thread keeps only 8 columns of alpha and of the dalpha / dbeta sums in
+// registers.  Each step handles two rows of the row group.  The vectors of the following steps are
+// already on their way: every lane copies its own 16-byte pieces into a private slot of a
+// shared-memory ring with cp.async (LN_DEPTH steps deep, no registers held, no barrier needed since
+// a lane reads back only what it copied itself), which keeps about 100 KB per SM in flight - what
+// the HBM latency needs at this bandwidth.  The two row sums are reduced by warp shuffles and
+// exchanged between the G warps through shared memory behind a named barrier (double-buffered).
+constexpr int LN_DEPTH = 4;
+constexpr int LN_RING_BYTES = 8 * LN_DEPTH * 2 * 3 * 32 * 16;  // warps x steps x rows x tensors x lanes x 16 B
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)),
+               "l"(gsrc)
+               : "memory");
+}
+
+template <typename T, int G>
+__global__ void __launch_bounds__(256, 2) ln_bwd_split_kernel(
     const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ alpha,
     const float* __restrict__ mean, const float* __restrict__ rstd, T* __restrict__ dx,
     float* __restrict__ partials, int64_t rows, int d, int64_t dy_ld, int64_t x_ld, int64_t dx_ld,
     const T* __restrict__ dres, int64_t dres_ld) {
   grid_dependency_wait();
   allow_dependents();
-  extern __shared__ float fold[];  // [2][d]
+  constexpr int RG = 8 / G;  // row groups per CTA
+  extern __shared__ __align__(16) uint8_t ln_smem[];
+  uint4* ring = reinterpret_cast<uint4*>(ln_smem);                  // [warp][step][row][tensor][lane]
+  float* fold = reinterpret_cast<float*>(ln_smem + LN_RING_BYTES);  // [2][d]
+  __shared__ float4 xch[RG][2][G];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int part = warp % G, rg = warp / G;
   const int nvec = d >> 3;
-  for (int c = threadIdx.x; c < 2 * d; c += blockDim.x) fold[c] = 0.f;
+  const int per = (nvec + G - 1) / G;  // vectors per warp, at most 32
+  const int c = part * per + lane;
+  const bool has = lane < per && c < nvec;
+  for (int i = threadIdx.x; i < 2 * d; i += blockDim.x) fold[i] = 0.f;
   __syncthreads();
 
-  float a[NV][8], acc_a[NV][8], acc_b[NV][8];
+  float a[8], acc_a[8], acc_b[8];
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int c = i * 32 + lane;
-    if (c < nvec) unpack8<T>(__ldg(reinterpret_cast<const uint4*>(alpha) + c), a[i]);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) acc_a[i][j] = acc_b[i][j] = 0.f;
-  }
+  for (int j = 0; j < 8; ++j) a[j] = acc_a[j] = acc_b[j] = 0.f;
+  if (has) unpack8<T>(__ldg(reinterpret_cast<const uint4*>(alpha) + c), a);
   const float inv_d = 1.f / (float)d;
-  const int64_t stride = (int64_t)gridDim.x * (blockDim.x >> 5);
-  int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
+  const int64_t stride = (int64_t)gridDim.x * RG;  // rows between the two rows of a step
+  const int64_t step_rows = 2 * stride;
+  int64_t row = (int64_t)blockIdx.x * RG + rg;
+  uint4* mine = ring + (size_t)warp * LN_DEPTH * 2 * 3 * 32 + lane;
 
-  uint4 cx[NV], cg[NV], cr[NV], nx[NV], ng[NV], nr[NV];
-  auto fetch = [&](int64_t r, uint4 (&vx)[NV], uint4 (&vg)[NV], uint4 (&vr)[NV]) {
+  // one commit group per step, issued by every lane (empty groups keep the count uniform)
+  auto issue = [&](int64_t r0, int slot) {
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const int c = i * 32 + lane;
-      if (c < nvec) {
-        vx[i] = ld_stream16(reinterpret_cast<const uint4*>(x + r * x_ld) + c);
-        vg[i] = ld_stream16(reinterpret_cast<const uint4*>(dy + r * dy_ld) + c);
-        if (dres) vr[i] = ld_stream16(reinterpret_cast<const uint4*>(dres + r * dres_ld) + c);
+    for (int k = 0; k < 2; ++k) {
+      const int64_t r = r0 + k * stride;
+      if (has && r < rows) {
+        uint4* dst = mine + ((slot * 2 + k) * 3) * 32;
+        cp_async16(dst, reinterpret_cast<const uint4*>(x + r * x_ld) + c);
+        cp_async16(dst + 32, reinterpret_cast<const uint4*>(dy + r * dy_ld) + c);
+        if (dres) cp_async16(dst + 64, reinterpret_cast<const uint4*>(dres + r * dres_ld) + c);
       }
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  if (row < rows) fetch(row, cx, cg, cr);
-  for (; row < rows; row += stride) {
-    const bool more = row + stride < rows;
-    if (more) fetch(row + stride, nx, ng, nr);
-    const float mu = __ldg(mean + row), rs = __ldg(rstd + row);
-    float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      if (i * 32 + lane < nvec) {
+  for (int s = 0; s < LN_DEPTH - 1; ++s) issue(row + s * step_rows, s);
+  // the row statistics travel one step ahead in registers (a dependent load per step otherwise)
+  float mu_next[2], rs_next[2];
+  auto fetch_stats = [&](int64_t r0) {
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int64_t r = r0 + k * stride;
+      mu_next[k] = r < rows ? __ldg(mean + r) : 0.f;
+      rs_next[k] = r < rows ? __ldg(rstd + r) : 0.f;
+    }
+  };
+  fetch_stats(row);
+  int slot = 0, parity = 0;
+  for (; row < rows; row += step_rows) {
+    issue(row + (LN_DEPTH - 1) * step_rows, (slot + LN_DEPTH - 1) % LN_DEPTH);
+    const float mu_cur[2] = {mu_next[0], mu_next[1]}, rs_cur[2] = {rs_next[0], rs_next[1]};
+    fetch_stats(row + step_rows);
+    asm volatile("cp.async.wait_group %0;" ::"n"(LN_DEPTH - 1) : "memory");  // this step's copies have landed
+    uint4 cr[2];
+    float rs[2], s1[2], s2[2];
+    float h[2][8], gg[2][8];  // normalised input and alpha-scaled gradient, kept for the second pass
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int64_t r = row + k * stride;
+      const bool live = r < rows;
+      const float mu = mu_cur[k];
+      rs[k] = rs_cur[k];
+      const float shift = -mu * rs[k];
+      s1[k] = s2[k] = 0.f;
+      if (has && live) {
+        const uint4* src = mine + ((slot * 2 + k) * 3) * 32;
         float xv[8], dv[8];
-        unpack8<T>(cx[i], xv);
-        unpack8<T>(cg[i], dv);
+        unpack8<T>(src[0], xv);
+        unpack8<T>(src[32], dv);
+        if (dres) cr[k] = src[64];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const float h = (xv[j] - mu) * rs;
-          const float gg = dv[j] * a[i][j];
-          acc_a[i][j] += dv[j] * h;
-          acc_b[i][j] += dv[j];
-          s1 += gg * h;
-          s2 += gg;
+          h[k][j] = fmaf(xv[j], rs[k], shift);
+          gg[k][j] = dv[j] * a[j];
+          acc_a[j] = fmaf(dv[j], h[k][j], acc_a[j]);
+          acc_b[j] += dv[j];
+          s1[k] = fmaf(gg[k][j], h[k][j], s1[k]);
+          s2[k] += gg[k][j];
         }
       }
     }
-    s1 = warp_sum(s1) * inv_d;
-    s2 = warp_sum(s2) * inv_d;
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const int c = i * 32 + lane;
-      if (c < nvec) {
-        // the normalised value and the scaled gradient are recomputed from the packed vectors rather
-        // than kept across the reduction: two multiplies each instead of 16 live registers per vector
-        float xv[8], dv[8], o[8];
-        unpack8<T>(cx[i], xv);
-        unpack8<T>(cg[i], dv);
+    for (int k = 0; k < 2; ++k) {
+      s1[k] = warp_sum(s1[k]);
+      s2[k] = warp_sum(s2[k]);
+    }
+    if (G > 1) {
+      // all G warps of the row group run the same number of steps, so the barrier counts match
+      if (lane == 0) xch[rg][parity][part] = make_float4(s1[0], s2[0], s1[1], s2[1]);
+      asm volatile("bar.sync %0, %1;" ::"r"(1 + rg), "r"(32 * G) : "memory");
+      float4 t = xch[rg][parity][0];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = rs * (dv[j] * a[i][j] - (xv[j] - mu) * rs * s1 - s2);
+      for (int g = 1; g < G; ++g) {
+        const float4 u = xch[rg][parity][g];
+        t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
+      }
+      s1[0] = t.x; s2[0] = t.y; s1[1] = t.z; s2[1] = t.w;
+      parity ^= 1;
+    }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int64_t r = row + k * stride;
+      if (has && r < rows) {
+        // dx = rstd * (g - h * mean(g h) - mean(g)) as two fused multiply-adds per element
+        const float k1 = -rs[k] * s1[k] * inv_d, k2 = -rs[k] * s2[k] * inv_d;
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = fmaf(rs[k], gg[k][j], fmaf(k1, h[k][j], k2));
         if (dres) {
           float e[8];
-          unpack8<T>(cr[i], e);
+          unpack8<T>(cr[k], e);
 #pragma unroll
           for (int j = 0; j < 8; ++j) o[j] += e[j];
         }
-        st_stream16(reinterpret_cast<uint4*>(dx + row * dx_ld) + c, pack8<T>(o));
+        st_stream16(reinterpret_cast<uint4*>(dx + r * dx_ld) + c, pack8<T>(o));
       }
     }
-    if (more) {
-#pragma unroll
-      for (int i = 0; i < NV; ++i) {
-        cx[i] = nx[i];
-        cg[i] = ng[i];
-        cr[i] = nr[i];
-      }
-    }
+    slot = (slot + 1) % LN_DEPTH;
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  if (has) {
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int c = i * 32 + lane;
-    if (c < nvec) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        atomicAdd(&fold[c * 8 + j], acc_a[i][j]);
-        atomicAdd(&fold[d + c * 8 + j], acc_b[i][j]);
+    for (int j = 0; j < 8; ++j) {
+      if (RG > 1) {
+        atomicAdd(&fold[c * 8 + j], acc_a[j]);
+        atomicAdd(&fold[d + c * 8 + j], acc_b[j]);
+      } else {
+        fold[c * 8 + j] = acc_a[j];
+        fold[d + c * 8 + j] = acc_b[j];
       }
     }
   }
   __syncthreads();
   float* pa = partials + (int64_t)blockIdx.x * 2 * d;
-  for (int c = threadIdx.x; c < 2 * d; c += blockDim.x) pa[c] = fold[c];
+  for (int i = threadIdx.x; i < 2 * d; i += blockDim.x) pa[i] = fold[i];
 }
 
-// out0[c] (c < split) / out1[c - split] = sum over n rows of partials[r, c]; ncols total.
 template <typename T>
 __global__ void __launch_bounds__(256) finalize_partials_kernel(
     const float* __restrict__ partials, int64_t n, int ncols, int split, T* __restrict__ out0,
@@ -397,14 +448,25 @@ static int ln_bwd_launch(const void* dy, const void* x, const void* alpha, const
   launch_overlapped(ln_bwd_kernel<T, V, MT>, dim3((unsigned)n_partials), dim3(threads), 0, st, \
       (const T*)dy, (const T*)x, (const T*)alpha, mean, rstd, (T*)dx, partials, rows, d, dy_ld, \
       x_ld, dx_ld, (const T*)dres, dres_ld)
-  if (vec && d <= 1024 && aligned16(alpha)) {
-    const size_t sm = (size_t)2 * d * sizeof(float);
+  if (vec && d <= 2048 && aligned16(alpha)) {
+    const size_t sm = (size_t)LN_RING_BYTES + (size_t)2 * d * sizeof(float);
     const T *gp = (const T*)dy, *xp = (const T*)x, *ap = (const T*)alpha, *rp = (const T*)dres;
     T* op = (T*)dx;
-    const unsigned grid = (unsigned)n_partials;
-    if (d <= 256) launch_overlapped(ln_bwd_warp_kernel<T, 1>, dim3(grid), dim3(256), sm, st, gp, xp, ap, mean, rstd, op, partials, rows, d, dy_ld, x_ld, dx_ld, rp, dres_ld);
-    else if (d <= 512) launch_overlapped(ln_bwd_warp_kernel<T, 2>, dim3(grid), dim3(256), sm, st, gp, xp, ap, mean, rstd, op, partials, rows, d, dy_ld, x_ld, dx_ld, rp, dres_ld);
-    else launch_overlapped(ln_bwd_warp_kernel<T, 4>, dim3(grid), dim3(256), sm, st, gp, xp, ap, mean, rstd, op, partials, rows, d, dy_ld, x_ld, dx_ld, rp, dres_ld);
+    const dim3 grid((unsigned)n_partials), block(256);
+#define TFB_LN_SPLIT(G)                                                                                         \
+  do {                                                                                                          \
+    static std::atomic<uint64_t> attr_done{0};                                                                  \
+    if (int rc0 = ensure_dynamic_smem(ln_bwd_split_kernel<T, G>, (int)(LN_RING_BYTES + 2 * 2048 * sizeof(float)), \
+                                      attr_done, "layernorm_bwd"))                                              \
+      return rc0;                                                                                               \
+    launch_overlapped(ln_bwd_split_kernel<T, G>, grid, block, sm, st, gp, xp, ap, mean, rstd, op, partials, rows, d, \
+                      dy_ld, x_ld, dx_ld, rp, dres_ld);                                                         \
+  } while (0)
+    if (d <= 256) TFB_LN_SPLIT(1);
+    else if (d <= 512) TFB_LN_SPLIT(2);
+    else if (d <= 1024) TFB_LN_SPLIT(4);
+    else TFB_LN_SPLIT(8);
+#undef TFB_LN_SPLIT
   } else if (vec && threads <= 256) TFB_LN_BWD(true, 256);
   else if (vec) TFB_LN_BWD(true, 1024);
   else if (threads <= 256) TFB_LN_BWD(false, 256);
