@@ -230,6 +230,30 @@ def test_overlapped_launches_match_serialised_launches(graph):
         assert norm_rel(a.float(), b.float()) < 1e-3, n
 
 
+def test_layer_runs_twelve_products():
+    """The q, k, v projections are one product forward, one for the input gradient and one for the three weight
+    gradients (the attention backward lays dq, dk, dv out as column blocks of one buffer): twelve products per
+    layer and three for the LM head."""
+    import tritonformer_b200.linear as lin
+    from tritonformer_b200.transformer import Transformer
+    cfg = _cfg(vocab_size=1024, hidden_size=256, max_position_embeddings=256, num_attention_heads=4, head_dim=64,
+               ffn_dim=1024, num_hidden_layers=2, use_linear_bias=False, attn_bias=False)
+    torch.manual_seed(0)
+    model = Transformer(cfg, device="cuda")
+    ids = torch.randint(0, 1024, (2, 256), device="cuda")
+    recs = []
+    lin.PROFILE = recs
+    try:
+        with torch.autocast("cuda", dtype=torch.float16):
+            _, loss = model(ids, ids)
+        loss.backward()
+    finally:
+        lin.PROFILE = None
+    assert len(recs) == 12 * cfg.num_hidden_layers + 3, [(r["m"], r["n"], r["k"]) for r in recs]
+    assert sum(1 for r in recs if r["n"] == 3 * 256) == 2 * cfg.num_hidden_layers      # forward, weight gradients
+    assert sum(1 for r in recs if r["k"] == 3 * 256) == cfg.num_hidden_layers          # input gradient
+
+
 def test_small_model_fp16_bias_alibi_hd32():
     cfg = _cfg(vocab_size=1000, hidden_size=192, max_position_embeddings=256, num_attention_heads=6, head_dim=32,
                ffn_dim=768, num_hidden_layers=2, use_linear_bias=True, attn_bias=True)

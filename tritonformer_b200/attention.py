@@ -102,10 +102,26 @@ def attention_forward(q, k, v, bias: _Bias):
     return out, lse, (q, k, v)
 
 
+def _are_column_blocks(q, k, v):
+    """q, k, v of shape (B, H, T, hd) are the views [.., 0:d], [.., d:2d], [.., 2d:3d] of one (B, T, 3 d) tensor."""
+    b, h, t, hd = q.shape
+    d = h * hd
+    want = (t * 3 * d, hd, 3 * d, 1)
+    es = q.element_size()
+    return (q.shape == k.shape == v.shape and q.stride() == want and k.stride() == want and v.stride() == want
+            and k.data_ptr() == q.data_ptr() + d * es and v.data_ptr() == q.data_ptr() + 2 * d * es)
+
+
 def attention_backward(d_out, out, q, k, v, lse, bias: _Bias):
     b, h, t, hd = q.shape
     d_out = _unit_inner(d_out.to(q.dtype))
-    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    if _are_column_blocks(q, k, v):
+        # q, k, v are column blocks of one (B, T, 3 H hd) projection output: lay their gradients out the same
+        # way, so that the projection's backward is one product over the whole block
+        grads = torch.empty((b, t, 3, h, hd), device=q.device, dtype=q.dtype)
+        dq, dk, dv = (grads[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    else:
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     nbytes = _lib.lib.tfb_attention_bwd_scratch_bytes(b, h, t, hd)
     scratch = torch.empty((nbytes,), device=q.device, dtype=torch.uint8)
     path = ctypes.c_int(0)

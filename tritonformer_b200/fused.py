@@ -4,8 +4,8 @@ these steps as its own kernel).  Same arithmetic as the plain Functions, fewer p
 * `LayerNormFork`   (y, r) = (LayerNorm(x), x): the pre-LN fork.  Its backward adds the gradient that
                     arrives through the residual branch inside the LayerNorm backward kernel.
 * `LinearResidual`  x @ W (+ b) + residual with the add in the GEMM epilogue.
-* `QKVProjection`   the three projections of one input; the backward chains the three input-gradient
-                    products through the GEMM epilogue's addend instead of summing them afterwards.
+* `QKVProjection`   the three projections of one input as one product with the concatenated weight; the
+                    backward is one product for the input gradient and one for the three weight gradients.
 * `MLPResidual`     relu(x W1 + b1) W2 + b2 + residual; the backward applies the ReLU mask in the
                     epilogue of the product that yields the hidden gradient.
 """
@@ -60,27 +60,81 @@ class LinearResidual(Function):
         return dx, dw, db, dy
 
 
+def _adjacent_columns(parts, width):
+    """True if `parts` are the column blocks [0, w), [w, 2w), ... of one row-major matrix of `width` columns."""
+    first = parts[0]
+    es = first.element_size()
+    for i, t in enumerate(parts):
+        if t is None or t.dtype != first.dtype or t.shape != first.shape or t.stride(-1) != 1:
+            return False
+        if t.data_ptr() != first.data_ptr() + i * first.shape[-1] * es:
+            return False
+        lead = t.reshape(-1, t.shape[-1]) if t.dim() > 2 else t
+        if lead.stride(0) != width or (t.dim() > 2 and lead.data_ptr() != t.data_ptr()):
+            return False
+    return True
+
+
 class QKVProjection(Function):
+    """q, k, v = x Wq, x Wk, x Wv as ONE product with the concatenated weight [Wq | Wk | Wv]: the three outputs
+    are column blocks of one (rows, 3 d) buffer.  When the three incoming gradients are again column blocks of
+    one buffer (the attention backward allocates them that way), the input gradient and the three weight
+    gradients are one product each as well; otherwise the input-gradient products are chained through the GEMM
+    epilogue's addend."""
+
     @staticmethod
     @amp_forward
     def forward(ctx, x, wq, wk, wv):
-        ctx.save_for_backward(x, wq, wk, wv)
-        return (L.linear_forward(x, wq, None, False), L.linear_forward(x, wk, None, False),
-                L.linear_forward(x, wv, None, False))
+        same = wq.shape == wk.shape == wv.shape and wq.dtype == wk.dtype == wv.dtype
+        if not same:
+            ctx.fused = False
+            ctx.save_for_backward(x, wq, wk, wv)
+            return (L.linear_forward(x, wq, None, False), L.linear_forward(x, wk, None, False),
+                    L.linear_forward(x, wv, None, False))
+        ctx.fused = True
+        d = wq.shape[1]
+        w = torch.cat((wq, wk, wv), dim=1)  # (in, 3 d)
+        y = L.linear_forward(x, w, None, False)
+        ctx.save_for_backward(x, w, wq, wk, wv)
+        return y[..., :d], y[..., d:2 * d], y[..., 2 * d:]
 
     @staticmethod
     @amp_backward
     def backward(ctx, dq, dk, dv):
-        x, wq, wk, wv = ctx.saved_tensors
+        need = ctx.needs_input_grad
+        if ctx.fused:
+            x, w, wq, wk, wv = ctx.saved_tensors
+            d = wq.shape[1]
+            grads = [g.to(x.dtype) if g is not None else None for g in (dq, dk, dv)]
+            if all(g is not None for g in grads) and _adjacent_columns(grads, 3 * d):
+                rows = x.numel() // x.shape[-1]
+                dy = torch.as_strided(grads[0], (rows, 3 * d), (3 * d, 1))
+                dx = L.input_grad(dy, w, x.shape) if need[0] else None
+                dws = [None, None, None]
+                if any(need[1:4]):
+                    dw = L.weight_grad(x, dy, w)  # (in, 3 d); w is a temporary, so this is a fresh tensor
+                    for i, p in enumerate((wq, wk, wv)):
+                        if not need[1 + i]:
+                            continue
+                        part = dw[:, i * d:(i + 1) * d]
+                        if L.ACCUMULATE_INTO_GRAD and p.grad is not None and p.grad.dtype == part.dtype \
+                                and p.grad.shape == part.shape:
+                            p.grad.add_(part)
+                        else:
+                            dws[i] = part
+                return (dx, *dws)
+            ws = (wq, wk, wv)
+        else:
+            x, *ws = ctx.saved_tensors
+            grads = (dq, dk, dv)
         dx = None
-        if ctx.needs_input_grad[0]:
-            for g, w in ((dq, wq), (dk, wk), (dv, wv)):
+        if need[0]:
+            for g, w_ in zip(grads, ws):
                 if g is not None:
-                    dx = L.input_grad(g.to(x.dtype), w, x.shape, addend=dx, out=dx)
-        grads = [L.weight_grad(x, g.to(x.dtype), w) if (g is not None and need) else None
-                 for g, w, need in ((dq, wq, ctx.needs_input_grad[1]), (dk, wk, ctx.needs_input_grad[2]),
-                                    (dv, wv, ctx.needs_input_grad[3]))]
-        return (dx, *grads)
+                    dx = L.input_grad(g.to(x.dtype), w_, x.shape, addend=dx, out=dx)
+        dws = [L.weight_grad(x, g.to(x.dtype), w_) if (g is not None and n) else None
+               for g, w_, n in zip(grads, ws, need[1:4])]
+        return (dx, *dws)
 
 
 class MLPResidual(Function):
