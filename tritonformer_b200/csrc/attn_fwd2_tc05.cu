@@ -13,12 +13,19 @@
 // applies scale / ALiBi / causal mask in the log2 domain, and updates the running maximum lazily
 // (the accumulator row is rescaled only when the maximum grew by more than 2^8; P stays below 2^8,
 // inside fp16/bf16 range), so in the steady state no TMEM round trip of O is needed.
+// For tiles below the diagonal the softmax is a single pass against the maximum of the earlier tiles
+// (redone in two passes if the tile's maximum exceeds it by more than the threshold), with one
+// exponential in four evaluated on the FMA pipe.  P has two shared-memory buffers per tile and the
+// tensor core is given the tile's NEXT scores before the product of the current P with V, so the
+// softmax warps of a tile go from one step to the next without waiting for that product.
 // TMEM columns: [0,128) S_A, [128,256) S_B, [256,320) O_A, [320,384) O_B.
 #include "attn.cuh"
 #include "tc05.cuh"
 #include <type_traits>
 
 namespace tfb {
+
+extern std::atomic<int> g_attn_debug;
 
 namespace {
 
@@ -31,13 +38,14 @@ constexpr int F2_TILE_BYTES = 16384;  // 128 rows x 64 x 2 B
 constexpr int F2_OFF_Q = 0;                        // [2]
 constexpr int F2_OFF_K = 2 * F2_TILE_BYTES;        // [2]
 constexpr int F2_OFF_V = 4 * F2_TILE_BYTES;        // [2]
-constexpr int F2_OFF_P = 6 * F2_TILE_BYTES;        // [2] x 32 KB
-constexpr int F2_OFF_BAR = F2_OFF_P + 2 * 32768;
+constexpr int F2_OFF_P = 6 * F2_TILE_BYTES;        // [2 tiles][2 buffers] x 32 KB
+constexpr int F2_OFF_BAR = F2_OFF_P + 4 * 32768;
 constexpr int F2_SMEM_BYTES = F2_OFF_BAR + 256 + 1024;
 constexpr int F2_COL_S = 0, F2_COL_O = 256;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct F2Params {
+  int debug;  // bit 1: cycle counters of one softmax warp and the MMA thread (tfb_debug_set key 2)
   void* out;
   float* lse;
   int64_t so_b, so_h, so_t;
@@ -61,6 +69,23 @@ __device__ __forceinline__ float alibi_term2(int mode, float slope, int dist) {
 
 }  // namespace
 
+static __device__ unsigned long long g_prof_f2[16];
+#define F2_PROF(idx, t0, t1) do { if (prof) atomicAdd(&g_prof_f2[idx], (unsigned long long)((t1) - (t0))); } while (0)
+
+// 2^x on the FMA pipe, for a share of the exponentials (the exponential unit gives 16 results per
+// clock and SM and is the busiest pipe of this kernel).  x is split into a rounded integer and a
+// fraction in [-0.5, 0.5] with the 1.5 * 2^23 constant; a cubic fitted to 2^f (relative error 7.5e-5,
+// far below the 16-bit rounding of P) is scaled by adding the integer to the exponent field.
+__device__ __forceinline__ float ex2_fma(float x) {
+  x = fmaxf(x, -125.f);
+  const float xr = x + 12582912.f;
+  const float f = x - (xr - 12582912.f);
+  float q = fmaf(f, 0.0551716685f, 0.2426111251f);
+  q = fmaf(q, f, 0.6932609677f);
+  q = fmaf(q, f, 0.9999280572f);
+  return __int_as_float(__float_as_int(q) + (__float_as_int(xr) << 23));
+}
+
 template <typename T, bool BIAS>
 __global__ void __launch_bounds__(F2_THREADS, 1) attn_fwd2_tc05_kernel(const __grid_constant__ CUtensorMap tmQ,
                                                                        const __grid_constant__ CUtensorMap tmK,
@@ -76,8 +101,8 @@ __global__ void __launch_bounds__(F2_THREADS, 1) attn_fwd2_tc05_kernel(const __g
   uint64_t* v_empty = bars + 7;   // [2]
   uint64_t* s_full = bars + 9;    // [2 tiles] scores of the tile are in TMEM
   uint64_t* p_full = bars + 11;   // [2 tiles] probabilities in smem, accumulator rescaled
-  uint64_t* pv_done = bars + 13;  // [2 tiles] P·V of the tile retired
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 16);
+  uint64_t* pv_done = bars + 13;  // [2 tiles][2 P buffers] the P·V that read the buffer has retired
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 18);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -99,7 +124,8 @@ __global__ void __launch_bounds__(F2_THREADS, 1) attn_fwd2_tc05_kernel(const __g
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 4);
-      mbar_init(&pv_done[i], 1);
+      mbar_init(&pv_done[2 * i], 1);
+      mbar_init(&pv_done[2 * i + 1], 1);
     }
     mbar_fence_init();
   }
@@ -150,10 +176,14 @@ __global__ void __launch_bounds__(F2_THREADS, 1) attn_fwd2_tc05_kernel(const __g
       auto issue_s = [&](int x, int j) -> bool {
         const int st = j & 1;
         if (k_ready < j) {
+          const bool prof = (p.debug & 2) != 0;
+          const long long m0 = clock64();
           if (!mbar_wait(&k_full[st], (j >> 1) & 1, 0x3400 | st, abort_flag)) return false;
+          F2_PROF(8, m0, clock64());
           k_ready = j;
         }
         tc_fence_after();
+        const long long i0 = clock64();
         const uint32_t sq = smem_u32(smem + F2_OFF_Q + x * F2_TILE_BYTES);
         const uint32_t sk = smem_u32(smem + F2_OFF_K + st * F2_TILE_BYTES);
 #pragma unroll
@@ -164,26 +194,32 @@ __global__ void __launch_bounds__(F2_THREADS, 1) attn_fwd2_tc05_kernel(const __g
         // K_j is free once the last query tile that attends to it has been multiplied
         const bool last_user = (x == 1) || !active(1, j);
         if (last_user) tc_commit(&k_empty[st]);
+        if (p.debug & 2) atomicAdd(&g_prof_f2[10], (unsigned long long)(clock64() - i0));
         return true;
       };
       // O_x += P_x(j) V_j
       auto issue_pv = [&](int x, int j) -> bool {
         const int st = j & 1;
-        if (!mbar_wait(&p_full[x], j & 1, 0x3500 | x, abort_flag)) return false;
+        const bool prof = (p.debug & 2) != 0;
+        const long long m1 = clock64();
         if (v_ready < j) {
           if (!mbar_wait(&v_full[st], (j >> 1) & 1, 0x3600 | st, abort_flag)) return false;
           v_ready = j;
         }
+        F2_PROF(7, m1, clock64());
+        if (prof) atomicAdd(&g_prof_f2[9], 1ull);
         tc_fence_after();
-        const uint32_t sp = smem_u32(smem + F2_OFF_P + x * 32768);
+        const long long i1 = clock64();
+        const uint32_t sp = smem_u32(smem + F2_OFF_P + (x * 2 + (j & 1)) * 32768);
         const uint32_t sv = smem_u32(smem + F2_OFF_V + st * F2_TILE_BYTES);
 #pragma unroll
         for (int s = 0; s < F2_TILE / 16; ++s)
           tc_mma_ss(tmem_base + F2_COL_O + x * F2_HD, smem_desc_sw128(sp + (s / 4) * 16384 + (s % 4) * 32, 16, 1024),
                     smem_desc_sw128(sv + s * 2048, 16384, 1024), idesc_o, (j | s) ? 1u : 0u);
-        tc_commit(&pv_done[x]);
+        tc_commit(&pv_done[2 * x + (j & 1)]);
         const bool last_user = (x == 1) || !active(1, j);
         if (last_user) tc_commit(&v_empty[st]);
+        if (p.debug & 2) atomicAdd(&g_prof_f2[11], (unsigned long long)(clock64() - i1));
         return true;
       };
       if (ok) ok = issue_s(0, 0);
@@ -191,8 +227,16 @@ __global__ void __launch_bounds__(F2_THREADS, 1) attn_fwd2_tc05_kernel(const __g
       for (int j = 0; j <= jmax && ok; ++j) {
         for (int x = 0; x < 2 && ok; ++x) {
           if (!active(x, j)) continue;
-          ok = issue_pv(x, j);
+          // P_x(j) is complete and every read of S_x(j) has been made: the next scores of the tile go
+          // first (its softmax warps wait for nothing else), the product with V behind them
+          {
+            const bool prof = (p.debug & 2) != 0;
+            const long long m0 = clock64();
+            ok = mbar_wait(&p_full[x], j & 1, 0x3500 | x, abort_flag);
+            F2_PROF(6, m0, clock64());
+          }
           if (ok && active(x, j + 1)) ok = issue_s(x, j + 1);
+          if (ok) ok = issue_pv(x, j);
         }
       }
     }
@@ -210,7 +254,7 @@ __global__ void __launch_bounds__(F2_THREADS, 1) attn_fwd2_tc05_kernel(const __g
       const uint32_t o_addr = lane_addr + F2_COL_O + x * F2_HD;
       const float c2 = p.scale * kLog2e2;
       const float slope = p.bias_mode ? p.slopes[h] : 0.f;
-      uint8_t* sp = smem + F2_OFF_P + x * 32768;
+      uint8_t* sp_base = smem + F2_OFF_P + x * 2 * 32768;
       float m_run = -INFINITY;   // true running maximum
       float m_used = -INFINITY;  // maximum the accumulator and the running sum are expressed against
       float l_run = 0.f;
@@ -218,9 +262,68 @@ __global__ void __launch_bounds__(F2_THREADS, 1) attn_fwd2_tc05_kernel(const __g
       for (int j = 0; j <= jlast && ok; ++j) {
         const int j0 = j * F2_TILE;
         const bool diag = (j == jlast);
+        uint8_t* sp = sp_base + (j & 1) * 32768;  // P buffers alternate, so P(j) never waits for P(j-1)·V
         const bool plain = !BIAS && !diag;  // scores need only the common scale
+        const bool prof = (p.debug & 2) && warp == 2 && lane == 0;
+        const long long w0 = clock64();
         if (!mbar_wait(&s_full[x], j & 1, 0x3700 | x, abort_flag)) { ok = false; break; }
+        const long long w1 = clock64();
+        F2_PROF(1, w0, w1);
+        if (prof) atomicAdd(&g_prof_f2[0], 1ull);
         tc_fence_after();
+        // ---- single pass for tiles below the diagonal once a maximum is known: p = 2^(s - m_used)
+        // with the maximum of the EARLIER tiles, the row maximum of this tile tracked alongside.  If
+        // that exceeds m_used by more than the rescale threshold (rare after the first tiles) the
+        // tile is redone by the two passes below; otherwise O and the running sum keep their scale.
+        // The scores of this tile were issued after the previous P·V of the tile, so P's buffer is
+        // free as soon as they have landed.
+        bool done = false;
+        if (plain && j > 0) {
+          // the product that read this P buffer two steps ago (long retired)
+          if (j >= 2 && !mbar_wait(&pv_done[2 * x + (j & 1)], ((j - 2) >> 1) & 1, 0x3a00 | x, abort_flag)) {
+            ok = false;
+            break;
+          }
+          float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+          float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+          const float neg_m = -m_used;
+          uint32_t buf[2][32];
+          tmem_ld32(s_addr, buf[0]);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            tc_wait_ld();
+            if (c < 3) tmem_ld32(s_addr + (c + 1) * 32, buf[(c + 1) & 1]);
+            const uint32_t* v = buf[c & 1];
+            float g[32];
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              const float sv = __uint_as_float(v[e]);
+              mx4[e & 3] = fmaxf(mx4[e & 3], sv);
+              const float t = fmaf(sv, c2, neg_m);
+              g[e] = (e & 3) == 3 ? ex2_fma(t) : ex2_approx(t);  // one exponential in four on the FMA pipe
+            }
+#pragma unroll
+            for (int e = 0; e < 32; ++e) ls4[e & 3] += g[e];
+#pragma unroll
+            for (int v4 = 0; v4 < 4; ++v4) {
+              float h8[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) h8[e] = g[v4 * 8 + e];
+              const int cc = c * 4 + v4;
+              uint8_t* dst = sp + (cc >> 3) * 16384 + r * 128 + (((cc & 7) ^ (r & 7)) << 4);
+              *reinterpret_cast<uint4*>(dst) = pack8<T>(h8);
+            }
+          }
+          const float m_tile = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * c2;
+          if (!__any_sync(0xffffffffu, (m_tile - m_used) > kRescaleThreshold)) {
+            m_run = fmaxf(m_run, m_tile);
+            l_run += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+            done = true;
+          }
+          F2_PROF(2, w1, clock64());
+          if (prof && done) atomicAdd(&g_prof_f2[3], 1ull);
+        }
+        if (!done) {
         // ---- pass 1: row maximum (four independent chains; the next chunk is in flight meanwhile)
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
         {
@@ -250,7 +353,10 @@ __global__ void __launch_bounds__(F2_THREADS, 1) attn_fwd2_tc05_kernel(const __g
         if (plain) mx *= c2;  // c2 > 0: scaling commutes with the maximum
         m_run = fmaxf(m_run, mx);
         // the previous P·V of this tile must have retired before P's buffer or O is touched
-        if (j > 0 && !mbar_wait(&pv_done[x], (j - 1) & 1, 0x3800 | x, abort_flag)) { ok = false; break; }
+        if (j > 0 && !mbar_wait(&pv_done[2 * x + ((j - 1) & 1)], ((j - 1) >> 1) & 1, 0x3800 | x, abort_flag)) {
+          ok = false;
+          break;
+        }
         if (j == 0) {
           m_used = m_run;
         } else {
@@ -310,12 +416,16 @@ __global__ void __launch_bounds__(F2_THREADS, 1) attn_fwd2_tc05_kernel(const __g
           }
         }
         l_run += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+        }  // two-pass path
+        const long long w2 = clock64();
         tc_fence_before();
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[x]);
+        F2_PROF(4, w1, w2);
+        F2_PROF(5, w2, clock64());
       }
-      if (ok && mbar_wait(&pv_done[x], jlast & 1, 0x3900 | x, abort_flag)) {
+      if (ok && mbar_wait(&pv_done[2 * x + (jlast & 1)], (jlast >> 1) & 1, 0x3900 | x, abort_flag)) {
         tc_fence_after();
         const float inv = 1.f / l_run;
         T* orow = reinterpret_cast<T*>(p.out) + b * p.so_b + h * p.so_h + (int64_t)i * p.so_t;
@@ -353,6 +463,15 @@ __global__ void __launch_bounds__(F2_THREADS, 1) attn_fwd2_tc05_kernel(const __g
 // ------------------------------------------------------------------------------- host side
 int attn_fwd2_tc05_status(int reset) { return read_dev_status(reset); }
 
+// Copies the 16 cycle counters to the host and clears them.
+int attn_fwd2_tc05_counters(unsigned long long* out) {
+  cudaDeviceSynchronize();
+  if (cudaMemcpyFromSymbol(out, g_prof_f2, sizeof(unsigned long long) * 16) != cudaSuccess) return -1;
+  unsigned long long z[16] = {0};
+  cudaMemcpyToSymbol(g_prof_f2, z, sizeof(z));
+  return 0;
+}
+
 template <typename T>
 static int fwd2_launch(const AttnArgs& a, int dtype, cudaStream_t st) {
   CUtensorMap tq, tk, tv;
@@ -374,6 +493,7 @@ static int fwd2_launch(const AttnArgs& a, int dtype, cudaStream_t st) {
   F2Params p;
   p.out = a.out; p.lse = a.lse; p.so_b = a.so.b; p.so_h = a.so.h; p.so_t = a.so.t;
   p.H = a.H; p.T = a.T; p.scale = a.scale; p.bias_mode = a.bias_mode; p.slopes = a.slopes;
+  p.debug = g_attn_debug.load();
   static std::atomic<uint64_t> done_plain{0}, done_bias{0};
   if ((rc = ensure_dynamic_smem(attn_fwd2_tc05_kernel<T, false>, F2_SMEM_BYTES, done_plain, "attention_fwd(tcgen05)")))
     return rc;

@@ -29,6 +29,7 @@ int attn_bwd_tc05_status(int reset);
 int attn_fwd2_tc05_status(int reset);
 int attn_bwd_tc05_counters(unsigned long long* out);
 int gemm_pair_counters(int cta, unsigned long long* out);
+int attn_fwd2_tc05_counters(unsigned long long* out);
 std::atomic<int> g_counter_select{-1};
 }  // namespace tfb
 
@@ -50,6 +51,7 @@ extern "C" int tfb_device_status(int reset) {
 
 extern "C" int tfb_debug_counters(unsigned long long* out16) {
   const int sel = g_counter_select.load();
+  if (sel == -2) return attn_fwd2_tc05_counters(out16);
   return sel >= 0 ? gemm_pair_counters(sel, out16) : attn_bwd_tc05_counters(out16);
 }
 
