@@ -15,10 +15,11 @@
 // inside fp16/bf16 range), so in the steady state no TMEM round trip of O is needed.
 // For tiles below the diagonal the softmax is a single pass against the maximum of the earlier tiles
 // (redone in two passes if the tile's maximum exceeds it by more than the threshold), with one
-// exponential in four evaluated on the FMA pipe.  P has two shared-memory buffers per tile and the
-// tensor core is given the tile's NEXT scores before the product of the current P with V, so the
-// softmax warps of a tile go from one step to the next without waiting for that product.
-// TMEM columns: [0,128) S_A, [128,256) S_B, [256,320) O_A, [320,384) O_B.
+// exponential in four evaluated on the FMA pipe.  P never touches shared memory: the softmax warps
+// store it (16-bit, two keys per 32-bit column) into tensor memory and the product with V takes it
+// from there as its A operand, so the tensor core reads only V from shared memory for it.  The tensor
+// core is given a tile's NEXT scores before the product of its current P with V.
+// TMEM columns: [0,128) S_A, [128,256) S_B, [256,320) O_A, [320,384) O_B, [384,448) P_A, [448,512) P_B.
 #include "attn.cuh"
 #include "tc05.cuh"
 #include <type_traits>
@@ -38,10 +39,9 @@ constexpr int F2_TILE_BYTES = 16384;  // 128 rows x 64 x 2 B
 constexpr int F2_OFF_Q = 0;                        // [2]
 constexpr int F2_OFF_K = 2 * F2_TILE_BYTES;        // [2]
 constexpr int F2_OFF_V = 4 * F2_TILE_BYTES;        // [2]
-constexpr int F2_OFF_P = 6 * F2_TILE_BYTES;        // [2 tiles][2 buffers] x 32 KB
-constexpr int F2_OFF_BAR = F2_OFF_P + 4 * 32768;
+constexpr int F2_OFF_BAR = 6 * F2_TILE_BYTES;
 constexpr int F2_SMEM_BYTES = F2_OFF_BAR + 256 + 1024;
-constexpr int F2_COL_S = 0, F2_COL_O = 256;
+constexpr int F2_COL_S = 0, F2_COL_O = 256, F2_COL_P = 384;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct F2Params {
@@ -101,8 +101,8 @@ __global__ void __launch_bounds__(F2_THREADS, 1) attn_fwd2_tc05_kernel(const __g
   uint64_t* v_empty = bars + 7;   // [2]
   uint64_t* s_full = bars + 9;    // [2 tiles] scores of the tile are in TMEM
   uint64_t* p_full = bars + 11;   // [2 tiles] probabilities in smem, accumulator rescaled
-  uint64_t* pv_done = bars + 13;  // [2 tiles][2 P buffers] the P·V that read the buffer has retired
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 18);
+  uint64_t* pv_done = bars + 13;  // [2 tiles] P·V of the tile retired
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -124,8 +124,7 @@ __global__ void __launch_bounds__(F2_THREADS, 1) attn_fwd2_tc05_kernel(const __g
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 4);
-      mbar_init(&pv_done[2 * i], 1);
-      mbar_init(&pv_done[2 * i + 1], 1);
+      mbar_init(&pv_done[i], 1);
     }
     mbar_fence_init();
   }
@@ -170,18 +169,14 @@ __global__ void __launch_bounds__(F2_THREADS, 1) attn_fwd2_tc05_kernel(const __g
       constexpr uint32_t idesc_s = instr_desc_f16(128, 128, fmt, 0, 0);
       constexpr uint32_t idesc_o = instr_desc_f16(128, F2_HD, fmt, 0, 1);
       bool ok = mbar_wait(q_full, 0, 0x3300, abort_flag);
-      int k_ready = -1, v_ready = -1;  // highest key tile whose K / V load has been waited for
-      auto active = [&](int x, int j) { return x == 0 ? (j <= last_a) : (has_b && j <= last_b); };
+      const bool prof = (p.debug & 2) != 0;
+      auto last = [&](int x) { return x == 0 ? last_a : last_b; };
+      // query tiles that attend to key tile j (its K / V stage is released by the last of them)
+      auto users = [&](int j) { return (j <= last_a ? 1 : 0) + ((has_b && j <= last_b) ? 1 : 0); };
+      int s_cnt[2] = {0, 0}, pv_cnt[2] = {0, 0};  // per ring stage: products issued against the resident tile
       // S_x(j) = Q_x K_jᵀ
-      auto issue_s = [&](int x, int j) -> bool {
+      auto issue_s = [&](int x, int j) {
         const int st = j & 1;
-        if (k_ready < j) {
-          const bool prof = (p.debug & 2) != 0;
-          const long long m0 = clock64();
-          if (!mbar_wait(&k_full[st], (j >> 1) & 1, 0x3400 | st, abort_flag)) return false;
-          F2_PROF(8, m0, clock64());
-          k_ready = j;
-        }
         tc_fence_after();
         const long long i0 = clock64();
         const uint32_t sq = smem_u32(smem + F2_OFF_Q + x * F2_TILE_BYTES);
@@ -191,52 +186,80 @@ __global__ void __launch_bounds__(F2_THREADS, 1) attn_fwd2_tc05_kernel(const __g
           tc_mma_ss(tmem_base + F2_COL_S + x * 128, smem_desc_sw128(sq + s * 32, 16, 1024),
                     smem_desc_sw128(sk + s * 32, 16, 1024), idesc_s, s ? 1u : 0u);
         tc_commit(&s_full[x]);
-        // K_j is free once the last query tile that attends to it has been multiplied
-        const bool last_user = (x == 1) || !active(1, j);
-        if (last_user) tc_commit(&k_empty[st]);
-        if (p.debug & 2) atomicAdd(&g_prof_f2[10], (unsigned long long)(clock64() - i0));
-        return true;
+        if (++s_cnt[st] == users(j)) {  // K_j is free once every query tile that attends to it has been multiplied
+          tc_commit(&k_empty[st]);
+          s_cnt[st] = 0;
+        }
+        F2_PROF(10, i0, clock64());
       };
       // O_x += P_x(j) V_j
-      auto issue_pv = [&](int x, int j) -> bool {
+      auto issue_pv = [&](int x, int j) {
         const int st = j & 1;
-        const bool prof = (p.debug & 2) != 0;
-        const long long m1 = clock64();
-        if (v_ready < j) {
-          if (!mbar_wait(&v_full[st], (j >> 1) & 1, 0x3600 | st, abort_flag)) return false;
-          v_ready = j;
-        }
-        F2_PROF(7, m1, clock64());
-        if (prof) atomicAdd(&g_prof_f2[9], 1ull);
         tc_fence_after();
         const long long i1 = clock64();
-        const uint32_t sp = smem_u32(smem + F2_OFF_P + (x * 2 + (j & 1)) * 32768);
+        // A = P_x from tensor memory (a lane is a query row, a 32-bit column holds two consecutive keys),
+        // B = V_j from shared memory
+        const uint32_t tp = tmem_base + F2_COL_P + x * 64;
         const uint32_t sv = smem_u32(smem + F2_OFF_V + st * F2_TILE_BYTES);
 #pragma unroll
         for (int s = 0; s < F2_TILE / 16; ++s)
-          tc_mma_ss(tmem_base + F2_COL_O + x * F2_HD, smem_desc_sw128(sp + (s / 4) * 16384 + (s % 4) * 32, 16, 1024),
-                    smem_desc_sw128(sv + s * 2048, 16384, 1024), idesc_o, (j | s) ? 1u : 0u);
-        tc_commit(&pv_done[2 * x + (j & 1)]);
-        const bool last_user = (x == 1) || !active(1, j);
-        if (last_user) tc_commit(&v_empty[st]);
-        if (p.debug & 2) atomicAdd(&g_prof_f2[11], (unsigned long long)(clock64() - i1));
-        return true;
+          tc_mma_ts(tmem_base + F2_COL_O + x * F2_HD, tp + s * 8, smem_desc_sw128(sv + s * 2048, 16384, 1024), idesc_o,
+                    (j | s) ? 1u : 0u);
+        tc_commit(&pv_done[x]);
+        if (++pv_cnt[st] == users(j)) {
+          tc_commit(&v_empty[st]);
+          pv_cnt[st] = 0;
+        }
+        F2_PROF(11, i1, clock64());
+        if (prof) atomicAdd(&g_prof_f2[9], 1ull);
       };
-      if (ok) ok = issue_s(0, 0);
-      if (ok && has_b) ok = issue_s(1, 0);
-      for (int j = 0; j <= jmax && ok; ++j) {
-        for (int x = 0; x < 2 && ok; ++x) {
-          if (!active(x, j)) continue;
-          // P_x(j) is complete and every read of S_x(j) has been made: the next scores of the tile go
-          // first (its softmax warps wait for nothing else), the product with V behind them
-          {
-            const bool prof = (p.debug & 2) != 0;
-            const long long m0 = clock64();
-            ok = mbar_wait(&p_full[x], j & 1, 0x3500 | x, abort_flag);
-            F2_PROF(6, m0, clock64());
+      if (ok) ok = mbar_wait(&k_full[0], 0, 0x3400, abort_flag);
+      if (ok) {
+        issue_s(0, 0);
+        if (has_b) issue_s(1, 0);
+      }
+      // Event loop: whichever tile has its probabilities ready is served, its NEXT scores first (the
+      // tile's softmax warps wait for nothing else) and the product with V behind them.  Every
+      // condition is probed without blocking, so a tile never waits for the other one's turn.
+      int js[2] = {1, 1};  // next scores to issue per tile
+      int jp[2] = {0, 0};  // next P·V to issue per tile
+      uint64_t t_idle = global_ns();
+      while (ok) {
+        bool pending = false, progress = false;
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          if (x == 1 && !has_b) continue;
+          const int L = last(x);
+          if (js[x] <= L) {
+            pending = true;
+            const int j = js[x];  // needs P_x(j-1) complete (every read of S_x(j-1) made) and K_j resident
+            if (mbar_test(&p_full[x], (j - 1) & 1) && mbar_test(&k_full[j & 1], (j >> 1) & 1)) {
+              issue_s(x, j);
+              js[x] = j + 1;
+              progress = true;
+            }
           }
-          if (ok && active(x, j + 1)) ok = issue_s(x, j + 1);
-          if (ok) ok = issue_pv(x, j);
+          if (jp[x] <= L) {
+            pending = true;
+            const int j = jp[x];  // behind the tile's next scores; needs P_x(j) and V_j
+            if ((js[x] > j + 1 || j == L) && mbar_test(&p_full[x], j & 1) && mbar_test(&v_full[j & 1], (j >> 1) & 1)) {
+              issue_pv(x, j);
+              jp[x] = j + 1;
+              progress = true;
+            }
+          }
+        }
+        if (!pending) break;
+        if (progress) {
+          t_idle = global_ns();
+        } else if (*abort_flag) {
+          ok = false;
+        } else if (global_ns() - t_idle > kWaitLimitNs) {
+          *abort_flag = 1;
+          atomicCAS(&g_dev_status, 0, 0x3500);
+          ok = false;
+        } else {
+          __nanosleep(20);
         }
       }
     }
@@ -254,7 +277,7 @@ __global__ void __launch_bounds__(F2_THREADS, 1) attn_fwd2_tc05_kernel(const __g
       const uint32_t o_addr = lane_addr + F2_COL_O + x * F2_HD;
       const float c2 = p.scale * kLog2e2;
       const float slope = p.bias_mode ? p.slopes[h] : 0.f;
-      uint8_t* sp_base = smem + F2_OFF_P + x * 2 * 32768;
+      const uint32_t p_addr = lane_addr + F2_COL_P + x * 64;
       float m_run = -INFINITY;   // true running maximum
       float m_used = -INFINITY;  // maximum the accumulator and the running sum are expressed against
       float l_run = 0.f;
@@ -262,12 +285,13 @@ __global__ void __launch_bounds__(F2_THREADS, 1) attn_fwd2_tc05_kernel(const __g
       for (int j = 0; j <= jlast && ok; ++j) {
         const int j0 = j * F2_TILE;
         const bool diag = (j == jlast);
-        uint8_t* sp = sp_base + (j & 1) * 32768;  // P buffers alternate, so P(j) never waits for P(j-1)·V
         const bool plain = !BIAS && !diag;  // scores need only the common scale
         const bool prof = (p.debug & 2) && warp == 2 && lane == 0;
         const long long w0 = clock64();
         if (!mbar_wait(&s_full[x], j & 1, 0x3700 | x, abort_flag)) { ok = false; break; }
         const long long w1 = clock64();
+        const long long w1b = clock64();
+        F2_PROF(12, w1, w1b);
         F2_PROF(1, w0, w1);
         if (prof) atomicAdd(&g_prof_f2[0], 1ull);
         tc_fence_after();
@@ -279,11 +303,6 @@ __global__ void __launch_bounds__(F2_THREADS, 1) attn_fwd2_tc05_kernel(const __g
         // free as soon as they have landed.
         bool done = false;
         if (plain && j > 0) {
-          // the product that read this P buffer two steps ago (long retired)
-          if (j >= 2 && !mbar_wait(&pv_done[2 * x + (j & 1)], ((j - 2) >> 1) & 1, 0x3a00 | x, abort_flag)) {
-            ok = false;
-            break;
-          }
           float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
           float ls4[4] = {0.f, 0.f, 0.f, 0.f};
           const float neg_m = -m_used;
@@ -304,23 +323,25 @@ __global__ void __launch_bounds__(F2_THREADS, 1) attn_fwd2_tc05_kernel(const __g
             }
 #pragma unroll
             for (int e = 0; e < 32; ++e) ls4[e & 3] += g[e];
+            uint32_t pk[16];
 #pragma unroll
-            for (int v4 = 0; v4 < 4; ++v4) {
-              float h8[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) h8[e] = g[v4 * 8 + e];
-              const int cc = c * 4 + v4;
-              uint8_t* dst = sp + (cc >> 3) * 16384 + r * 128 + (((cc & 7) ^ (r & 7)) << 4);
-              *reinterpret_cast<uint4*>(dst) = pack8<T>(h8);
+            for (int e = 0; e < 16; ++e) {
+              const typename Num<T>::T2 h2 = Num<T>::from_f2(g[2 * e], g[2 * e + 1]);
+              pk[e] = *reinterpret_cast<const uint32_t*>(&h2);
             }
+            // P of the previous step is read by its product with V until that has retired; the first
+            // chunk's exponentials above overlap its tail
+            if (c == 0 && !mbar_wait(&pv_done[x], (j - 1) & 1, 0x3a00 | x, abort_flag)) { ok = false; break; }
+            tmem_st16(p_addr + c * 16, pk);
           }
+          if (!ok) break;
           const float m_tile = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * c2;
           if (!__any_sync(0xffffffffu, (m_tile - m_used) > kRescaleThreshold)) {
             m_run = fmaxf(m_run, m_tile);
             l_run += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
             done = true;
           }
-          F2_PROF(2, w1, clock64());
+          F2_PROF(2, w1b, clock64());
           if (prof && done) atomicAdd(&g_prof_f2[3], 1ull);
         }
         if (!done) {
@@ -353,10 +374,7 @@ __global__ void __launch_bounds__(F2_THREADS, 1) attn_fwd2_tc05_kernel(const __g
         if (plain) mx *= c2;  // c2 > 0: scaling commutes with the maximum
         m_run = fmaxf(m_run, mx);
         // the previous P·V of this tile must have retired before P's buffer or O is touched
-        if (j > 0 && !mbar_wait(&pv_done[2 * x + ((j - 1) & 1)], ((j - 1) >> 1) & 1, 0x3800 | x, abort_flag)) {
-          ok = false;
-          break;
-        }
+        if (j > 0 && !mbar_wait(&pv_done[x], (j - 1) & 1, 0x3800 | x, abort_flag)) { ok = false; break; }
         if (j == 0) {
           m_used = m_run;
         } else {
@@ -404,28 +422,26 @@ __global__ void __launch_bounds__(F2_THREADS, 1) attn_fwd2_tc05_kernel(const __g
             }
 #pragma unroll
             for (int e = 0; e < 32; ++e) ls4[e & 3] += g[e];
+            uint32_t pk[16];
 #pragma unroll
-            for (int v4 = 0; v4 < 4; ++v4) {
-              float h8[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) h8[e] = g[v4 * 8 + e];
-              const int cc = c * 4 + v4;  // 16-byte chunk index along the 128 keys
-              uint8_t* dst = sp + (cc >> 3) * 16384 + r * 128 + (((cc & 7) ^ (r & 7)) << 4);
-              *reinterpret_cast<uint4*>(dst) = pack8<T>(h8);
+            for (int e = 0; e < 16; ++e) {
+              const typename Num<T>::T2 h2 = Num<T>::from_f2(g[2 * e], g[2 * e + 1]);
+              pk[e] = *reinterpret_cast<const uint32_t*>(&h2);
             }
+            tmem_st16(p_addr + c * 16, pk);
           }
         }
         l_run += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
         }  // two-pass path
         const long long w2 = clock64();
+        tc_wait_st();  // P is in tensor memory
         tc_fence_before();
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[x]);
-        F2_PROF(4, w1, w2);
+        F2_PROF(4, w1b, w2);
         F2_PROF(5, w2, clock64());
       }
-      if (ok && mbar_wait(&pv_done[2 * x + (jlast & 1)], (jlast >> 1) & 1, 0x3900 | x, abort_flag)) {
+      if (ok && mbar_wait(&pv_done[x], jlast & 1, 0x3900 | x, abort_flag)) {
         tc_fence_after();
         const float inv = 1.f / l_run;
         T* orow = reinterpret_cast<T*>(p.out) + b * p.so_b + h * p.so_h + (int64_t)i * p.so_t;
