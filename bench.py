@@ -203,7 +203,7 @@ def run_b200_arm(args):
     model = build_model(cfg, dtype, dev)
     broadcast_parameters(model)
     n_params = sum(p.numel() for p in model.parameters())
-    buckets = GradBuckets(model.parameters())
+    buckets = GradBuckets(model.parameters(), column_blocks=model.projection_weight_groups())
     tlinear.ACCUMULATE_INTO_GRAD = True  # weight-gradient GEMMs add into the bucket views themselves
     loss_scale = 4096.0 if dtype is torch.float16 else 1.0
 

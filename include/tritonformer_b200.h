@@ -86,6 +86,15 @@ int tfb_layernorm_bwd_res(const void* dy, const void* x, const void* alpha,
                           int64_t rows, int64_t d, int64_t dy_ld, int64_t x_ld, int64_t dres_ld,
                           int64_t dx_ld, int dtype, void* stream);
 
+/* The same again, optionally ADDING the column sums to what dalpha / dbeta already hold
+ * (accumulate != 0): gradient accumulation into existing .grad buffers without a separate add
+ * (no counterpart in the reference, where autograd adds).                                   */
+int tfb_layernorm_bwd_acc(const void* dy, const void* x, const void* alpha,
+                          const float* mean, const float* rstd, const void* dres, void* dx,
+                          void* dalpha, void* dbeta, float* partials, int64_t n_partials,
+                          int64_t rows, int64_t d, int64_t dy_ld, int64_t x_ld, int64_t dres_ld,
+                          int64_t dx_ld, int accumulate, int dtype, void* stream);
+
 /* LayerNorm backward for callers that cannot supply scratch memory (no counterpart in the
  * reference, which allocates freely through torch): same results as tfb_layernorm_bwd, but the
  * fp32 partial sums live in a fixed array inside the library image (about 9.7 MB, held by every

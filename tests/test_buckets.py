@@ -1,0 +1,38 @@
+"""Host logic of the gradient buckets (CPU): flat layout, column-block layout of grouped weights."""
+import torch
+
+from tritonformer_b200.dp import GradBuckets
+
+
+def _params():
+    torch.manual_seed(0)
+    return [torch.nn.Parameter(torch.randn(s)) for s in [(8, 16), (8, 16), (8, 16), (16, 8), (5,), (3, 7)]]
+
+
+def test_column_blocks_share_one_matrix():
+    ps = _params()
+    b = GradBuckets(ps, column_blocks=[(ps[0], ps[1], ps[2])])
+    g0, g1, g2 = ps[0].grad, ps[1].grad, ps[2].grad
+    assert g0.shape == (8, 16) and g0.stride() == (48, 1) and g1.stride() == (48, 1)
+    assert g1.data_ptr() == g0.data_ptr() + 16 * 4 and g2.data_ptr() == g0.data_ptr() + 32 * 4
+    whole = torch.as_strided(g0, (8, 48), (48, 1))
+    whole.copy_(torch.arange(8 * 48, dtype=torch.float32).view(8, 48))
+    assert torch.equal(g1, whole[:, 16:32]) and torch.equal(g2, whole[:, 32:])
+    # everything still lives in the flat buckets and nothing overlaps
+    b.check_views()
+    total = sum(p.grad.numel() for p in ps)
+    assert sum(x.numel() for x in b.buckets) >= total
+    b.zero()
+    for i, p in enumerate(ps):
+        p.grad.fill_(float(i + 1))
+    for i, p in enumerate(ps):
+        assert bool((p.grad == float(i + 1)).all()), i
+
+
+def test_groups_that_do_not_qualify_fall_back_to_flat_views():
+    ps = _params()
+    GradBuckets(ps, column_blocks=[(ps[0], ps[3])])  # different shapes
+    assert ps[0].grad.is_contiguous() and ps[3].grad.is_contiguous()
+    ps = _params()
+    GradBuckets(ps, bucket_bytes=8 * 16 * 4, column_blocks=[(ps[0], ps[1], ps[2])])  # one parameter per bucket
+    assert all(p.grad.is_contiguous() for p in ps)

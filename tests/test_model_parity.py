@@ -142,7 +142,8 @@ def test_small_model_module_by_module_layers(bias):
         tr.USE_FUSED_BLOCKS = True
 
 
-def test_gradients_accumulated_into_existing_grad_buffers():
+@pytest.mark.parametrize("column_blocks", [False, True])
+def test_gradients_accumulated_into_existing_grad_buffers(column_blocks):
     """With ACCUMULATE_INTO_GRAD the weight-gradient GEMMs add into .grad themselves: two steps give twice
     the gradient of one, and .grad keeps its storage."""
     import tritonformer_b200.linear as lin
@@ -164,7 +165,11 @@ def test_gradients_accumulated_into_existing_grad_buffers():
     step()
     once = {n: p.grad.detach().float().clone() for n, p in model.named_parameters()}
     model.zero_grad(set_to_none=True)
-    buckets = GradBuckets(model.parameters())
+    buckets = GradBuckets(model.parameters(),
+                          column_blocks=model.projection_weight_groups() if column_blocks else ())
+    if column_blocks:
+        att = model.layer_list[0].attention
+        assert att.k_proj.weight.grad.data_ptr() == att.q_proj.weight.grad.data_ptr() + 2 * att.q_proj.weight.shape[1]
     lin.ACCUMULATE_INTO_GRAD = True
     try:
         step()

@@ -30,6 +30,7 @@ _SIGNATURES = {
     "tfb_layernorm_bwd_partials": (_i64, [_i64, _i64]),
     "tfb_layernorm_bwd": (_i32, [_vp] * 9 + [_i64] * 6 + [_i32, _vp]),
     "tfb_layernorm_bwd_res": (_i32, [_vp] * 10 + [_i64] * 7 + [_i32, _vp]),
+    "tfb_layernorm_bwd_acc": (_i32, [_vp] * 10 + [_i64] * 7 + [_i32, _i32, _vp]),
     "tfb_layernorm_bwd_static": (_i32, [_vp] * 8 + [_i64] * 5 + [_i32, _vp]),
     "tfb_softmax_fwd": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp]),
     "tfb_softmax_bwd": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),

@@ -4,7 +4,7 @@
 
 namespace tfb {
 
-template <typename T> int finalize_partials(const float*, int64_t, int, int, void*, void*, cudaStream_t);
+template <typename T> int finalize_partials(const float*, int64_t, int, int, void*, void*, cudaStream_t, int);
 
 template <typename T>
 __global__ void __launch_bounds__(256) relu_bwd_vec_kernel(const uint4* __restrict__ dy,
@@ -120,6 +120,6 @@ extern "C" int tfb_colsum(const void* x, void* out, float* partials, int64_t n_p
     else launch_overlapped(colsum_kernel<T, false>, dim3(grid), dim3(256), 0, st, (const T*)x, partials, rows, (int)cols, x_ld);
     int rc = launched("colsum");
     if (rc) return rc;
-    return finalize_partials<T>(partials, n_partials, (int)cols, (int)cols, out, out, st);
+    return finalize_partials<T>(partials, n_partials, (int)cols, (int)cols, out, out, st, 0);
   })
 }

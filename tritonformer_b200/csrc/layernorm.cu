@@ -408,7 +408,7 @@ __global__ void __launch_bounds__(256, 2) ln_bwd_split_kernel(
 template <typename T>
 __global__ void __launch_bounds__(256) finalize_partials_kernel(
     const float* __restrict__ partials, int64_t n, int ncols, int split, T* __restrict__ out0,
-    T* __restrict__ out1) {
+    T* __restrict__ out1, int accumulate) {
   grid_dependency_wait();
   allow_dependents();
   __shared__ float sm[8][33];
@@ -422,19 +422,21 @@ __global__ void __launch_bounds__(256) finalize_partials_kernel(
   if (ry == 0 && c < ncols) {
 #pragma unroll
     for (int i = 1; i < 8; ++i) s += sm[i][cx];
-    if (c < split) out0[c] = Num<T>::from_f(s);
-    else out1[c - split] = Num<T>::from_f(s);
+    T* dst = c < split ? out0 + c : out1 + (c - split);
+    if (accumulate) s += Num<T>::to_f(*dst);  // the sums are added to what the output already holds
+    *dst = Num<T>::from_f(s);
   }
 }
 
 template <typename T>
 int finalize_partials(const float* partials, int64_t n, int ncols, int split, void* out0,
-                      void* out1, cudaStream_t st) {
-  launch_overlapped(finalize_partials_kernel<T>, dim3((unsigned)ceil_div(ncols, 32)), dim3(256), 0, st, partials, n, ncols, split, (T*)out0, (T*)out1);
+                      void* out1, cudaStream_t st, int accumulate) {
+  launch_overlapped(finalize_partials_kernel<T>, dim3((unsigned)ceil_div(ncols, 32)), dim3(256), 0, st, partials, n,
+                    ncols, split, (T*)out0, (T*)out1, accumulate);
   return launched("finalize_partials");
 }
-template int finalize_partials<__half>(const float*, int64_t, int, int, void*, void*, cudaStream_t);
-template int finalize_partials<__nv_bfloat16>(const float*, int64_t, int, int, void*, void*, cudaStream_t);
+template int finalize_partials<__half>(const float*, int64_t, int, int, void*, void*, cudaStream_t, int);
+template int finalize_partials<__nv_bfloat16>(const float*, int64_t, int, int, void*, void*, cudaStream_t, int);
 
 static int ln_bwd_threads(int64_t d) { return (int)(ceil_div(ceil_div(d, 8), 32) * 32); }
 
@@ -443,7 +445,7 @@ static int ln_bwd_launch(const void* dy, const void* x, const void* alpha, const
                          const float* rstd, void* dx, void* dalpha, void* dbeta, float* partials,
                          int64_t n_partials, int64_t rows, int d, int64_t dy_ld, int64_t x_ld,
                          int64_t dx_ld, bool vec, int threads, cudaStream_t st, const void* dres = nullptr,
-                         int64_t dres_ld = 0) {
+                         int64_t dres_ld = 0, int accumulate = 0) {
 #define TFB_LN_BWD(V, MT)                                                                     \
   launch_overlapped(ln_bwd_kernel<T, V, MT>, dim3((unsigned)n_partials), dim3(threads), 0, st, \
       (const T*)dy, (const T*)x, (const T*)alpha, mean, rstd, (T*)dx, partials, rows, d, dy_ld, \
@@ -474,7 +476,7 @@ static int ln_bwd_launch(const void* dy, const void* x, const void* alpha, const
 #undef TFB_LN_BWD
   int rc = launched("layernorm_bwd");
   if (rc) return rc;
-  return finalize_partials<T>(partials, n_partials, 2 * d, d, dalpha, dbeta, st);
+  return finalize_partials<T>(partials, n_partials, 2 * d, d, dalpha, dbeta, st, accumulate);
 }
 
 }  // namespace tfb
@@ -518,10 +520,11 @@ extern "C" int64_t tfb_layernorm_bwd_partials(int64_t rows, int64_t d) {
   return n < 1 ? 1 : n;
 }
 
-extern "C" int tfb_layernorm_bwd_res(const void* dy, const void* x, const void* alpha, const float* mean,
+extern "C" int tfb_layernorm_bwd_acc(const void* dy, const void* x, const void* alpha, const float* mean,
                                      const float* rstd, const void* dres, void* dx, void* dalpha, void* dbeta,
                                      float* partials, int64_t n_partials, int64_t rows, int64_t d, int64_t dy_ld,
-                                     int64_t x_ld, int64_t dres_ld, int64_t dx_ld, int dtype, void* stream) {
+                                     int64_t x_ld, int64_t dres_ld, int64_t dx_ld, int accumulate, int dtype,
+                                     void* stream) {
   TFB_REQUIRE(rows > 0 && d > 0, "layernorm_bwd: bad shape rows=%lld d=%lld", (long long)rows,
               (long long)d);
   if (d > 8192) return fail(TFB_ERR_UNSUPPORTED, "layernorm_bwd: d=%lld > 8192", (long long)d);
@@ -536,8 +539,16 @@ extern "C" int tfb_layernorm_bwd_res(const void* dy, const void* x, const void* 
   const int threads = ln_bwd_threads(d);
   TFB_DISPATCH_16(dtype, T, {
     return ln_bwd_launch<T>(dy, x, alpha, mean, rstd, dx, dalpha, dbeta, partials, n_partials, rows,
-                            (int)d, dy_ld, x_ld, dx_ld, vec, threads, st, dres, dres_ld);
+                            (int)d, dy_ld, x_ld, dx_ld, vec, threads, st, dres, dres_ld, accumulate ? 1 : 0);
   })
+}
+
+extern "C" int tfb_layernorm_bwd_res(const void* dy, const void* x, const void* alpha, const float* mean,
+                                     const float* rstd, const void* dres, void* dx, void* dalpha, void* dbeta,
+                                     float* partials, int64_t n_partials, int64_t rows, int64_t d, int64_t dy_ld,
+                                     int64_t x_ld, int64_t dres_ld, int64_t dx_ld, int dtype, void* stream) {
+  return tfb_layernorm_bwd_acc(dy, x, alpha, mean, rstd, dres, dx, dalpha, dbeta, partials, n_partials, rows, d,
+                               dy_ld, x_ld, dres_ld, dx_ld, 0, dtype, stream);
 }
 
 extern "C" int tfb_layernorm_bwd(const void* dy, const void* x, const void* alpha,

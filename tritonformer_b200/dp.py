@@ -14,11 +14,21 @@ import torch.distributed as dist
 
 
 class GradBuckets:
-    def __init__(self, params, bucket_bytes: int = 256 << 20):
+    def __init__(self, params, bucket_bytes: int = 256 << 20, column_blocks=()):
+        """`column_blocks`: tuples of 2-D parameters of one shape (in, d) whose gradients are laid out as the column
+        blocks of ONE (in, len * d) matrix inside the bucket (the q/k/v projection weights: their gradients are then
+        a single product that accumulates straight into the bucket)."""
         self.params = [p for p in params if p.requires_grad]
         self.buckets: List[torch.Tensor] = []
         self.members: List[list] = []  # parameters of each bucket
         self._views = []
+        block_of = {}
+        for blk in column_blocks:
+            blk = tuple(blk)
+            if len(blk) > 1 and all(q.dim() == 2 and q.shape == blk[0].shape and q.dtype == blk[0].dtype
+                                    and q.requires_grad for q in blk):
+                for q in blk:
+                    block_of[id(q)] = blk
         groups, cur, cur_bytes = [], [], 0
         for p in reversed(self.params):  # backward produces gradients roughly in reverse order
             nbytes = p.numel() * p.element_size()
@@ -29,15 +39,32 @@ class GradBuckets:
             cur_bytes += nbytes
         if cur:
             groups.append(cur)
+        pad = lambda n: -(-n // 8) * 8  # keep every view 16-byte aligned
         for group in groups:
-            total = sum(-(-p.numel() // 8) * 8 for p in group)  # keep every view 16-byte aligned
+            total = sum(pad(p.numel()) for p in group)
             flat = torch.zeros(total, device=group[0].device, dtype=group[0].dtype)
+            in_group = {id(p) for p in group}
+            placed = set()
             off = 0
             for p in group:
+                if id(p) in placed:
+                    continue
+                blk = block_of.get(id(p))
+                if blk is not None and all(id(q) in in_group for q in blk) and p.numel() % 8 == 0:
+                    rows, d = p.shape
+                    mat = flat[off:off + len(blk) * p.numel()].view(rows, len(blk) * d)
+                    for i, q in enumerate(blk):
+                        view = mat[:, i * d:(i + 1) * d]
+                        q.grad = view
+                        self._views.append((q, view))
+                        placed.add(id(q))
+                    off += len(blk) * pad(p.numel())
+                    continue
                 view = flat[off:off + p.numel()].view_as(p)
                 p.grad = view
                 self._views.append((p, view))
-                off += -(-p.numel() // 8) * 8
+                placed.add(id(p))
+                off += pad(p.numel())
             self.buckets.append(flat)
             self.members.append(list(group))
 

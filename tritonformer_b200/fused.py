@@ -27,17 +27,25 @@ class LayerNormFork(Function):
     @amp_forward
     def forward(ctx, x, alpha, beta, eps):
         y, stats = layernorm_forward(x, alpha, beta, eps)
-        ctx.save_for_backward(x, alpha, stats)
+        ctx.save_for_backward(x, alpha, beta, stats)
         return y, x.view_as(x)
 
     @staticmethod
     @amp_backward
     def backward(ctx, dy, dres):
-        x, alpha, stats = ctx.saved_tensors
+        x, alpha, beta, stats = ctx.saved_tensors
         if dy is None:
             return dres, None, None, None
         dres = dres.to(x.dtype) if dres is not None else None
-        dx, dalpha, dbeta = layernorm_backward(dy.to(x.dtype), x, alpha, stats, dres)
+        into = None
+        if L.ACCUMULATE_INTO_GRAD and ctx.needs_input_grad[1] and ctx.needs_input_grad[2]:
+            ga, gb = alpha.grad, beta.grad
+            if ga is not None and gb is not None and ga.is_contiguous() and gb.is_contiguous() \
+                    and ga.dtype == x.dtype and gb.dtype == x.dtype and ga.shape == alpha.shape == gb.shape:
+                into = (ga, gb)  # the column sums are added to .grad by the kernel that folds them
+        dx, dalpha, dbeta = layernorm_backward(dy.to(x.dtype), x, alpha, stats, dres, into=into)
+        if into is not None:
+            return dx, None, None, None
         return dx, dalpha.view(alpha.shape), dbeta.view(alpha.shape), None
 
 
@@ -111,7 +119,17 @@ class QKVProjection(Function):
                 dy = torch.as_strided(grads[0], (rows, 3 * d), (3 * d, 1))
                 dx = L.input_grad(dy, w, x.shape) if need[0] else None
                 dws = [None, None, None]
-                if any(need[1:4]):
+                pgrads = [p.grad for p in (wq, wk, wv)]
+                if L.ACCUMULATE_INTO_GRAD and all(need[1:4]) and all(g is not None for g in pgrads) \
+                        and pgrads[0].dtype == x.dtype and pgrads[0].shape == wq.shape \
+                        and _adjacent_columns(pgrads, 3 * d):
+                    # the three .grad are column blocks of one (in, 3 d) matrix (GradBuckets column_blocks):
+                    # one product that adds straight into it
+                    x2 = x.reshape(-1, x.shape[-1])
+                    into = torch.as_strided(pgrads[0], (wq.shape[0], 3 * d), (3 * d, 1))
+                    L.gemm(x2, x2.stride(1), x2.stride(0), dy, dy.stride(0), dy.stride(1), wq.shape[0], 3 * d, rows,
+                           out=into, accumulate=True)
+                elif any(need[1:4]):
                     dw = L.weight_grad(x, dy, w)  # (in, 3 d); w is a temporary, so this is a fresh tensor
                     for i, p in enumerate((wq, wk, wv)):
                         if not need[1 + i]:

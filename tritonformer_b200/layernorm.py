@@ -31,25 +31,31 @@ def layernorm_forward(x, alpha, beta, eps):
     return y.view(x.shape), stats
 
 
-def layernorm_backward(dy, x, alpha, stats, dres=None):
-    """dx, dalpha, dbeta; `dres` (same shape as x) is added to dx inside the kernel."""
+def layernorm_backward(dy, x, alpha, stats, dres=None, into=None):
+    """dx, dalpha, dbeta; `dres` (same shape as x) is added to dx inside the kernel.  `into` = (dalpha, dbeta)
+    buffers to ADD the parameter gradients to (then returned as None, None)."""
     d = x.shape[-1]
     x2, dy2 = _rows(x), _rows(dy)
     r2 = _rows(dres) if dres is not None else None
     rows = x2.shape[0]
     dx = torch.empty((rows, d), device=x.device, dtype=x.dtype)
-    dalpha = torch.empty((d,), device=x.device, dtype=x.dtype)
-    dbeta = torch.empty_like(dalpha)
+    if into is None:
+        dalpha = torch.empty((d,), device=x.device, dtype=x.dtype)
+        dbeta = torch.empty_like(dalpha)
+    else:
+        dalpha, dbeta = into
     n = _lib.lib.tfb_layernorm_bwd_partials(rows, d)
     partials = torch.empty((n, 2, d), device=x.device, dtype=torch.float32)
     alpha = alpha.contiguous()
-    _lib.check(_lib.lib.tfb_layernorm_bwd_res(
+    _lib.check(_lib.lib.tfb_layernorm_bwd_acc(
         dy2.data_ptr(), x2.data_ptr(), alpha.data_ptr(), stats[0].data_ptr(), stats[1].data_ptr(),
         r2.data_ptr() if r2 is not None else None,
         dx.data_ptr(), dalpha.data_ptr(), dbeta.data_ptr(), partials.data_ptr(), n, rows, d,
         dy2.stride(0) if rows > 1 else d, x2.stride(0) if rows > 1 else d,
         (r2.stride(0) if rows > 1 else d) if r2 is not None else 0, d,
-        _lib.dtype_code(x.dtype), _lib.stream_ptr(x.device)))
+        1 if into is not None else 0, _lib.dtype_code(x.dtype), _lib.stream_ptr(x.device)))
+    if into is not None:
+        return dx.view(x.shape), None, None
     return dx.view(x.shape), dalpha, dbeta
 
 

@@ -189,6 +189,12 @@ class Transformer(nn.Module):
         else:
             self.attn_bias = None
 
+    def projection_weight_groups(self):
+        """The (q, k, v) projection weights of every layer: `GradBuckets(..., column_blocks=...)` lays their
+        gradients out as column blocks of one matrix, so the three weight gradients are one product."""
+        return [(layer.attention.q_proj.weight, layer.attention.k_proj.weight, layer.attention.v_proj.weight)
+                for layer in self.layer_list]
+
     def forward(self, input_ids: torch.Tensor, labels: Optional[torch.Tensor]
                 ) -> Tuple[torch.Tensor, torch.Tensor]:
         batch, seq = input_ids.shape
