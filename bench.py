@@ -479,12 +479,12 @@ def run_kernel_bench(args):
         lse = torch.empty(n, device=dev, dtype=torch.float32)
         g = torch.ones(n, device=dev, dtype=torch.float16)
         dl = torch.empty_like(logits)
-        st = L.stream_ptr(dev)
+        st = lambda: L.stream_ptr(dev)  # read at call time: the timing harness replays from its own stream
         fwd = lambda: L.check(L.lib.tfb_cross_entropy_fwd(logits.data_ptr(), labels.data_ptr(), loss.data_ptr(), None,
-                                                          lse.data_ptr(), n, v, v, 0, st))
+                                                          lse.data_ptr(), n, v, v, 0, st()))
         emit("ce_fwd_kernel", f"rows {n} vocab {v} fp16", _time_cuda(fwd, iters, warmup), 2.0 * n * v, "GB/s", "hbm")
         bwd = lambda: L.check(L.lib.tfb_cross_entropy_bwd(logits.data_ptr(), labels.data_ptr(), lse.data_ptr(),
-                                                          g.data_ptr(), 1, dl.data_ptr(), n, v, v, v, 0, st))
+                                                          g.data_ptr(), 1, dl.data_ptr(), n, v, v, v, 0, st()))
         emit("ce_bwd_kernel", f"rows {n} vocab {v} fp16", _time_cuda(bwd, iters, warmup), 4.0 * n * v, "GB/s", "hbm")
     if which in ("softmax", "all"):
         rows, cols = (65536, 1024) if args.small else (131072, 1024)
@@ -492,8 +492,8 @@ def run_kernel_bench(args):
         dy = torch.randn((1, rows, cols), device=dev)
         y = torch.empty_like(x)
         dx = torch.empty_like(x)
-        st = L.stream_ptr(dev)
-        fwd = lambda: L.check(L.lib.tfb_softmax_fwd(x.data_ptr(), y.data_ptr(), rows, cols, cols, cols, 2, st))
+        st = lambda: L.stream_ptr(dev)  # read at call time: the timing harness replays from its own stream
+        fwd = lambda: L.check(L.lib.tfb_softmax_fwd(x.data_ptr(), y.data_ptr(), rows, cols, cols, cols, 2, st()))
         emit("softmax_fwd_vec_kernel", f"rows {rows} cols {cols} fp32", _time_cuda(fwd, iters, warmup), 8.0 * rows * cols,
              "GB/s", "hbm")
         bwd = lambda: L.check(L.lib.tfb_softmax_bwd(dy.data_ptr(), y.data_ptr(), dx.data_ptr(), rows, cols, cols, cols,
