@@ -63,3 +63,25 @@ def test_ln_under_autocast_casts_to_fp16():
     assert y.dtype == torch.float16
     with pytest.raises(AssertionError):
         m(x)  # outside autocast nothing is cast, fp32 input is rejected like the reference does
+
+
+def test_ln_backward_adds_parameter_gradients_into_given_buffers():
+    """`into=(dalpha, dbeta)`: the kernel that folds the partial column sums adds them to what the buffers hold
+    (gradient accumulation without a separate add), dx is unchanged."""
+    from tritonformer_b200.layernorm import layernorm_backward, layernorm_forward
+    torch.manual_seed(1)
+    x = torch.randn((3, 70, 512), device="cuda").half()
+    dy = torch.randn_like(x)
+    alpha = torch.randn(512, device="cuda").half()
+    beta = torch.randn(512, device="cuda").half()
+    _, stats = layernorm_forward(x, alpha, beta, 1e-5)
+    dx, da, db = layernorm_backward(dy, x, alpha, stats)
+    old_a = torch.randn(512, device="cuda").half()
+    old_b = torch.randn(512, device="cuda").half()
+    buf_a, buf_b = old_a.clone(), old_b.clone()
+    dx2, none_a, none_b = layernorm_backward(dy, x, alpha, stats, into=(buf_a, buf_b))
+    assert none_a is None and none_b is None
+    assert torch.equal(dx, dx2)
+    # one fp32 add of the fp32 column sum and the old value, one rounding
+    assert_close(buf_a, old_a.float() + da.float(), 2e-2, "dalpha", rtol=2e-3)
+    assert_close(buf_b, old_b.float() + db.float(), 2e-2, "dbeta", rtol=2e-3)
