@@ -60,7 +60,6 @@ struct GemmParams {
   int relu;
   int tiles_m, tiles_n;
   int sk_tiles;        // tiles [0, sk_tiles) are split along K over all CTAs; 0 = whole tiles only
-  int debug;           // timing experiments (tfb_debug_set key 4): bit 1 skips the partial reads, bit 2 the partial writes
 };
 
 template <typename T, int BN, bool A_MN, bool B_MN>
@@ -232,7 +231,7 @@ __global__ void __launch_bounds__(TB_THREADS, 1) gemm_tc05_kernel(const __grid_c
         // slot layout [column group of 4][row]: the 32 lanes of a warp touch 512 contiguous bytes
         float4* slot = reinterpret_cast<float4*>(p.partials + (int64_t)blockIdx.x * TB_M * BN) + q * 32 + lane;
 #pragma unroll 1
-        for (int st = 0; st < ((p.debug & 4) ? 0 : STEPS); ++st) {
+        for (int st = 0; st < STEPS; ++st) {
           uint32_t r0[32], r1[32];
           tmem_ld32(taddr + st * 64, r0);
           tmem_ld32(taddr + st * 64 + 32, r1);
@@ -277,7 +276,7 @@ __global__ void __launch_bounds__(TB_THREADS, 1) gemm_tc05_kernel(const __grid_c
         tmem_ld32(taddr + st * 64, r0);
         tmem_ld32(taddr + st * 64 + 32, r1);
         tc_wait_ld();
-        for (int c = 1; c <= ((p.debug & 2) ? 0 : n_parts); ++c) {
+        for (int c = 1; c <= n_parts; ++c) {
           // all sixteen loads of this thread's 64 columns are issued before the first add
           const float4* src = reinterpret_cast<const float4*>(p.partials + (int64_t)(blockIdx.x + c) * TB_M * BN) +
                               st * 16 * TB_M + q * 32 + lane;
@@ -540,7 +539,7 @@ int gemm_tc05(const void* a, const void* b, void* c, const void* bias, const voi
   p.partials = sk_tiles ? reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + kFlagBytes) : nullptr;
   p.M = (int)M; p.N = (int)N; p.K = (int)K; p.ldc = ldc; p.ld_addend = ld_addend; p.ld_mask = ld_mask;
   p.relu = relu;
-  p.tiles_m = (int)tm; p.tiles_n = (int)ceil_div(N, BN); p.sk_tiles = (int)sk_tiles; p.debug = dbg;
+  p.tiles_m = (int)tm; p.tiles_n = (int)ceil_div(N, BN); p.sk_tiles = (int)sk_tiles;
   TFB_DISPATCH_16(dtype, T, {
     if (BN == 256) return dispatch_major<T, 256>(a_mn, b_mn, tmA, tmB, tmC, tmX, p, (int)grid, st);
     return dispatch_major<T, 128>(a_mn, b_mn, tmA, tmB, tmC, tmX, p, (int)grid, st);
