@@ -497,7 +497,7 @@ def run_kernel_bench(args):
         emit("softmax_fwd_vec_kernel", f"rows {rows} cols {cols} fp32", _time_cuda(fwd, iters, warmup), 8.0 * rows * cols,
              "GB/s", "hbm")
         bwd = lambda: L.check(L.lib.tfb_softmax_bwd(dy.data_ptr(), y.data_ptr(), dx.data_ptr(), rows, cols, cols, cols,
-                                                    cols, 2, st))
+                                                    cols, 2, st()))
         emit("softmax_bwd_vec_kernel", f"rows {rows} cols {cols} fp32", _time_cuda(bwd, iters, warmup),
              12.0 * rows * cols, "GB/s", "hbm")
     if which in ("relu", "all"):

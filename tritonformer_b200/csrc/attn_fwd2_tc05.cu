@@ -174,17 +174,24 @@ __global__ void __launch_bounds__(F2_THREADS, 1) attn_fwd2_tc05_kernel(const __g
       // query tiles that attend to key tile j (its K / V stage is released by the last of them)
       auto users = [&](int j) { return (j <= last_a ? 1 : 0) + ((has_b && j <= last_b) ? 1 : 0); };
       int s_cnt[2] = {0, 0}, pv_cnt[2] = {0, 0};  // per ring stage: products issued against the resident tile
+      // operand descriptors are built once; the issuing thread shares its scheduler with two softmax
+      // warps, so every instruction it saves per MMA shortens the tensor core's idle gaps
+      uint64_t dq[2], dk[2], dv[2];
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        dq[t] = smem_desc_sw128(smem_u32(smem + F2_OFF_Q + t * F2_TILE_BYTES), 16, 1024);
+        dk[t] = smem_desc_sw128(smem_u32(smem + F2_OFF_K + t * F2_TILE_BYTES), 16, 1024);
+        dv[t] = smem_desc_sw128(smem_u32(smem + F2_OFF_V + t * F2_TILE_BYTES), 16384, 1024);
+      }
       // S_x(j) = Q_x K_jᵀ
       auto issue_s = [&](int x, int j) {
         const int st = j & 1;
         tc_fence_after();
         const long long i0 = clock64();
-        const uint32_t sq = smem_u32(smem + F2_OFF_Q + x * F2_TILE_BYTES);
-        const uint32_t sk = smem_u32(smem + F2_OFF_K + st * F2_TILE_BYTES);
 #pragma unroll
         for (int s = 0; s < F2_HD / 16; ++s)
-          tc_mma_ss(tmem_base + F2_COL_S + x * 128, smem_desc_sw128(sq + s * 32, 16, 1024),
-                    smem_desc_sw128(sk + s * 32, 16, 1024), idesc_s, s ? 1u : 0u);
+          tc_mma_ss(tmem_base + F2_COL_S + x * 128, desc_advance(dq[x], s * 32), desc_advance(dk[st], s * 32), idesc_s,
+                    s ? 1u : 0u);
         tc_commit(&s_full[x]);
         if (++s_cnt[st] == users(j)) {  // K_j is free once every query tile that attends to it has been multiplied
           tc_commit(&k_empty[st]);
@@ -200,10 +207,9 @@ __global__ void __launch_bounds__(F2_THREADS, 1) attn_fwd2_tc05_kernel(const __g
         // A = P_x from tensor memory (a lane is a query row, a 32-bit column holds two consecutive keys),
         // B = V_j from shared memory
         const uint32_t tp = tmem_base + F2_COL_P + x * 64;
-        const uint32_t sv = smem_u32(smem + F2_OFF_V + st * F2_TILE_BYTES);
 #pragma unroll
         for (int s = 0; s < F2_TILE / 16; ++s)
-          tc_mma_ts(tmem_base + F2_COL_O + x * F2_HD, tp + s * 8, smem_desc_sw128(sv + s * 2048, 16384, 1024), idesc_o,
+          tc_mma_ts(tmem_base + F2_COL_O + x * F2_HD, tp + s * 8, desc_advance(dv[st], s * 2048), idesc_o,
                     (j | s) ? 1u : 0u);
         tc_commit(&pv_done[x]);
         if (++pv_cnt[st] == users(j)) {
