@@ -52,6 +52,10 @@ template <int HD> struct FbCfg {
   // dQ_i has columns of its own when they fit (hd 64); otherwise it reuses the Sᵀ columns
   static constexpr bool DQ_ALIASED = (256 + 3 * HD > 512);
   static constexpr int COL_DQ = DQ_ALIASED ? 0 : 256 + 2 * HD;
+  // Pᵀ (16-bit, two queries per column) lives in tensor memory when 64 columns are left for it (hd 64):
+  // it is the A operand of the dV product, which then reads only dO from shared memory
+  static constexpr bool P_TMEM = (256 + 3 * HD + 64 <= 512);
+  static constexpr int COL_PT = 256 + 3 * HD;
 };
 
 struct FbParams {
@@ -239,8 +243,12 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
         for (int s = 0; s < FB_T / 16; ++s) {  // contraction over the 128 queries of this tile
           const uint32_t koff = (s / 4) * 16384 + (s % 4) * 32;  // K-major A: 16 queries = 32 B along the row
           const uint32_t moff = s * 2048;                         // MN-major B: 16 query rows of 128 B
-          tc_mma_ss(tmem_base + Cfg::COL_DV, desc_advance(dp_k, koff), desc_advance(do_mn, moff), idesc_kv,
-                    (it | s) ? 1u : 0u);
+          if (Cfg::P_TMEM)
+            tc_mma_ts(tmem_base + Cfg::COL_DV, tmem_base + Cfg::COL_PT + s * 8, desc_advance(do_mn, moff), idesc_kv,
+                      (it | s) ? 1u : 0u);
+          else
+            tc_mma_ss(tmem_base + Cfg::COL_DV, desc_advance(dp_k, koff), desc_advance(do_mn, moff), idesc_kv,
+                      (it | s) ? 1u : 0u);
           tc_mma_ss(tmem_base + Cfg::COL_DK, desc_advance(dds_k, koff), desc_advance(q_mn, moff), idesc_kv,
                     (it | s) ? 1u : 0u);
         }
@@ -361,13 +369,16 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
           PROF_ADD(3, t3, t4);
         }
         if (ok) {
+          if (Cfg::P_TMEM) tmem_st32(lane_addr + Cfg::COL_PT + half * 32, pk);  // this thread's 64 queries of Pᵀ
 #pragma unroll
           for (int v4 = 0; v4 < 8; ++v4) {
             const int cc = half * 8 + v4;  // 16-byte chunk index along the 128 queries
             const uint32_t off = (cc >> 3) * 16384 + r * 128 + (((cc & 7) ^ (r & 7)) << 4);
-            *reinterpret_cast<uint4*>(sp + off) = make_uint4(pk[v4 * 4], pk[v4 * 4 + 1], pk[v4 * 4 + 2], pk[v4 * 4 + 3]);
+            if (!Cfg::P_TMEM)
+              *reinterpret_cast<uint4*>(sp + off) = make_uint4(pk[v4 * 4], pk[v4 * 4 + 1], pk[v4 * 4 + 2], pk[v4 * 4 + 3]);
             *reinterpret_cast<uint4*>(sds + off) = make_uint4(dk_[v4 * 4], dk_[v4 * 4 + 1], dk_[v4 * 4 + 2], dk_[v4 * 4 + 3]);
           }
+          if (Cfg::P_TMEM) tc_wait_st();
           PROF_T(t45);
           tc_fence_before();
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
