@@ -29,7 +29,8 @@ extern std::atomic<int> g_attn_debug;
 
 constexpr float kLog2eB = 1.4426950408889634f;
 constexpr int FB_T = 128;           // tile edge (keys and queries)
-constexpr int FB_THREADS = 448;     // 14 warps: TMA, MMA, 8 compute, 4 dQ drain
+constexpr int FB_CWARPS = 16;        // compute warps: 4 TMEM lane quarters x 4 column quarters
+constexpr int FB_THREADS = 64 + 32 * FB_CWARPS + 128;  // TMA, MMA, compute warps, 4 dQ-drain warps
 constexpr int FB_COMPUTE = 256;     // threads in the compute warps
 
 template <int HD> struct FbCfg {
@@ -96,7 +97,7 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-__device__ __forceinline__ void compute_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ void compute_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(32 * FB_CWARPS) : "memory"); }
 
 template <typename T, int HD, bool BIAS>
 __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __grid_constant__ CUtensorMap tmQ,
@@ -135,7 +136,7 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
       mbar_init(&q_empty[i], 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(pds_full, 8);
+    mbar_init(pds_full, FB_CWARPS);
     mbar_init(dq_full, 1);
     mbar_init(dq_free, 4);
     mbar_fence_init();
@@ -285,12 +286,12 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
       PROF_T(tm_end);
       PROF_ADD(9, tm_start, tm_end);
     }
-  } else if (warp < 10) {
+  } else if (warp < 2 + FB_CWARPS) {
     // -------------------------------------------------------------------------- compute
     if (!dead) {
-      const int cw = warp - 2;           // 0..7
+      const int cw = warp - 2;           // 0..15
       const int qd = warp & 3;           // TMEM lane quarter
-      const int half = cw >> 2;          // which half of the columns
+      const int cq = cw >> 2;            // which quarter (32) of the 128 query columns
       const int r = qd * 32 + lane;      // TMEM lane = key row
       const int ct = threadIdx.x - 64;   // 0..255 within the compute group
       const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
@@ -312,7 +313,7 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
         float* s_lse2 = s_stat + (it & 1) * 256;
         float* s_delta = s_lse2 + FB_T;
         if (ct < FB_T) s_lse2[ct] = p.lse[(int64_t)bh * p.T + i0 + ct] * kLog2eB;
-        else s_delta[ct - FB_T] = p.delta[(int64_t)bh * p.T + i0 + ct - FB_T];
+        else if (ct < 2 * FB_T) s_delta[ct - FB_T] = p.delta[(int64_t)bh * p.T + i0 + ct - FB_T];
         compute_bar_sync();
         PROF_T(t1);
         if (ok) ok = mbar_wait(s_full, it & 1, 0x2600, abort_flag);
@@ -320,14 +321,14 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
         PROF_ADD(5, t0, t1);
         PROF_ADD(1, t1, t2);
         if (prof) atomicAdd(&g_prof[0], 1ull);
-        uint32_t pk[32], dk_[32];  // this thread's 64 columns of Pᵀ and dSᵀ, packed 16-bit pairs
+        uint32_t pk[16], dk_[16];  // this thread's 32 columns of Pᵀ and dSᵀ, packed 16-bit pairs
         long long t3 = 0, t4 = 0;
         if (ok) {
           tc_fence_after();
           const bool plain = !BIAS && !diag;  // no bias and not the diagonal tile: scale, subtract, 2^x
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {         // 16-column steps keep the live register set small
-            const int col0 = half * 64 + c * 16;
+          for (int c = 0; c < 2; ++c) {         // 16-column steps keep the live register set small
+            const int col0 = cq * 32 + c * 16;
             uint32_t sv_[16], dv_[16];
             PROF_T(tl0);
             tmem_ld16(lane_addr + Cfg::COL_S + col0, sv_);
@@ -369,10 +370,10 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
           PROF_ADD(3, t3, t4);
         }
         if (ok) {
-          if (Cfg::P_TMEM) tmem_st32(lane_addr + Cfg::COL_PT + half * 32, pk);  // this thread's 64 queries of Pᵀ
+          if (Cfg::P_TMEM) tmem_st16(lane_addr + Cfg::COL_PT + cq * 16, pk);  // this thread's 32 queries of Pᵀ
 #pragma unroll
-          for (int v4 = 0; v4 < 8; ++v4) {
-            const int cc = half * 8 + v4;  // 16-byte chunk index along the 128 queries
+          for (int v4 = 0; v4 < 4; ++v4) {
+            const int cc = cq * 4 + v4;  // 16-byte chunk index along the 128 queries
             const uint32_t off = (cc >> 3) * 16384 + r * 128 + (((cc & 7) ^ (r & 7)) << 4);
             if (!Cfg::P_TMEM)
               *reinterpret_cast<uint4*>(sp + off) = make_uint4(pk[v4 * 4], pk[v4 * 4 + 1], pk[v4 * 4 + 2], pk[v4 * 4 + 3]);
@@ -395,14 +396,14 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
         T* dvp = reinterpret_cast<T*>(p.dv) + b * p.sdv_b + h * p.sdv_h + (int64_t)j * p.sdv_t;
         T* dkp = reinterpret_cast<T*>(p.dk) + b * p.sdk_b + h * p.sdk_h + (int64_t)j * p.sdk_t;
 #pragma unroll 1
-        for (int c = 0; c < HD / 64; ++c) {
-          const int col0 = half * (HD / 2) + c * 32;
-          uint32_t v[32], w[32];
-          tmem_ld32(lane_addr + Cfg::COL_DV + col0, v);
-          tmem_ld32(lane_addr + Cfg::COL_DK + col0, w);
+        for (int c = 0; c < HD / 64; ++c) {  // this warp's HD / 4 columns in steps of 16
+          const int col0 = cq * (HD / 4) + c * 16;
+          uint32_t v[16], w[16];
+          tmem_ld16(lane_addr + Cfg::COL_DV + col0, v);
+          tmem_ld16(lane_addr + Cfg::COL_DK + col0, w);
           tc_wait_ld();
 #pragma unroll
-          for (int v4 = 0; v4 < 4; ++v4) {
+          for (int v4 = 0; v4 < 2; ++v4) {
             float g[8], d[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
@@ -417,15 +418,15 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
     }
   } else if (!dead) {
     // ---------------------------------------------------------------------------- dQ drain
-    // warps 10-13: lanes are query rows here; each warp adds its 32 rows of dQ_i to the fp32 accumulator.
+    // the last four warps: lanes are query rows here; each warp adds its 32 rows of dQ_i to the fp32 accumulator.
     // head_dim 64: the rows go through swizzled shared-memory boxes and the TMA unit performs the
     // reduction (cp.reduce.async.bulk.tensor), which keeps the load/store path free for the compute
     // warps; head_dim 128: vector red.global.add.
     const int qd = warp & 3;
     const int r = qd * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
-    const bool prof = (p.debug & 2) && warp == 10 && lane == 0;
-    uint8_t* stage = smem + Cfg::OFF_DQ + (warp - 10) * 8192;
+    const bool prof = (p.debug & 2) && warp == 2 + FB_CWARPS && lane == 0;
+    uint8_t* stage = smem + Cfg::OFF_DQ + (warp - 2 - FB_CWARPS) * 8192;
     if (Cfg::DQ_TMA && lane == 0) tma_prefetch_desc(&tmDQ);
     for (int it = 0; it < iters; ++it) {
       const int i0 = (kt + it) * FB_T;
