@@ -13,8 +13,10 @@
 // and an MN-major operand with 128 contraction rows, so each of K, V, Q_i, dO_i, dSᵀ sits in
 // shared memory once and serves two products.
 //
-// Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2-9 compute (thread = TMEM lane, two
-// warps per lane quarter, each taking half of the columns), warps 10-13 drain dQ_i.
+// Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2-17 compute (thread = TMEM lane, four
+// warps per lane quarter, each taking a quarter of the columns), warps 18-21 drain dQ_i.
+// At head_dim 64, Pᵀ goes into the 64 TMEM columns that are left instead of shared memory and is
+// the A operand of the dV product.
 // At head_dim 64 the scores of tile i+1 are issued before the gradient products of tile i, so the
 // compute warps work on tile i+1 while the tensor core finishes tile i.
 // TMEM columns: [0,128) Sᵀ; [128,256) dPᵀ; [256,256+hd) dV; then dK; then dQ_i (at head_dim 128
