@@ -27,4 +27,22 @@ int attn_delta(const AttnArgs& a, int hd, int dtype, cudaStream_t st);
 int attn_generic_fwd(const AttnArgs& a, int hd, int dtype, cudaStream_t st);
 int attn_generic_bwd(const AttnArgs& a, int hd, int dtype, cudaStream_t st);
 
+// ALiBi bias -(i - j) * slope as the reference's 16-bit table holds it (mode 2: fp16, mode 4: bf16):
+// distance, slope and product each rounded to nearest-even at 11 or 8 significant bits; mode 1: exact
+// fp32.  The rounding is integer arithmetic on the ALU pipe rather than three conversions per score on
+// the pipe the exponentials need.  Exact while the values stay in the 16-bit type's normal range
+// (slopes >= 2^-8 times distances below 2^23 do).
+__device__ __forceinline__ float round_significand(float x, int drop) {  // drop the low `drop` mantissa bits
+  uint32_t t = __float_as_uint(x);
+  t += ((1u << (drop - 1)) - 1u) + ((t >> drop) & 1u);
+  return __uint_as_float(t & ~((1u << drop) - 1u));
+}
+__device__ __forceinline__ float alibi_table_value(int mode, float slope, int dist) {
+  const float d = __uint_as_float(0x4B000000u | (uint32_t)dist) - 8388608.f;  // exact int -> float
+  if (mode == 1) return -slope * d;
+  const int drop = (mode == 2) ? 13 : 16;
+  const float s16 = (mode == 2) ? __half2float(__float2half_rn(slope)) : __bfloat162float(__float2bfloat16_rn(slope));
+  return -round_significand(round_significand(d, drop) * s16, drop);
+}
+
 }  // namespace tfb

@@ -75,9 +75,7 @@ struct FbParams {
 };
 
 __device__ __forceinline__ float alibi_term_b(int mode, float slope, int dist) {
-  if (mode == 1) return -slope * (float)dist;
-  if (mode == 2) return __half2float(__hmul(__float2half_rn(-(float)dist), __float2half_rn(slope)));
-  return __bfloat162float(__hmul(__float2bfloat16_rn(-(float)dist), __float2bfloat16_rn(slope)));
+  return alibi_table_value(mode, slope, dist);
 }
 
 // Cycle counters for the timing switch (debug bit 1): [0] CTA iterations, [1..5] compute warp 2:
