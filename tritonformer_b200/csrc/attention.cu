@@ -3,9 +3,11 @@
 
 namespace tfb {
 extern std::atomic<int> g_force_fallback_attn;
+extern std::atomic<int> g_attn_debug;
 bool attn_tc05_fwd_eligible(const AttnArgs& a, int hd);
 int attn_tc05_fwd(const AttnArgs& a, int hd, int dtype, cudaStream_t st);
 int attn_fwd2_tc05(const AttnArgs& a, int dtype, cudaStream_t st);
+int attn_fwd1_tc05(const AttnArgs& a, int dtype, cudaStream_t st);
 bool attn_tc05_bwd_eligible(const AttnArgs& a, int hd);
 int attn_tc05_bwd(const AttnArgs& a, int hd, int dtype, cudaStream_t st);
 }  // namespace tfb
@@ -51,7 +53,11 @@ extern "C" int tfb_attention_fwd(const void* q, const void* k, const void* v, vo
   a.slopes = slopes; a.bias = bias; a.bias_sh = bias_sh; a.bias_si = bias_si;
   const bool fast = !g_force_fallback_attn.load() && attn_tc05_fwd_eligible(a, (int)hd);
   if (path) *path = fast ? 1 : 0;
-  if (fast && hd == 64) return attn_fwd2_tc05(a, dtype, (cudaStream_t)stream);  // two query tiles per CTA
+  if (fast && hd == 64) {
+    // one tile per CTA with doubled score buffers; tfb_debug_set(2, 16) selects the two-tiles-per-CTA kernel
+    if (g_attn_debug.load() & 16) return attn_fwd2_tc05(a, dtype, (cudaStream_t)stream);
+    return attn_fwd1_tc05(a, dtype, (cudaStream_t)stream);
+  }
   if (fast) return attn_tc05_fwd(a, (int)hd, dtype, (cudaStream_t)stream);
   return attn_generic_fwd(a, (int)hd, dtype, (cudaStream_t)stream);
 }

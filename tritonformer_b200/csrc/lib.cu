@@ -27,9 +27,11 @@ int64_t gemm_tc05_workspace_bytes();
 int attn_tc05_status(int reset);
 int attn_bwd_tc05_status(int reset);
 int attn_fwd2_tc05_status(int reset);
+int attn_fwd1_tc05_status(int reset);
 int attn_bwd_tc05_counters(unsigned long long* out);
 int gemm_pair_counters(int cta, unsigned long long* out);
 int attn_fwd2_tc05_counters(unsigned long long* out);
+int attn_fwd1_tc05_counters(unsigned long long* out);
 std::atomic<int> g_counter_select{-1};
 }  // namespace tfb
 
@@ -46,12 +48,14 @@ extern "C" int tfb_device_status(int reset) {
   const int c = attn_bwd_tc05_status(reset);
   const int d = attn_fwd2_tc05_status(reset);
   const int e = gemm_pair_tc05_status(reset);
-  return a ? a : (b ? b : (c ? c : (d ? d : e)));
+  const int f = attn_fwd1_tc05_status(reset);
+  return a ? a : (b ? b : (c ? c : (d ? d : (e ? e : f))));
 }
 
 extern "C" int tfb_debug_counters(unsigned long long* out16) {
   const int sel = g_counter_select.load();
   if (sel == -2) return attn_fwd2_tc05_counters(out16);
+  if (sel == -3) return attn_fwd1_tc05_counters(out16);
   return sel >= 0 ? gemm_pair_counters(sel, out16) : attn_bwd_tc05_counters(out16);
 }
 
