@@ -4,12 +4,14 @@
 //   warp 0      TMA producer (Q once, K_j / V_j tiles of 128 keys through 3-stage rings)
 //   warp 1      MMA issuer (one elected lane, an event loop over non-blocking barrier probes)
 //   warps 2-9   softmax: two warps per TMEM lane quarter, each taking 64 of the 128 keys of a step
+//               (F1_NW; four per quarter measured slower: the pass is bound by issue slots and the
+//               exponential unit of a scheduler, not by latency)
 // The scores of step j+1 are computed into the other score buffer while the softmax warps work on
 // step j, so they go from step to step without waiting for the tensor core (with one buffer per tile
 // the round trip "probabilities ready -> next scores issued -> scores landed" is a fixed 1.5 k cycles
-// per step that nothing hides).  A thread owns 64 keys of one query row; the two warps of a row pair
-// agree on the row maximum through shared memory once per step (an mbarrier with two arrivals per
-// lane quarter, so the wait is bounded), keep separate partial row sums and add them at the end.
+// per step that nothing hides).  A thread owns 64 keys of one query row; the two warps of a row
+// exchange one value per step through shared memory (an mbarrier with one arrival per warp and lane
+// quarter, so the wait is bounded), keep separate partial row sums and add them at the end.
 // Below the diagonal the softmax is a single pass against the maximum of the EARLIER steps (redone in
 // two passes if the new maximum exceeds it by more than 2^8, which also bounds P inside fp16/bf16
 // range; the accumulator row is rescaled only then), with one exponential in four on the FMA pipe.
@@ -29,14 +31,18 @@ constexpr float kLog2e1 = 1.4426950408889634f;
 constexpr float kLn2_1 = 0.6931471805599453f;
 constexpr int F1_HD = 64;
 constexpr int F1_TILE = 128;
-constexpr int F1_THREADS = 320;
+constexpr int F1_NW = 2;                       // softmax warps per TMEM lane quarter (per query row)
+constexpr int F1_KW = F1_TILE / F1_NW;         // keys of a step per softmax warp
+constexpr int F1_NC = F1_KW / 32;              // 32-key chunks per warp and step
+constexpr int F1_OW = F1_HD / F1_NW;           // accumulator columns per warp (rescale, output)
+constexpr int F1_THREADS = 64 + 128 * F1_NW;
 constexpr int F1_STAGES = 3;
 constexpr int F1_TILE_BYTES = 16384;  // 128 rows x 64 x 2 B
 constexpr int F1_OFF_Q = 0;
 constexpr int F1_OFF_K = F1_TILE_BYTES;                          // [STAGES]
 constexpr int F1_OFF_V = F1_OFF_K + F1_STAGES * F1_TILE_BYTES;   // [STAGES]
-constexpr int F1_OFF_X = F1_OFF_V + F1_STAGES * F1_TILE_BYTES;   // row-pair exchange: [2 parities][2 halves][128 rows] floats
-constexpr int F1_OFF_BAR = F1_OFF_X + 2 * 2 * 128 * 4;
+constexpr int F1_OFF_X = F1_OFF_V + F1_STAGES * F1_TILE_BYTES;   // row exchange: [2 parities][warps per row][128 rows] floats
+constexpr int F1_OFF_BAR = F1_OFF_X + 2 * F1_NW * 128 * 4;
 constexpr int F1_SMEM_BYTES = F1_OFF_BAR + 256 + 1024;
 constexpr int F1_COL_S = 0, F1_COL_P = 256, F1_COL_O = 384;
 constexpr float kRescale1 = 8.0f;  // log2 units
@@ -112,10 +118,10 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 8);
+      mbar_init(&p_full[i], 4 * F1_NW);
       mbar_init(&pv_done[i], 1);
     }
-    for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 2);
+    for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], F1_NW);
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -212,7 +218,7 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
   } else if (!dead) {
     // -------------------------------------------------------------------------- softmax
     const int qd = warp & 3;            // TMEM lane quarter
-    const int ch = (warp - 2) >> 2;     // which 64 of the step's 128 keys
+    const int ch = (warp - 2) >> 2;     // which F1_KW of the step's 128 keys
     const int r = qd * 32 + lane;       // row within the tile == TMEM lane
     const int i = qt * F1_TILE + r;     // query
     const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
@@ -229,26 +235,34 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
     // other 64 keys of the same rows).  Both warps of a pair take the same path through a step, so
     // they make the same number of exchanges.  Bounded wait; double-buffered by exchange parity.
     long long xw_total = 0;
-    auto exchange = [&](float mine, bool& fine) -> float {
+    // Row exchange: publish a value for this row and combine the values of the other warps that share
+    // the row (maximum, or sum when `add`).  All warps of a row take the same path through a step, so
+    // they make the same number of exchanges.  Bounded wait; double-buffered by exchange parity.
+    auto exchange = [&](float mine, bool& fine, bool add) -> float {
       const long long x0 = clock64();
-      float* slot = xch + xpar * 256;
+      float* slot = xch + xpar * (F1_NW * 128);
       slot[ch * 128 + r] = mine;
       __syncwarp();
       if (lane == 0) mbar_arrive(&pair_bar[qd]);
       if (fine) fine = mbar_wait(&pair_bar[qd], pair_phase, 0x5c00 | qd, abort_flag);
       pair_phase ^= 1;
-      const float other = slot[(ch ^ 1) * 128 + r];
+      float acc = mine;
+#pragma unroll
+      for (int w = 1; w < F1_NW; ++w) {
+        const float other = slot[((ch + w) % F1_NW) * 128 + r];
+        acc = add ? acc + other : fmaxf(acc, other);
+      }
       xpar ^= 1;
       xw_total += clock64() - x0;
-      return other;
+      return acc;
     };
     for (int j = 0; j <= jlast; ++j) {
       const int bsel = j & 1;
-      const int j0 = j * F1_TILE + ch * 64;   // first key of this thread's share
+      const int j0 = j * F1_TILE + ch * F1_KW;  // first key of this thread's share
       const bool diag = (j == jlast);
       const bool plain = !BIAS && !diag;      // scores need only the common scale
-      const uint32_t s_addr = lane_addr + F1_COL_S + bsel * 128 + ch * 64;
-      const uint32_t p_addr = lane_addr + F1_COL_P + bsel * 64 + ch * 32;
+      const uint32_t s_addr = lane_addr + F1_COL_S + bsel * 128 + ch * F1_KW;
+      const uint32_t p_addr = lane_addr + F1_COL_P + bsel * 64 + ch * (F1_KW / 2);
       const bool prof = (p.debug & 2) && warp == 2 && lane == 0;
       const long long w0 = clock64();
       if (ok) ok = mbar_wait(&s_full[bsel], (j >> 1) & 1, 0x5700 | bsel, abort_flag);
@@ -268,10 +282,10 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
         uint32_t buf[2][32];
         tmem_ld32(s_addr, buf[0]);
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
+        for (int c = 0; c < F1_NC; ++c) {
           tc_wait_ld();
-          if (c < 1) tmem_ld32(s_addr + 32, buf[1]);
-          const uint32_t* v = buf[c];
+          if (c + 1 < F1_NC) tmem_ld32(s_addr + (c + 1) * 32, buf[(c + 1) & 1]);
+          const uint32_t* v = buf[c & 1];
           float g[32];
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
@@ -292,7 +306,7 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
         }
         const float part = (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
         float bad = __any_sync(0xffffffffu, !(part <= 256.f)) ? 1.f : 0.f;  // also true for inf / nan
-        bad = fmaxf(bad, exchange(bad, ok));
+        bad = exchange(bad, ok, false);
         if (bad == 0.f) {
           l_run += part;
           done = true;
@@ -305,10 +319,10 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
           uint32_t buf[2][32];
           tmem_ld32(s_addr, buf[0]);
 #pragma unroll
-          for (int c = 0; c < 2; ++c) {
+          for (int c = 0; c < F1_NC; ++c) {
             tc_wait_ld();
-            if (c < 1) tmem_ld32(s_addr + 32, buf[1]);
-            const uint32_t* v = buf[c];
+            if (c + 1 < F1_NC) tmem_ld32(s_addr + (c + 1) * 32, buf[(c + 1) & 1]);
+            const uint32_t* v = buf[c & 1];
             if (plain) {
 #pragma unroll
               for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(v[e]));
@@ -326,7 +340,7 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
         }
         float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
         if (plain) mx *= c2;  // c2 > 0: scaling commutes with the maximum
-        mx = fmaxf(mx, exchange(mx, ok));  // finite: every row sees key 0 .. i within its first steps
+        mx = exchange(mx, ok, false);  // finite: every row sees key 0 .. i within its first steps
         m_run = fmaxf(m_run, mx);
         // every earlier P·V must have retired before O is rescaled or this P buffer rewritten (the
         // tensor core retires them in order, so the latest one covers the rest)
@@ -339,13 +353,15 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
           if (__any_sync(0xffffffffu, grow)) {
             tc_fence_after();
             const float f = grow ? ex2_mufu(m_used - m_run) : 1.f;
-            // each warp of the pair rescales half of the accumulator row
-            uint32_t v[32];
-            tmem_ld32(o_addr + ch * 32, v);
+            // each warp of the row rescales its share of the accumulator columns
+            uint32_t v[F1_OW];
+            if (F1_OW == 32) tmem_ld32(o_addr + ch * F1_OW, *reinterpret_cast<uint32_t(*)[32]>(v));
+            else tmem_ld16(o_addr + ch * F1_OW, *reinterpret_cast<uint32_t(*)[16]>(v));
             tc_wait_ld();
 #pragma unroll
-            for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * f);
-            tmem_st32(o_addr + ch * 32, v);
+            for (int e = 0; e < F1_OW; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * f);
+            if (F1_OW == 32) tmem_st32(o_addr + ch * F1_OW, *reinterpret_cast<uint32_t(*)[32]>(v));
+            else tmem_st16(o_addr + ch * F1_OW, *reinterpret_cast<uint32_t(*)[16]>(v));
             tc_wait_st();
             l_run *= f;
             if (grow) m_used = m_run;
@@ -357,10 +373,10 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
           uint32_t buf[2][32];
           tmem_ld32(s_addr, buf[0]);
 #pragma unroll
-          for (int c = 0; c < 2; ++c) {
+          for (int c = 0; c < F1_NC; ++c) {
             tc_wait_ld();
-            if (c < 1) tmem_ld32(s_addr + 32, buf[1]);
-            const uint32_t* v = buf[c];
+            if (c + 1 < F1_NC) tmem_ld32(s_addr + (c + 1) * 32, buf[(c + 1) & 1]);
+            const uint32_t* v = buf[c & 1];
             float g[32];
             if (plain) {
               const float neg_m = -m_used;
@@ -398,16 +414,17 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
       if (prof) { atomicAdd(&g_prof_f1[3], (unsigned long long)(xw_total - xw)); }
     }
     // the row sum is the sum of the pair's partial sums
-    const float l_tot = l_run + exchange(l_run, ok);
+    const float l_tot = exchange(l_run, ok, true);
     if (ok && mbar_wait(&pv_done[jlast & 1], (jlast >> 1) & 1, 0x5900, abort_flag)) {
       tc_fence_after();
       const float inv = 1.f / l_tot;
-      T* orow = reinterpret_cast<T*>(p.out) + b * p.so_b + h * p.so_h + (int64_t)i * p.so_t + ch * 32;
-      uint32_t v[32];
-      tmem_ld32(o_addr + ch * 32, v);  // each warp of the pair writes half of the row
+      T* orow = reinterpret_cast<T*>(p.out) + b * p.so_b + h * p.so_h + (int64_t)i * p.so_t + ch * F1_OW;
+      uint32_t v[F1_OW];  // each warp of the row writes its share of the columns
+      if (F1_OW == 32) tmem_ld32(o_addr + ch * F1_OW, *reinterpret_cast<uint32_t(*)[32]>(v));
+      else tmem_ld16(o_addr + ch * F1_OW, *reinterpret_cast<uint32_t(*)[16]>(v));
       tc_wait_ld();
 #pragma unroll
-      for (int v4 = 0; v4 < 4; ++v4) {
+      for (int v4 = 0; v4 < F1_OW / 8; ++v4) {
         float g[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) g[e] = __uint_as_float(v[v4 * 8 + e]) * inv;
