@@ -109,3 +109,36 @@ def test_reference_asserts_are_kept():
         CausalAttention.apply(mk(1, 2, 64, 48), mk(1, 2, 64, 48), mk(1, 2, 64, 48))
     with pytest.raises(AssertionError, match="number of heads"):
         BiasedCausalAttention.apply(mk(1, 2, 64, 64), mk(1, 2, 64, 64), mk(1, 2, 64, 64), mk(3, 64, 64))
+
+
+@pytest.mark.parametrize("dims", [(2, 4, 2048, 64), (1, 5, 640, 64), (2, 16, 512, 64)])
+@pytest.mark.parametrize("alibi", [False, True])
+def test_both_head_dim_64_forward_kernels_agree(dims, alibi):
+    """head_dim 64 has two tcgen05 forward kernels (one query tile per CTA with doubled score buffers, the
+    default; two query tiles per CTA, selected by a switch).  Both must match the oracle and each other."""
+    from tritonformer_b200 import _lib
+    from tritonformer_b200.attention import _Bias, attention_forward
+    b, nh, sq, hd = dims
+    q, k, v, _ = _make(dims, torch.float16, True)
+    q, k, v = q.detach(), k.detach(), v.detach()
+    slopes = torch.tensor([2.0 ** (-8.0 * (i + 1) / nh) for i in range(nh)], device="cuda") if alibi else None
+    bias = _Bias(slopes=slopes)
+    out1, lse1, _ = attention_forward(q, k, v, bias)
+    _lib.lib.tfb_debug_set(2, 16)
+    try:
+        out2, lse2, _ = attention_forward(q, k, v, bias)
+    finally:
+        _lib.lib.tfb_debug_set(2, 0)
+    torch.cuda.synchronize()
+    assert _lib.lib.tfb_device_status(0) == 0
+    bias_f32 = None
+    if alibi:
+        pos = torch.arange(sq, device="cuda")
+        dist = (pos.view(sq, 1) - pos.view(1, sq)).clamp(min=0).float()
+        bias_f32 = -dist.view(1, sq, sq) * slopes.view(nh, 1, 1)
+    ref = ops.attention(q.float(), k.float(), v.float(), bias_f32)
+    for out in (out1, out2):
+        assert_close(out, ref, 1e-2, "out")
+        assert norm_rel(out, ref) < 2e-3
+    assert_close(out1, out2, 4e-3, "kernels")
+    assert_close(lse1, lse2, 2e-3, "lse")
