@@ -111,11 +111,12 @@ def test_reference_asserts_are_kept():
         BiasedCausalAttention.apply(mk(1, 2, 64, 64), mk(1, 2, 64, 64), mk(1, 2, 64, 64), mk(3, 64, 64))
 
 
-@pytest.mark.parametrize("dims", [(2, 4, 2048, 64), (1, 5, 640, 64), (2, 16, 512, 64)])
+@pytest.mark.parametrize("dims", [(2, 4, 2048, 64), (1, 5, 640, 64), (2, 16, 512, 64), (1, 3, 1024, 128)])
 @pytest.mark.parametrize("alibi", [False, True])
-def test_both_head_dim_64_forward_kernels_agree(dims, alibi):
-    """head_dim 64 has two tcgen05 forward kernels (one query tile per CTA with doubled score buffers, the
-    default; two query tiles per CTA, selected by a switch).  Both must match the oracle and each other."""
+def test_both_generations_of_forward_kernels_agree(dims, alibi):
+    """The tcgen05 forward has two generations of kernels: one query tile per CTA with doubled score buffers and
+    P in tensor memory (the default), and the earlier ones selected by a switch (two query tiles per CTA at
+    head_dim 64, P through shared memory at 128).  Both must match the oracle and each other."""
     from tritonformer_b200 import _lib
     from tritonformer_b200.attention import _Bias, attention_forward
     b, nh, sq, hd = dims

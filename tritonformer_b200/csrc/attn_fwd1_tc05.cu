@@ -1,5 +1,5 @@
 // Causal flash attention forward on tcgen05 / TMEM, one 128-query tile per CTA with its score and P
-// buffers doubled and eight softmax warps (head_dim 64, T % 128 == 0).
+// buffers doubled and eight softmax warps (head_dim 64 or 128, T % 128 == 0).
 //
 //   warp 0      TMA producer (Q once, K_j / V_j tiles of 128 keys through 3-stage rings)
 //   warp 1      MMA issuer (one elected lane, an event loop over non-blocking barrier probes)
@@ -16,7 +16,7 @@
 // two passes if the new maximum exceeds it by more than 2^8, which also bounds P inside fp16/bf16
 // range; the accumulator row is rescaled only then), with one exponential in four on the FMA pipe.
 // P is stored 16-bit, two keys per 32-bit column, into tensor memory and is the A operand of P·V.
-// TMEM columns: [0,128) S0, [128,256) S1, [256,320) P0, [320,384) P1, [384,448) O.
+// TMEM columns: [0,128) S0, [128,256) S1, [256,320) P0, [320,384) P1, [384,384+head_dim) O.
 #include "attn.cuh"
 #include "tc05.cuh"
 #include <type_traits>
@@ -29,22 +29,27 @@ namespace {
 
 constexpr float kLog2e1 = 1.4426950408889634f;
 constexpr float kLn2_1 = 0.6931471805599453f;
-constexpr int F1_HD = 64;
 constexpr int F1_TILE = 128;
 constexpr int F1_NW = 2;                       // softmax warps per TMEM lane quarter (per query row)
 constexpr int F1_KW = F1_TILE / F1_NW;         // keys of a step per softmax warp
 constexpr int F1_NC = F1_KW / 32;              // 32-key chunks per warp and step
-constexpr int F1_OW = F1_HD / F1_NW;           // accumulator columns per warp (rescale, output)
 constexpr int F1_THREADS = 64 + 128 * F1_NW;
-constexpr int F1_STAGES = 3;
-constexpr int F1_TILE_BYTES = 16384;  // 128 rows x 64 x 2 B
-constexpr int F1_OFF_Q = 0;
-constexpr int F1_OFF_K = F1_TILE_BYTES;                          // [STAGES]
-constexpr int F1_OFF_V = F1_OFF_K + F1_STAGES * F1_TILE_BYTES;   // [STAGES]
-constexpr int F1_OFF_X = F1_OFF_V + F1_STAGES * F1_TILE_BYTES;   // row exchange: [2 parities][warps per row][128 rows] floats
-constexpr int F1_OFF_BAR = F1_OFF_X + 2 * F1_NW * 128 * 4;
-constexpr int F1_SMEM_BYTES = F1_OFF_BAR + 256 + 1024;
 constexpr int F1_COL_S = 0, F1_COL_P = 256, F1_COL_O = 384;
+
+template <int HD> struct F1Cfg {
+  static constexpr int PANELS = HD / 64;                 // 64-element (128-byte) panels along head_dim
+  static constexpr int TILE_BYTES = PANELS * 16384;      // 128 rows x HD x 2 B
+  static constexpr int STAGES = (HD == 64) ? 3 : 2;      // K / V ring depth (shared memory bound at 128)
+  static constexpr int OW = HD / F1_NW;                  // accumulator columns per warp (rescale, output)
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = TILE_BYTES;                         // [STAGES]
+  static constexpr int OFF_V = OFF_K + STAGES * TILE_BYTES;        // [STAGES]
+  static constexpr int OFF_X = OFF_V + STAGES * TILE_BYTES;        // row exchange: [2 parities][warps per row][128 rows] floats
+  static constexpr int OFF_BAR = OFF_X + 2 * F1_NW * 128 * 4;
+  static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+  static_assert(OW % 32 == 0, "a softmax warp handles whole 32-column chunks of the accumulator");
+  static_assert(F1_COL_O + HD <= 512, "tensor memory");
+};
 constexpr float kRescale1 = 8.0f;  // log2 units
 
 struct F1Params {
@@ -82,11 +87,15 @@ __device__ __forceinline__ float ex2_fma1(float x) {
 static __device__ unsigned long long g_prof_f1[16];
 #define F1_PROF(idx, t0, t1) do { if (prof) atomicAdd(&g_prof_f1[idx], (unsigned long long)((t1) - (t0))); } while (0)
 
-template <typename T, bool BIAS>
+template <typename T, int HD, bool BIAS>
 __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __grid_constant__ CUtensorMap tmQ,
                                                                        const __grid_constant__ CUtensorMap tmK,
                                                                        const __grid_constant__ CUtensorMap tmV,
                                                                        const F1Params p) {
+  using Cfg = F1Cfg<HD>;
+  constexpr int F1_STAGES = Cfg::STAGES, F1_TILE_BYTES = Cfg::TILE_BYTES, F1_OW = Cfg::OW;
+  constexpr int F1_OFF_Q = Cfg::OFF_Q, F1_OFF_K = Cfg::OFF_K, F1_OFF_V = Cfg::OFF_V, F1_OFF_X = Cfg::OFF_X;
+  constexpr int F1_OFF_BAR = Cfg::OFF_BAR;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + F1_OFF_BAR);
@@ -145,16 +154,21 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
       tma_prefetch_desc(&tmK);
       tma_prefetch_desc(&tmV);
       mbar_expect_tx(q_full, F1_TILE_BYTES);
-      tma_load_4d(smem + F1_OFF_Q, &tmQ, 0, qt * F1_TILE, h, b, q_full);
+#pragma unroll
+      for (int c = 0; c < Cfg::PANELS; ++c) tma_load_4d(smem + F1_OFF_Q + c * 16384, &tmQ, c * 64, qt * F1_TILE, h, b, q_full);
       int st = 0;
       uint32_t ph = 0;
       for (int j = 0; j <= jlast; ++j) {
         if (!mbar_wait(&k_empty[st], ph ^ 1, 0x5100 | st, abort_flag)) break;
         mbar_expect_tx(&k_full[st], F1_TILE_BYTES);
-        tma_load_4d(smem + F1_OFF_K + st * F1_TILE_BYTES, &tmK, 0, j * F1_TILE, h, b, &k_full[st]);
+#pragma unroll
+        for (int c = 0; c < Cfg::PANELS; ++c)
+          tma_load_4d(smem + F1_OFF_K + st * F1_TILE_BYTES + c * 16384, &tmK, c * 64, j * F1_TILE, h, b, &k_full[st]);
         if (!mbar_wait(&v_empty[st], ph ^ 1, 0x5200 | st, abort_flag)) break;
         mbar_expect_tx(&v_full[st], F1_TILE_BYTES);
-        tma_load_4d(smem + F1_OFF_V + st * F1_TILE_BYTES, &tmV, 0, j * F1_TILE, h, b, &v_full[st]);
+#pragma unroll
+        for (int c = 0; c < Cfg::PANELS; ++c)
+          tma_load_4d(smem + F1_OFF_V + st * F1_TILE_BYTES + c * 16384, &tmV, c * 64, j * F1_TILE, h, b, &v_full[st]);
         if (++st == F1_STAGES) { st = 0; ph ^= 1; }
       }
     }
@@ -163,7 +177,7 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
     if (lane == 0 && !dead) {
       constexpr int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
       constexpr uint32_t idesc_s = instr_desc_f16(128, 128, fmt, 0, 0);
-      constexpr uint32_t idesc_o = instr_desc_f16(128, F1_HD, fmt, 0, 1);
+      constexpr uint32_t idesc_o = instr_desc_f16(128, HD, fmt, 0, 1);
       bool ok = mbar_wait(q_full, 0, 0x5300, abort_flag);
       const uint64_t dq = smem_desc_sw128(smem_u32(smem + F1_OFF_Q), 16, 1024);
       // Event loop: the next scores go out as soon as their buffer has been read (two steps back) and
@@ -178,9 +192,11 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
           tc_fence_after();
           const uint64_t dk = smem_desc_sw128(smem_u32(smem + F1_OFF_K + ks * F1_TILE_BYTES), 16, 1024);
 #pragma unroll
-          for (int s = 0; s < F1_HD / 16; ++s)
-            tc_mma_ss(tmem_base + F1_COL_S + (us & 1) * 128, desc_advance(dq, s * 32), desc_advance(dk, s * 32), idesc_s,
+          for (int s = 0; s < HD / 16; ++s) {
+            const uint32_t off = (s / 4) * 16384 + (s % 4) * 32;  // 64-element panel, then 32 bytes per k-step
+            tc_mma_ss(tmem_base + F1_COL_S + (us & 1) * 128, desc_advance(dq, off), desc_advance(dk, off), idesc_s,
                       s ? 1u : 0u);
+          }
           tc_commit(&s_full[us & 1]);
           tc_commit(&k_empty[ks]);
           if (++ks == F1_STAGES) { ks = 0; kph ^= 1; }
@@ -354,14 +370,15 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
             tc_fence_after();
             const float f = grow ? ex2_mufu(m_used - m_run) : 1.f;
             // each warp of the row rescales its share of the accumulator columns
-            uint32_t v[F1_OW];
-            if (F1_OW == 32) tmem_ld32(o_addr + ch * F1_OW, *reinterpret_cast<uint32_t(*)[32]>(v));
-            else tmem_ld16(o_addr + ch * F1_OW, *reinterpret_cast<uint32_t(*)[16]>(v));
-            tc_wait_ld();
 #pragma unroll
-            for (int e = 0; e < F1_OW; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * f);
-            if (F1_OW == 32) tmem_st32(o_addr + ch * F1_OW, *reinterpret_cast<uint32_t(*)[32]>(v));
-            else tmem_st16(o_addr + ch * F1_OW, *reinterpret_cast<uint32_t(*)[16]>(v));
+            for (int cc = 0; cc < F1_OW / 32; ++cc) {
+              uint32_t v[32];
+              tmem_ld32(o_addr + ch * F1_OW + cc * 32, v);
+              tc_wait_ld();
+#pragma unroll
+              for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * f);
+              tmem_st32(o_addr + ch * F1_OW + cc * 32, v);
+            }
             tc_wait_st();
             l_run *= f;
             if (grow) m_used = m_run;
@@ -419,16 +436,18 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
       tc_fence_after();
       const float inv = 1.f / l_tot;
       T* orow = reinterpret_cast<T*>(p.out) + b * p.so_b + h * p.so_h + (int64_t)i * p.so_t + ch * F1_OW;
-      uint32_t v[F1_OW];  // each warp of the row writes its share of the columns
-      if (F1_OW == 32) tmem_ld32(o_addr + ch * F1_OW, *reinterpret_cast<uint32_t(*)[32]>(v));
-      else tmem_ld16(o_addr + ch * F1_OW, *reinterpret_cast<uint32_t(*)[16]>(v));
-      tc_wait_ld();
 #pragma unroll
-      for (int v4 = 0; v4 < F1_OW / 8; ++v4) {
-        float g[8];
+      for (int cc = 0; cc < F1_OW / 32; ++cc) {  // each warp of the row writes its share of the columns
+        uint32_t v[32];
+        tmem_ld32(o_addr + ch * F1_OW + cc * 32, v);
+        tc_wait_ld();
 #pragma unroll
-        for (int e = 0; e < 8; ++e) g[e] = __uint_as_float(v[v4 * 8 + e]) * inv;
-        *reinterpret_cast<uint4*>(orow + v4 * 8) = pack8<T>(g);
+        for (int v4 = 0; v4 < 4; ++v4) {
+          float g[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) g[e] = __uint_as_float(v[v4 * 8 + e]) * inv;
+          *reinterpret_cast<uint4*>(orow + cc * 32 + v4 * 8) = pack8<T>(g);
+        }
       }
       if (ch == 0) p.lse[(int64_t)bh * p.T + i] = (m_used + log2f(l_tot)) * kLn2_1;
     }
@@ -462,12 +481,13 @@ int attn_fwd1_tc05_counters(unsigned long long* out) {
 int encode_tmap_sw128(CUtensorMap* out, const void* base, int dtype, int rank, const uint64_t* dims,
                       const uint64_t* strides_bytes, const uint32_t* box);
 
-template <typename T>
+template <typename T, int HD>
 static int fwd1_launch(const AttnArgs& a, int dtype, cudaStream_t st) {
+  using Cfg = F1Cfg<HD>;
   CUtensorMap tq, tk, tv;
   int rc;
   const uint32_t box[4] = {64, 128, 1, 1};
-  const uint64_t dims[4] = {(uint64_t)F1_HD, (uint64_t)a.T, (uint64_t)a.H, (uint64_t)a.B};
+  const uint64_t dims[4] = {(uint64_t)HD, (uint64_t)a.T, (uint64_t)a.H, (uint64_t)a.B};
   {
     const uint64_t s[3] = {(uint64_t)a.sq.t * 2, (uint64_t)a.sq.h * 2, (uint64_t)a.sq.b * 2};
     if ((rc = encode_tmap_sw128(&tq, a.q, dtype, 4, dims, s, box))) return rc;
@@ -485,18 +505,21 @@ static int fwd1_launch(const AttnArgs& a, int dtype, cudaStream_t st) {
   p.H = a.H; p.T = a.T; p.scale = a.scale; p.bias_mode = a.bias_mode; p.slopes = a.slopes;
   p.debug = g_attn_debug.load();
   static std::atomic<uint64_t> done_plain{0}, done_bias{0};
-  if ((rc = ensure_dynamic_smem(attn_fwd1_tc05_kernel<T, false>, F1_SMEM_BYTES, done_plain, "attention_fwd(tcgen05)")))
+  if ((rc = ensure_dynamic_smem(attn_fwd1_tc05_kernel<T, HD, false>, Cfg::SMEM_BYTES, done_plain, "attention_fwd(tcgen05)")))
     return rc;
-  if ((rc = ensure_dynamic_smem(attn_fwd1_tc05_kernel<T, true>, F1_SMEM_BYTES, done_bias, "attention_fwd(tcgen05)")))
+  if ((rc = ensure_dynamic_smem(attn_fwd1_tc05_kernel<T, HD, true>, Cfg::SMEM_BYTES, done_bias, "attention_fwd(tcgen05)")))
     return rc;
   dim3 grid(a.T / F1_TILE, a.B * a.H);
-  if (a.bias_mode) launch_overlapped(attn_fwd1_tc05_kernel<T, true>, grid, dim3(F1_THREADS), F1_SMEM_BYTES, st, tq, tk, tv, p);
-  else launch_overlapped(attn_fwd1_tc05_kernel<T, false>, grid, dim3(F1_THREADS), F1_SMEM_BYTES, st, tq, tk, tv, p);
+  if (a.bias_mode) launch_overlapped(attn_fwd1_tc05_kernel<T, HD, true>, grid, dim3(F1_THREADS), Cfg::SMEM_BYTES, st, tq, tk, tv, p);
+  else launch_overlapped(attn_fwd1_tc05_kernel<T, HD, false>, grid, dim3(F1_THREADS), Cfg::SMEM_BYTES, st, tq, tk, tv, p);
   return launched("attention_fwd(tcgen05, doubled score buffers)");
 }
 
-int attn_fwd1_tc05(const AttnArgs& a, int dtype, cudaStream_t st) {
-  TFB_DISPATCH_16(dtype, T, { return fwd1_launch<T>(a, dtype, st); })
+int attn_fwd1_tc05(const AttnArgs& a, int hd, int dtype, cudaStream_t st) {
+  TFB_DISPATCH_16(dtype, T, {
+    if (hd == 64) return fwd1_launch<T, 64>(a, dtype, st);
+    return fwd1_launch<T, 128>(a, dtype, st);
+  })
 }
 
 }  // namespace tfb
