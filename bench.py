@@ -455,7 +455,7 @@ def run_kernel_bench(args):
             def fwd():
                 res["o"], res["lse"], _ = A.attention_forward(q, k, v, bias)
             fl = 2.0 * bsz * h * t * t * hd  # two products, causal half
-            emit("attn_fwd1_tc05_kernel" if hd == 64 else "attn_fwd_tc05_kernel", name, _time_cuda(fwd, iters, warmup), fl, "TFLOP/s", "tensor")
+            emit("attn_fwd1_tc05_kernel", name, _time_cuda(fwd, iters, warmup), fl, "TFLOP/s", "tensor")
             bwd = lambda: A.attention_backward(do, res["o"], q, k, v, res["lse"], bias)
             emit("attn_bwd_tc05_kernel (+delta, dQ convert)", name, _time_cuda(bwd, iters, warmup), 2.5 * fl,
                  "TFLOP/s", "tensor")
