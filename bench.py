@@ -505,6 +505,21 @@ def run_kernel_bench(args):
         a, b = torch.randn(n, device=dev).half(), torch.randn(n, device=dev).half()
         emit("relu_bwd_vec_kernel", f"{n} elements fp16", _time_cuda(lambda: LIN.relu_backward(a, b), iters, warmup),
              6.0 * n, "GB/s", "hbm")
+    if which in ("embed", "all"):
+        from tritonformer_b200 import embedding as EMB
+        bsz, t, d, v = (4, 2048, 1024, 50304) if args.small else (32, 2048, 1024, 50304)
+        ids = torch.randint(0, v, (bsz, t), device=dev)
+        tok, pos = torch.randn((v, d), device=dev).half(), torch.randn((t, d), device=dev).half()
+        dout = torch.randn((bsz, t, d), device=dev).half()
+        dtok, dpos = torch.zeros_like(tok), torch.zeros_like(pos)
+        case = f"B{bsz} T{t} d{d} vocab {v} fp16"
+        # forward: every position reads one table row and writes one row
+        emit("embed_fwd_kernel", case, _time_cuda(lambda: EMB.embedding_forward(ids, tok, pos), iters, warmup),
+             4.0 * bsz * t * d, "GB/s", "hbm")
+        # backward: reads the incoming row, reads and writes the table-gradient row it lands in
+        emit("embed_index + embed_bwd_scatter + embed_bwd_fold", case,
+             _time_cuda(lambda: EMB.embedding_backward(ids, dout, dtok, dpos), iters, warmup),
+             6.0 * bsz * t * d, "GB/s", "hbm")
     assert L.device_status() == 0
     return out
 
@@ -521,7 +536,7 @@ def main():
     ap.add_argument("--no-overlap", action="store_true",
                     help="N > 1: all-reduce the gradient buckets after the step instead of during backward")
     ap.add_argument("--kernel", default=None,
-                    choices=["all", "gemm", "attn", "layernorm", "crossentropy", "softmax", "relu"],
+                    choices=["all", "gemm", "attn", "layernorm", "crossentropy", "softmax", "relu", "embed"],
                     help="run the isolated-kernel micro-benchmarks instead of the model step")
     ap.add_argument("--small", action="store_true", help="with --kernel: one small case, one launch (for ncu captures)")
     args = ap.parse_args()

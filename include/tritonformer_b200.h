@@ -152,6 +152,29 @@ int64_t tfb_colsum_partials(int64_t rows, int64_t cols);
 int tfb_colsum(const void* x, void* out, float* partials, int64_t n_partials,
                int64_t rows, int64_t cols, int64_t x_ld, int dtype, void* stream);
 
+/* ------------------------------------------------------------------- embeddings
+ * Replaces the two torch.nn.Embedding lookups and their sum at the head of
+ * Transformer.forward (transformer.py:259-272, 311-321) and their gradients.
+ *   out[b,t,:] = tok[ids[b,t],:] (+ pos[t,:] when pos is not NULL), summed in fp32.
+ * ids is a contiguous (batch, seq) int64 array; tok is (vocab, d), pos (>= seq, d), out
+ * (batch, seq, d), all contiguous.  A token id outside [0, vocab) gives a zero row and
+ * the sticky code 0x7100 in tfb_device_status().                               */
+int tfb_embedding_fwd(const int64_t* ids, const void* tok, const void* pos, void* out,
+                      int64_t batch, int64_t seq, int64_t d, int64_t vocab, int dtype,
+                      void* stream);
+/* Bytes of scratch tfb_embedding_bwd needs (two int32 tables over the vocabulary
+ * plus one fp32 row per position).                                             */
+int64_t tfb_embedding_bwd_scratch_bytes(int64_t batch, int64_t seq, int64_t d, int64_t vocab);
+/* ADDS the gradients to what dtok (vocab, d) and dpos (>= seq, d; may be NULL) hold:
+ *   dtok[v,:] += sum over positions holding v of dout[b,t,:],  dpos[t,:] += sum_b dout[b,t,:]
+ * with fp32 sums and one rounding per touched row; untouched rows are not written.
+ * Tokens held by several positions are summed with fp32 atomics, so the order of
+ * that sum (not its operands) may differ between runs.  scratch needs no
+ * initialisation and is 16-byte aligned.                                       */
+int tfb_embedding_bwd(const int64_t* ids, const void* dout, void* dtok, void* dpos,
+                      void* scratch, int64_t scratch_bytes, int64_t batch, int64_t seq,
+                      int64_t d, int64_t vocab, int dtype, void* stream);
+
 /* ------------------------------------------------------------------------ GEMM
  * Replaces mm / gemm / bmm + torch.sum (tritonformer/kernels/gemm.py:81-616,
  * tritonformer/linear.py:15-102).

@@ -37,6 +37,15 @@ def cross_entropy_rows(logits, labels):
     return torch.where(valid, loss, torch.zeros_like(loss))
 
 
+def embedding(input_ids, tok, pos=None):
+    """Token rows plus, with a learned position table, the row of each position.  Restates the head of
+    Transformer.forward (transformer.py:311-321): embed_tokens(x) + embed_positions(arange(T))."""
+    x = F.embedding(input_ids, tok)
+    if pos is not None:
+        x = x + F.embedding(torch.arange(input_ids.shape[1], device=input_ids.device), pos)[None]
+    return x
+
+
 def causal_mask(t, device=None):
     return torch.ones((t, t), dtype=torch.bool, device=device).tril()
 

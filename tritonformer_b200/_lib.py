@@ -39,6 +39,9 @@ _SIGNATURES = {
     "tfb_relu_bwd": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp]),
     "tfb_colsum_partials": (_i64, [_i64, _i64]),
     "tfb_colsum": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp]),
+    "tfb_embedding_fwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp]),
+    "tfb_embedding_bwd_scratch_bytes": (_i64, [_i64] * 4),
+    "tfb_embedding_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
     "tfb_gemm": (_i32, [_vp, _vp, _vp, _vp] + [_i64] * 8 + [_i32, _i32, _i32, _vp, _pi32]),
     "tfb_gemm_workspace_bytes": (_i64, []),
     "tfb_gemm_fused": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64] + [_i64] * 8 + [_i32, _i32, _vp, _i64, _vp, _pi32]),

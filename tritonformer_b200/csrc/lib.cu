@@ -28,6 +28,7 @@ int attn_tc05_status(int reset);
 int attn_bwd_tc05_status(int reset);
 int attn_fwd2_tc05_status(int reset);
 int attn_fwd1_tc05_status(int reset);
+int embedding_status(int reset);
 int attn_bwd_tc05_counters(unsigned long long* out);
 int gemm_pair_counters(int cta, unsigned long long* out);
 int attn_fwd2_tc05_counters(unsigned long long* out);
@@ -49,7 +50,8 @@ extern "C" int tfb_device_status(int reset) {
   const int d = attn_fwd2_tc05_status(reset);
   const int e = gemm_pair_tc05_status(reset);
   const int f = attn_fwd1_tc05_status(reset);
-  return a ? a : (b ? b : (c ? c : (d ? d : (e ? e : f))));
+  const int g = embedding_status(reset);
+  return a ? a : (b ? b : (c ? c : (d ? d : (e ? e : (f ? f : g)))));
 }
 
 extern "C" int tfb_debug_counters(unsigned long long* out16) {

@@ -22,6 +22,7 @@ import torch.nn as nn
 from . import fast_causal_attention, fast_causal_attention_with_bias
 from . import nn as tnn
 from .crossentropy import CrossEntropyLossFP32
+from .embedding import Embedding
 from .fused import LayerNormFork, LinearResidual, MLPResidual, QKVProjection
 
 # The layer runs on fused Functions (residual adds, ReLU mask and the q/k/v input gradients folded into
@@ -198,10 +199,9 @@ class Transformer(nn.Module):
     def forward(self, input_ids: torch.Tensor, labels: Optional[torch.Tensor]
                 ) -> Tuple[torch.Tensor, torch.Tensor]:
         batch, seq = input_ids.shape
-        hidden_states = self.embed_tokens(input_ids)
-        if self.embed_positions is not None:
-            positions = torch.arange(seq, device=hidden_states.device)
-            hidden_states = hidden_states + self.embed_positions(positions)[None]
+        hidden_states = Embedding.apply(
+            input_ids, self.embed_tokens.weight,
+            self.embed_positions.weight if self.embed_positions is not None else None)
         for layer in self.layer_list:
             hidden_states = layer(hidden_states, self.attn_bias)
         hidden_states = self.final_layernorm(hidden_states)
