@@ -63,10 +63,9 @@ __global__ void __launch_bounds__(256) embed_fwd_kernel(const int64_t* __restric
 }
 
 // table[v] = smallest position holding token v, table[vocab + v] = kTableFill + how many hold it
-// (both start as kTableFill); also clears the fp32 scratch rows.
+// (both start as kTableFill).
 __global__ void __launch_bounds__(256) embed_index_kernel(const int64_t* __restrict__ ids, int* __restrict__ table,
-                                                          float4* __restrict__ scratch, int64_t n, int64_t vocab,
-                                                          int64_t scratch_vecs) {
+                                                          int64_t n, int64_t vocab) {
   const int64_t stride = (int64_t)gridDim.x * 256;
   for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) {
     const int64_t id = ids[i];
@@ -77,8 +76,22 @@ __global__ void __launch_bounds__(256) embed_index_kernel(const int64_t* __restr
       atomicCAS(&g_embed_status, 0, kBadToken);
     }
   }
-  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < scratch_vecs; i += stride)
-    scratch[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+}
+
+// Clears the fp32 scratch row of every position that is the first holder of a token held several
+// times: the only rows the scatter kernel adds into.
+__global__ void __launch_bounds__(256) embed_clear_kernel(const int64_t* __restrict__ ids,
+                                                          const int* __restrict__ table, float* __restrict__ scratch,
+                                                          int64_t n, int d, int64_t vocab, int lanes) {
+  grid_dependency_wait();
+  allow_dependents();
+  const int sub = threadIdx.x / lanes, l = threadIdx.x % lanes, per = 256 / lanes;
+  for (int64_t row = (int64_t)blockIdx.x * per + sub; row < n; row += (int64_t)gridDim.x * per) {
+    const int64_t id = ids[row];
+    if (id < 0 || id >= vocab) continue;
+    if (held(table, vocab, id) < 2u || table[id] != (int)row) continue;
+    for (int c = l; c < d; c += lanes) scratch[row * d + c] = 0.f;
+  }
 }
 
 // One sub-group of `lanes` threads per time step t: reads the gradient rows of every sequence at
@@ -99,27 +112,48 @@ __global__ void __launch_bounds__(256) embed_bwd_scatter_kernel(const int64_t* _
       float psum[W];
 #pragma unroll
       for (int j = 0; j < W; ++j) psum[j] = 0.f;
-      for (int64_t b = 0; b < batch; ++b) {
-        const int64_t row = b * seq + t;
-        float g[W];
-        load_w<T, W>(dout + row * d + c * W, g);
+      // four sequences at a time, so that their loads are in flight together; rows that take the
+      // direct path within one group belong to different tokens (a token held twice goes through
+      // the scratch), so their read-modify-writes do not overlap
+      for (int64_t b0 = 0; b0 < batch; b0 += 4) {
+        float g[4][W], w[4][W];
+        int64_t id[4];
+        bool direct[4];
 #pragma unroll
-        for (int j = 0; j < W; ++j) psum[j] += g[j];
-        const int64_t id = ids[row];
-        if (id < 0 || id >= vocab) continue;
-        if (held(table, vocab, id) == 1u) {
-          float w[W];
-          load_w<T, W>(dtok + id * d + c * W, w);
+        for (int u = 0; u < 4; ++u) {
+          id[u] = -1;
+          direct[u] = false;
+          if (b0 + u < batch) {
+            const int64_t row = (b0 + u) * seq + t;
+            load_w<T, W>(dout + row * d + c * W, g[u]);
+            const int64_t v = ids[row];
+            if (v >= 0 && v < vocab) {
+              id[u] = v;
+              direct[u] = held(table, vocab, v) == 1u;
+            }
+          }
+        }
 #pragma unroll
-          for (int j = 0; j < W; ++j) w[j] += g[j];
-          store_w<T, W>(dtok + id * d + c * W, w);
-        } else {
-          float* dst = scratch + (int64_t)table[id] * d + c * W;
-          if constexpr (W == 8) {
-            atomicAdd(reinterpret_cast<float4*>(dst), make_float4(g[0], g[1], g[2], g[3]));
-            atomicAdd(reinterpret_cast<float4*>(dst) + 1, make_float4(g[4], g[5], g[6], g[7]));
-          } else {
-            atomicAdd(dst, g[0]);
+        for (int u = 0; u < 4; ++u)
+          if (direct[u]) load_w<T, W>(dtok + id[u] * d + c * W, w[u]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (b0 + u < batch) {
+#pragma unroll
+            for (int j = 0; j < W; ++j) psum[j] += g[u][j];
+          }
+          if (direct[u]) {
+#pragma unroll
+            for (int j = 0; j < W; ++j) w[u][j] += g[u][j];
+            store_w<T, W>(dtok + id[u] * d + c * W, w[u]);
+          } else if (id[u] >= 0) {
+            float* dst = scratch + (int64_t)table[id[u]] * d + c * W;
+            if constexpr (W == 8) {
+              atomicAdd(reinterpret_cast<float4*>(dst), make_float4(g[u][0], g[u][1], g[u][2], g[u][3]));
+              atomicAdd(reinterpret_cast<float4*>(dst) + 1, make_float4(g[u][4], g[u][5], g[u][6], g[u][7]));
+            } else {
+              atomicAdd(dst, g[u][0]);
+            }
           }
         }
       }
@@ -227,14 +261,16 @@ extern "C" int tfb_embedding_bwd(const int64_t* ids, const void* dout, void* dto
   const int64_t table_bytes = ceil_div(2 * vocab * (int64_t)sizeof(int), 16) * 16;
   float* sums = (float*)((char*)scratch + table_bytes);
   TFB_REQUIRE(cudaMemsetAsync(table, 0x7f, (size_t)table_bytes, st) == cudaSuccess, "embedding_bwd: table fill failed");
-  const int64_t scratch_vecs = n * d / 4;  // n * d floats; d % 4 != 0 leaves a tail cleared below
-  embed_index_kernel<<<grid_for(scratch_vecs > n ? scratch_vecs : n, 256), 256, 0, st>>>(
-      ids, table, (float4*)sums, n, vocab, scratch_vecs);
+  embed_index_kernel<<<grid_for(n, 256), 256, 0, st>>>(ids, table, n, vocab);
   int rc = launched("embedding_bwd index");
   if (rc) return rc;
-  if (n * d % 4 != 0)
-    TFB_REQUIRE(cudaMemsetAsync(sums + scratch_vecs * 4, 0, (size_t)(n * d % 4) * sizeof(float), st) == cudaSuccess,
-                "embedding_bwd: scratch clear failed");
+  {
+    const int lanes = lanes_for(d);
+    launch_overlapped(embed_clear_kernel, dim3(grid_for(n, 256 / lanes)), dim3(256), 0, st, ids, (const int*)table, sums,
+                      n, (int)d, vocab, lanes);
+    rc = launched("embedding_bwd clear");
+    if (rc) return rc;
+  }
   const bool vec = d % 8 == 0 && aligned16(dout) && aligned16(dtok) && (dpos == nullptr || aligned16(dpos));
   TFB_DISPATCH_16(dtype, T, {
     if (vec) {
