@@ -25,6 +25,10 @@ def _as_rows(x: torch.Tensor) -> torch.Tensor:
 # When set to a list, every GEMM call appends a description of itself (shape, operand strides,
 # epilogue options): the benchmark replays that list to time the kernel family on its own.
 PROFILE = None
+# When set to a list, every GEMM call is bracketed by two CUDA events on its stream and appends
+# (start, end, flops): the benchmark sums the elapsed times of one eager step to time the kernels on
+# the step's own operands.
+TIMING = None
 
 
 def replay(calls, device):
@@ -84,12 +88,18 @@ def gemm(a, a_sm, a_sk, b, b_sk, b_sn, m, n, k, bias=None, relu=False, out=None,
     path = ctypes.c_int(0)
     stream = _lib.stream_ptr(a.device)
     ws = _gemm_workspace(a.device, stream)
+    if TIMING is not None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
     _lib.check(_lib.lib.tfb_gemm_fused(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), bias.data_ptr() if bias is not None else None,
         addend.data_ptr() if addend is not None else None, addend.stride(0) if addend is not None else 0,
         mask.data_ptr() if mask is not None else None, mask.stride(0) if mask is not None else 0,
         m, n, k, a_sm, a_sk, b_sk, b_sn, out.stride(0), 1 if relu else 0, _lib.dtype_code(a.dtype),
         ws.data_ptr(), ws.numel(), stream, ctypes.byref(path)))
+    if TIMING is not None:
+        e1.record()
+        TIMING.append((e0, e1, 2.0 * m * n * k))
     if PROFILE is not None:
         PROFILE.append({"m": m, "n": n, "k": k, "a": (a_sm, a_sk), "b": (b_sk, b_sn), "bias": bias is not None,
                         "relu": bool(relu), "addend": addend is not None, "accumulate": addend is out,
