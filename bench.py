@@ -215,7 +215,12 @@ def run_b200_arm(args):
 
     # N > 1: each gradient bucket is all-reduced from a hook as soon as backward has produced it, on a
     # side stream, so the collectives overlap the rest of backward (and are captured with the step)
-    reducer = OverlappedReducer(buckets, list(model.layer_list)) if (world > 1 and not args.no_overlap) else None
+    # TFB_BENCH_FREE_SMS=k: while collectives are in flight the persistent GEMM grids are sized for k SMs fewer
+    # (measured at 2 GPUs: 28.8 ms per step with k = 16 or 20 against 28.9 with 0, i.e. no difference; off)
+    free_sms = int(os.environ.get("TFB_BENCH_FREE_SMS", "0"))
+    reducer = OverlappedReducer(buckets, list(model.layer_list),
+                                on_collectives=(lambda on: L.lib.tfb_debug_set(6, free_sms if on else 0)) if free_sms else None) \
+        if (world > 1 and not args.no_overlap) else None
 
     def step(ids):
         with torch.autocast("cuda", dtype=dtype):

@@ -55,7 +55,9 @@ int tfb_device_status(int reset);
  *   key 4: GEMM: bit 0 whole tiles only (no sharing of a tile's contraction between SMs), bit 5 (32)
  *          no CTA-pair kernel, bit 6 (64) per-CTA timeline counters of the CTA-pair kernel.
  *   key 5: which counters tfb_debug_counters returns: -1 attention backward, -2 / -3 attention forward
- *          (head_dim 64, two-tile / one-tile kernel), n >= 0 the CTA-pair GEMM timeline of CTA n.                              */
+ *          (head_dim 64, two-tile / one-tile kernel), n >= 0 the CTA-pair GEMM timeline of CTA n.
+ *   key 6: how many SMs the persistent GEMM grids leave free (for a collective that runs beside
+ *          them on another stream); 0 by default.                                */
 void tfb_debug_set(int key, int value);
 /* Timing counters of the attention backward kernel (16 cycle sums, filled while tfb_debug_set(2, 2)
  * is in effect); copies and clears them.  Synchronises the device.                        */

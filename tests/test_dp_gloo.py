@@ -33,11 +33,14 @@ def _worker(rank, world, port, mode, out):
         x = shard_batch(data, rank, world)
         reducer = None
         if mode == "overlap":  # buckets are reduced from hooks while backward is still running
-            reducer = OverlappedReducer(buckets, [model[0], model[2]])
+            calls = []  # told when the first collective of the step is enqueued and when the step is joined
+            reducer = OverlappedReducer(buckets, [model[0], model[2]], on_collectives=calls.append)
             assert reducer.ready_at[0] >= 1 and min(reducer.ready_at) == 0
             model(x).square().mean().backward()
             assert any(reducer.launched), "no bucket was reduced during backward"
+            assert calls == [True]
             reducer.finish()
+            assert calls == [True, False]
             buckets.check_views()
             flat = torch.cat([p.grad.reshape(-1) for p in model.parameters()])
             out.put((rank, "ok", flat))

@@ -73,6 +73,8 @@ if os.environ.get("TFB_FORCE_GENERIC_ATTN") == "1":
     lib.tfb_debug_set(1, 1)
 if os.environ.get("TFB_SERIALISED_LAUNCHES") == "1":  # no programmatic dependent launch
     lib.tfb_debug_set(3, 1)
+if os.environ.get("TFB_GEMM_FREE_SMS"):  # SMs the GEMM grids leave to a collective running beside them
+    lib.tfb_debug_set(6, int(os.environ["TFB_GEMM_FREE_SMS"]))
 if os.environ.get("TFB_GEMM_SWITCHES"):  # bit 0: whole tiles only, bit 5 (32): no CTA-pair kernel
     lib.tfb_debug_set(4, int(os.environ["TFB_GEMM_SWITCHES"]))
 

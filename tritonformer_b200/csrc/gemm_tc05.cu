@@ -25,6 +25,7 @@
 namespace tfb {
 
 extern std::atomic<int> g_gemm_debug;
+extern std::atomic<int> g_gemm_free_sms;
 int64_t gemm_pair_tiles(int64_t M, int64_t N);
 int gemm_pair_tc05(const void* a, const void* b, void* c, const void* bias, const void* addend, int64_t ld_addend,
                    const void* mask, int64_t ld_mask, int64_t M, int64_t N, int64_t K, int64_t a_sm, int64_t a_sk,
@@ -474,7 +475,10 @@ int gemm_tc05(const void* a, const void* b, void* c, const void* bias, const voi
   const bool a_mn = (a_sk != 1);  // M contiguous
   const bool b_mn = (b_sk != 1);  // N contiguous
   const int64_t tm = ceil_div(M, TB_M);
-  const int sms = sm_count();
+  // SMs left to a collective that runs beside the GEMMs: a persistent grid sized for every SM would have its
+  // last CTAs wait for one the collective holds, and the whole product would take two rounds
+  int sms = sm_count() - g_gemm_free_sms.load();
+  sms = sms < 2 ? 2 : sms & ~1;
   const int64_t kblocks = ceil_div(K, TB_K);
   const int dbg = g_gemm_debug.load();
   const bool can_split = !(dbg & 1) && workspace != nullptr && aligned16(workspace) &&

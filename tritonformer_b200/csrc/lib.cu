@@ -10,6 +10,7 @@ std::atomic<int> g_force_fallback_attn{0};
 std::atomic<int> g_attn_debug{0};
 std::atomic<int> g_plain_launch{0};
 std::atomic<int> g_gemm_debug{0};
+std::atomic<int> g_gemm_free_sms{0};
 
 int gemm_generic(const void* a, const void* b, void* c, const void* bias, const void* addend, int64_t ld_addend,
                  const void* mask, int64_t ld_mask, int64_t M, int64_t N, int64_t K, int64_t a_sm, int64_t a_sk,
@@ -67,6 +68,7 @@ extern "C" void tfb_debug_set(int key, int value) {
   if (key == 2) g_attn_debug.store(value);
   if (key == 3) g_plain_launch.store(value);
   if (key == 4) g_gemm_debug.store(value);
+  if (key == 6) g_gemm_free_sms.store(value < 0 ? 0 : value);
   if (key == 5) g_counter_select.store(value);
 }
 

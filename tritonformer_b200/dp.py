@@ -107,8 +107,12 @@ class OverlappedReducer:
     captured in a CUDA graph together with the step.
     """
 
-    def __init__(self, buckets: GradBuckets, stages, group=None):
+    def __init__(self, buckets: GradBuckets, stages, group=None, on_collectives=None):
+        """`on_collectives(active)`: called with True when the first collective of a step is enqueued and with
+        False from finish(), on the thread that enqueues the kernels; the benchmark uses it to size the GEMM
+        grids for the SMs the collectives leave."""
         self.buckets, self.group = buckets, group
+        self.on_collectives = on_collectives
         stage_of = {}
         for i, m in enumerate(stages):
             for p in m.parameters():
@@ -146,6 +150,8 @@ class OverlappedReducer:
 
     def _reduce(self, k):
         b = self.buckets.buckets[k]
+        if self.on_collectives is not None and not any(self.launched):
+            self.on_collectives(True)
         self.launched[k] = True
         if self.side is not None:
             self.side.wait_stream(torch.cuda.current_stream())
@@ -169,6 +175,8 @@ class OverlappedReducer:
                     self._reduce(k)
             if self.side is not None:
                 torch.cuda.current_stream().wait_stream(self.side)
+        if self.on_collectives is not None and any(self.launched):
+            self.on_collectives(False)
         self.launched = [False] * len(self.launched)
 
     def remove(self):
