@@ -13,6 +13,7 @@ namespace tfb {
 static __device__ int g_embed_status = 0;
 constexpr int kBadToken = 0x7100;       // a token id outside [0, vocab)
 constexpr int kTableFill = 0x7f7f7f7f;  // what a byte fill of 0x7f leaves in every int32
+constexpr int kTestLanes = 32;          // threads per row in the kernels that mostly test and skip rows
 
 // How many positions hold token `id` (the count half of the table starts at kTableFill).
 __device__ __forceinline__ unsigned held(const int* table, int64_t vocab, int64_t id) {
@@ -265,7 +266,8 @@ extern "C" int tfb_embedding_bwd(const int64_t* ids, const void* dout, void* dto
   int rc = launched("embedding_bwd index");
   if (rc) return rc;
   {
-    const int lanes = lanes_for(d);
+    // most rows are only tested (few tokens are held twice): a warp per row keeps eight tests in flight per CTA
+    const int lanes = kTestLanes;
     launch_overlapped(embed_clear_kernel, dim3(grid_for(n, 256 / lanes)), dim3(256), 0, st, ids, (const int*)table, sums,
                       n, (int)d, vocab, lanes);
     rc = launched("embedding_bwd clear");
@@ -279,16 +281,16 @@ extern "C" int tfb_embedding_bwd(const int64_t* ids, const void* dout, void* dto
                         (const T*)dout, (T*)dtok, (T*)dpos, (const int*)table, sums, batch, seq, (int)d, vocab, lanes);
       rc = launched("embedding_bwd scatter");
       if (rc) return rc;
-      launch_overlapped(embed_bwd_fold_kernel<T, 8>, dim3(grid_for(n, 256 / lanes)), dim3(256), 0, st, ids, (T*)dtok,
-                        (const int*)table, (const float*)sums, n, (int)d, vocab, lanes);
+      launch_overlapped(embed_bwd_fold_kernel<T, 8>, dim3(grid_for(n, 256 / kTestLanes)), dim3(256), 0, st, ids,
+                        (T*)dtok, (const int*)table, (const float*)sums, n, (int)d, vocab, kTestLanes);
     } else {
       const int lanes = lanes_for(d);
       launch_overlapped(embed_bwd_scatter_kernel<T, 1>, dim3(grid_for(seq, 256 / lanes)), dim3(256), 0, st, ids,
                         (const T*)dout, (T*)dtok, (T*)dpos, (const int*)table, sums, batch, seq, (int)d, vocab, lanes);
       rc = launched("embedding_bwd scatter");
       if (rc) return rc;
-      launch_overlapped(embed_bwd_fold_kernel<T, 1>, dim3(grid_for(n, 256 / lanes)), dim3(256), 0, st, ids, (T*)dtok,
-                        (const int*)table, (const float*)sums, n, (int)d, vocab, lanes);
+      launch_overlapped(embed_bwd_fold_kernel<T, 1>, dim3(grid_for(n, 256 / kTestLanes)), dim3(256), 0, st, ids,
+                        (T*)dtok, (const int*)table, (const float*)sums, n, (int)d, vocab, kTestLanes);
     }
   })
   return launched("embedding_bwd fold");
