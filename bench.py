@@ -176,7 +176,7 @@ def build_model(cfg, dtype, device, seed=1234):
         model = model.to(torch.bfloat16)
         if table is not None:
             model.attn_bias = table  # the ALiBi table keeps the reference's fp16 rounding
-    return model
+    return model.fuse_projection_weights()
 
 
 def run_b200_arm(args):

@@ -21,7 +21,7 @@ def _free_port():
 def _worker(rank, world, port, mode, out):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     from datetime import timedelta
-    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=timedelta(seconds=8))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=timedelta(seconds=20))
     try:
         torch.manual_seed(rank)  # replicas start different on purpose
         model = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.ReLU(), torch.nn.Linear(32, 4))

@@ -259,6 +259,54 @@ def test_layer_runs_twelve_products():
     assert sum(1 for r in recs if r["k"] == 3 * 256) == cfg.num_hidden_layers          # input gradient
 
 
+def test_projection_weights_as_column_blocks_of_one_buffer():
+    """fuse_projection_weights() keeps names, values and results (bit for bit: the same product runs on the same
+    numbers, without the concatenation), the parameters stay live views of the shared buffer, and a state dict
+    saved before loads into the re-homed model."""
+    from tritonformer_b200.transformer import Transformer
+    cfg = _cfg(vocab_size=1024, hidden_size=256, max_position_embeddings=256, num_attention_heads=4, head_dim=64,
+               ffn_dim=1024, num_hidden_layers=2, use_linear_bias=False, attn_bias=False)
+    torch.manual_seed(5)
+    model = Transformer(cfg, device="cuda")
+    with torch.no_grad():
+        model.logits_out.weight.normal_(0.0, 0.02)
+    ids = torch.randint(0, 1024, (2, 256), device="cuda")
+
+    def step(m):
+        m.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.float16):
+            logits, loss = m(ids, ids)
+        (loss * 256.0).backward()
+        return logits.detach().clone(), {n: p.grad.detach().clone() for n, p in m.named_parameters()}
+
+    state = {k: v.clone() for k, v in model.state_dict().items()}
+    logits_a, grads_a = step(model)
+    names = [n for n, _ in model.named_parameters()]
+    model.fuse_projection_weights()
+    assert [n for n, _ in model.named_parameters()] == names
+    att = model.layer_list[0].attention
+    assert att.k_proj.weight.data_ptr() == att.q_proj.weight.data_ptr() + 256 * 2
+    assert att.q_proj.weight.stride() == (3 * 256, 1)
+    for k, v in model.state_dict().items():
+        assert torch.equal(v, state[k]), k
+    logits_b, grads_b = step(model)
+    assert torch.equal(logits_a, logits_b)
+    for n in names:  # equal up to the order of the fp32 dQ accumulation, which differs from run to run
+        assert norm_rel(grads_a[n].float(), grads_b[n].float()) < 1e-3, n
+    # an in-place update of one parameter is what the fused product sees
+    with torch.no_grad():
+        att.v_proj.weight.mul_(0.5)
+    state["layer_list.0.attention.v_proj.weight"] = state["layer_list.0.attention.v_proj.weight"] * 0.5
+    logits_c, _ = step(model)
+    fresh = Transformer(cfg, device="cuda")
+    fresh.load_state_dict(state)
+    logits_d, _ = step(fresh)
+    assert torch.equal(logits_c, logits_d)
+    # and a state dict loads into the re-homed parameters in place
+    model.load_state_dict({k: v.clone() for k, v in fresh.state_dict().items()})
+    assert att.k_proj.weight.data_ptr() == att.q_proj.weight.data_ptr() + 256 * 2
+
+
 def test_small_model_fp16_bias_alibi_hd32():
     cfg = _cfg(vocab_size=1000, hidden_size=192, max_position_embeddings=256, num_attention_heads=6, head_dim=32,
                ffn_dim=768, num_hidden_layers=2, use_linear_bias=True, attn_bias=True)

@@ -189,7 +189,12 @@ def broadcast_parameters(module: torch.nn.Module, src: int = 0, group=None):
     if not dist.is_initialized() or dist.get_world_size(group) == 1:
         return
     for t in list(module.parameters()) + list(module.buffers()):
-        dist.broadcast(t.data, src=src, group=group)
+        if t.data.is_contiguous():
+            dist.broadcast(t.data, src=src, group=group)
+        else:  # e.g. a projection weight that is a column block of a shared buffer
+            tmp = t.data.contiguous()
+            dist.broadcast(tmp, src=src, group=group)
+            t.data.copy_(tmp)
 
 
 def shard_batch(global_ids: torch.Tensor, rank: int, world: int) -> torch.Tensor:

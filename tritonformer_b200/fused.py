@@ -101,7 +101,12 @@ class QKVProjection(Function):
                     L.linear_forward(x, wv, None, False))
         ctx.fused = True
         d = wq.shape[1]
-        w = torch.cat((wq, wk, wv), dim=1)  # (in, 3 d)
+        if _adjacent_columns((wq, wk, wv), 3 * d):
+            # the three weights already are the column blocks of one (in, 3 d) matrix
+            # (Transformer.fuse_projection_weights): no copy
+            w = torch.as_strided(wq, (wq.shape[0], 3 * d), (3 * d, 1))
+        else:
+            w = torch.cat((wq, wk, wv), dim=1)  # (in, 3 d)
         y = L.linear_forward(x, w, None, False)
         ctx.save_for_backward(x, w, wq, wk, wv)
         return y[..., :d], y[..., d:2 * d], y[..., 2 * d:]

@@ -196,6 +196,23 @@ class Transformer(nn.Module):
         return [(layer.attention.q_proj.weight, layer.attention.k_proj.weight, layer.attention.v_proj.weight)
                 for layer in self.layer_list]
 
+    def fuse_projection_weights(self):
+        """Re-homes the q, k and v projection weights of every layer as the column blocks of one (d, 3 d) buffer.
+        The three parameters, their names and values stay; the fused projection then reads that buffer directly
+        instead of concatenating the weights every step.  Anything that replaces the parameters' storage
+        afterwards (`.to()`, `.half()`) undoes this, and the projection goes back to concatenating."""
+        with torch.no_grad():
+            for layer in self.layer_list:
+                att = layer.attention
+                ws = (att.q_proj.weight, att.k_proj.weight, att.v_proj.weight)
+                if not (ws[0].shape == ws[1].shape == ws[2].shape and ws[0].dtype == ws[1].dtype == ws[2].dtype):
+                    continue
+                rows, d = ws[0].shape
+                buf = torch.cat([w.detach() for w in ws], dim=1)
+                for i, lin in enumerate((att.q_proj, att.k_proj, att.v_proj)):
+                    lin.weight = nn.Parameter(buf[:, i * d:(i + 1) * d], requires_grad=lin.weight.requires_grad)
+        return self
+
     def forward(self, input_ids: torch.Tensor, labels: Optional[torch.Tensor]
                 ) -> Tuple[torch.Tensor, torch.Tensor]:
         batch, seq = input_ids.shape
