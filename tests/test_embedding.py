@@ -75,3 +75,14 @@ def test_embedding_token_out_of_range_is_reported():
     assert _lib.lib.tfb_device_status(1) == 0x7100
     assert _lib.lib.tfb_device_status(0) == 0
     assert out[0, 0].eq(1).all() and out[0, 1].eq(0).all() and out[0, 3].eq(0).all()
+
+
+def test_embedding_empty_batch():
+    """No positions: nothing is launched, shapes and gradients are still well-formed."""
+    from tritonformer_b200.embedding import Embedding
+    tok = torch.randn((10, 16), device="cuda").half().requires_grad_(True)
+    pos = torch.randn((4, 16), device="cuda").half().requires_grad_(True)
+    out = Embedding.apply(torch.zeros((0, 4), device="cuda", dtype=torch.int64), tok, pos)
+    assert out.shape == (0, 4, 16)
+    out.sum().backward()
+    assert tok.grad.eq(0).all() and pos.grad.eq(0).all()

@@ -405,23 +405,24 @@ __global__ void __launch_bounds__(256, 2) ln_bwd_split_kernel(
   for (int i = threadIdx.x; i < 2 * d; i += blockDim.x) pa[i] = fold[i];
 }
 
+// 32 columns per CTA; the rows are spread over the CTA's warps (32 for many partial rows, 8 otherwise), so
+// that each thread has only a few dependent-free loads to wait for.
 template <typename T>
-__global__ void __launch_bounds__(256) finalize_partials_kernel(
+__global__ void __launch_bounds__(1024) finalize_partials_kernel(
     const float* __restrict__ partials, int64_t n, int ncols, int split, T* __restrict__ out0,
     T* __restrict__ out1, int accumulate) {
   grid_dependency_wait();
   allow_dependents();
-  __shared__ float sm[8][33];
-  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  __shared__ float sm[32][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5, nry = blockDim.x >> 5;
   const int c = blockIdx.x * 32 + cx;
   float s = 0.f;
   if (c < ncols)
-    for (int64_t r = ry; r < n; r += 8) s += partials[r * ncols + c];
+    for (int64_t r = ry; r < n; r += nry) s += partials[r * ncols + c];
   sm[ry][cx] = s;
   __syncthreads();
   if (ry == 0 && c < ncols) {
-#pragma unroll
-    for (int i = 1; i < 8; ++i) s += sm[i][cx];
+    for (int i = 1; i < nry; ++i) s += sm[i][cx];
     T* dst = c < split ? out0 + c : out1 + (c - split);
     if (accumulate) s += Num<T>::to_f(*dst);  // the sums are added to what the output already holds
     *dst = Num<T>::from_f(s);
@@ -431,8 +432,8 @@ __global__ void __launch_bounds__(256) finalize_partials_kernel(
 template <typename T>
 int finalize_partials(const float* partials, int64_t n, int ncols, int split, void* out0,
                       void* out1, cudaStream_t st, int accumulate) {
-  launch_overlapped(finalize_partials_kernel<T>, dim3((unsigned)ceil_div(ncols, 32)), dim3(256), 0, st, partials, n,
-                    ncols, split, (T*)out0, (T*)out1, accumulate);
+  launch_overlapped(finalize_partials_kernel<T>, dim3((unsigned)ceil_div(ncols, 32)), dim3(n > 64 ? 1024 : 256), 0, st,
+                    partials, n, ncols, split, (T*)out0, (T*)out1, accumulate);
   return launched("finalize_partials");
 }
 template int finalize_partials<__half>(const float*, int64_t, int, int, void*, void*, cudaStream_t, int);
