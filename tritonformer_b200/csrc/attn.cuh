@@ -23,7 +23,8 @@ struct AttnArgs {
 
 
 // delta[b,h,i] = sum_d dO[i,d] * O[i,d] (fp32), shared by both backward paths
-int attn_delta(const AttnArgs& a, int hd, int dtype, cudaStream_t st);
+// `clear`: optional fp32 (B,H,T,hd) buffer that the same pass sets to zero (the dQ accumulator).
+int attn_delta(const AttnArgs& a, int hd, int dtype, cudaStream_t st, float* clear = nullptr);
 int attn_generic_fwd(const AttnArgs& a, int hd, int dtype, cudaStream_t st);
 int attn_generic_bwd(const AttnArgs& a, int hd, int dtype, cudaStream_t st);
 

@@ -549,11 +549,9 @@ template <typename T, int HD>
 static int bwd_tc05_launch(const AttnArgs& a, int dtype, cudaStream_t st) {
   using Cfg = FbCfg<HD>;
   int rc;
-  // clear the accumulator first, so that the main kernel directly follows a kernel in the stream
-  const size_t acc_bytes = (size_t)a.B * a.H * a.T * HD * sizeof(float);
-  cudaError_t e = cudaMemsetAsync(a.dq_acc, 0, acc_bytes, st);
-  if (e != cudaSuccess) return fail(TFB_ERR_LAUNCH, "attention_bwd(tcgen05): memset: %s", cudaGetErrorString(e));
-  if ((rc = attn_delta(a, HD, dtype, st))) return rc;
+  // the delta pass also clears the fp32 dQ accumulator (contiguous (B,H,T,HD), 16-byte aligned: checked by the
+  // caller), so no fill sits between the kernels in the stream
+  if ((rc = attn_delta(a, HD, dtype, st, a.dq_acc))) return rc;
   CUtensorMap tq, tk, tv, tdo, tdq;
   {
     // fp32 dQ accumulator as a (HD, B*H*T) matrix, boxes of 32 floats x 32 rows

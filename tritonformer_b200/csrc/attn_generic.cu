@@ -221,9 +221,10 @@ __global__ void __launch_bounds__(AT_THREADS) attn_fwd_kernel(const AttnArgs a) 
   }
 }
 
-// delta[b,h,i] = sum_d dO[i,d] * O[i,d]; hd/8 lanes per row, one 16-byte load of each operand per lane
+// delta[b,h,i] = sum_d dO[i,d] * O[i,d]; hd/8 lanes per row, one 16-byte load of each operand per lane.
+// `clear` (may be null): contiguous fp32 (B,H,T,HD) buffer; each lane zeroes the eight floats under its chunk.
 template <typename T, int HD>
-__global__ void __launch_bounds__(256) attn_delta_kernel(const AttnArgs a) {
+__global__ void __launch_bounds__(256) attn_delta_kernel(const AttnArgs a, float* __restrict__ clear) {
   grid_dependency_wait();
   allow_dependents();
   constexpr int LPR = HD / 8;          // lanes per row
@@ -244,6 +245,11 @@ __global__ void __launch_bounds__(256) attn_delta_kernel(const AttnArgs a) {
     unpack8<T>(ld_stream16(gp), y);
 #pragma unroll
     for (int j = 0; j < 8; ++j) s += x[j] * y[j];
+    if (clear) {
+      float4* z = reinterpret_cast<float4*>(clear + row * HD + sub * 8);
+      z[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+      z[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
   }
 #pragma unroll
   for (int o = LPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
@@ -536,12 +542,12 @@ static int bwd_launch(const AttnArgs& a, cudaStream_t st) {
   return TFB_OK;
 }
 
-int attn_delta(const AttnArgs& a, int hd, int dtype, cudaStream_t st) {
+int attn_delta(const AttnArgs& a, int hd, int dtype, cudaStream_t st, float* clear) {
   const int64_t rows = (int64_t)a.B * a.H * a.T;
   TFB_DISPATCH_16(dtype, T, {
-    if (hd == 32) launch_overlapped(attn_delta_kernel<T, 32>, dim3((unsigned)ceil_div(rows, 8 * 8)), dim3(256), 0, st, a);
-    else if (hd == 64) launch_overlapped(attn_delta_kernel<T, 64>, dim3((unsigned)ceil_div(rows, 8 * 4)), dim3(256), 0, st, a);
-    else launch_overlapped(attn_delta_kernel<T, 128>, dim3((unsigned)ceil_div(rows, 8 * 2)), dim3(256), 0, st, a);
+    if (hd == 32) launch_overlapped(attn_delta_kernel<T, 32>, dim3((unsigned)ceil_div(rows, 8 * 8)), dim3(256), 0, st, a, clear);
+    else if (hd == 64) launch_overlapped(attn_delta_kernel<T, 64>, dim3((unsigned)ceil_div(rows, 8 * 4)), dim3(256), 0, st, a, clear);
+    else launch_overlapped(attn_delta_kernel<T, 128>, dim3((unsigned)ceil_div(rows, 8 * 2)), dim3(256), 0, st, a, clear);
   })
   return launched("attention_delta");
 }
