@@ -50,3 +50,9 @@ def test_argument_checks_without_device():
     assert L.lib.tfb_layernorm_bwd_partials(8192, 1024) > 0
     assert L.lib.tfb_colsum_partials(8192, 4096) > 0
     assert L.lib.tfb_attention_bwd_scratch_bytes(1, 2, 64, 64) == 2 * 64 * 4 + 2 * 64 * 64 * 4  # 512 is 256-aligned
+    # embeddings: shape, position count and scratch are checked before anything is launched
+    assert L.lib.tfb_embedding_fwd(None, None, None, None, 2, 8, 0, 100, 0, None) == -1  # d = 0
+    assert L.lib.tfb_embedding_fwd(None, None, None, None, 0, 8, 64, 100, 0, None) == 0  # no positions: nothing to do
+    assert L.lib.tfb_embedding_bwd_scratch_bytes(2, 8, 64, 100) == 2 * 100 * 4 + 2 * 8 * 64 * 4
+    rc = L.lib.tfb_embedding_bwd(None, None, None, None, None, 0, 2, 8, 64, 100, 0, None)
+    assert rc == -1 and b"scratch" in L.lib.tfb_last_error()
