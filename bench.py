@@ -204,7 +204,6 @@ def run_b200_arm(args):
     broadcast_parameters(model)
     n_params = sum(p.numel() for p in model.parameters())
     buckets = GradBuckets(model.parameters(), column_blocks=model.projection_weight_groups())
-    tlinear.ACCUMULATE_INTO_GRAD = True  # weight-gradient GEMMs add into the bucket views themselves
     loss_scale = 4096.0 if dtype is torch.float16 else 1.0
 
     gen = torch.Generator().manual_seed(1234 + rank)
@@ -222,10 +221,20 @@ def run_b200_arm(args):
                                 on_collectives=(lambda on: L.lib.tfb_debug_set(6, free_sms if on else 0)) if free_sms else None) \
         if (world > 1 and not args.no_overlap) else None
 
+    zero_stream = torch.cuda.Stream()
+
     def step(ids):
-        with torch.autocast("cuda", dtype=dtype):
-            _, loss = model(ids, ids)
-        (loss * loss_scale).backward()
+        # the gradient buckets are cleared on a side stream while the forward pass runs (nothing reads them
+        # before backward), then the weight-gradient GEMMs add into the bucket views themselves
+        main = torch.cuda.current_stream()
+        zero_stream.wait_stream(main)
+        with torch.cuda.stream(zero_stream):
+            buckets.zero()
+        with buckets.accumulate():
+            with torch.autocast("cuda", dtype=dtype):
+                _, loss = model(ids, ids)
+            main.wait_stream(zero_stream)
+            (loss * loss_scale).backward()
         if reducer is not None:
             reducer.finish()
         return loss.detach()

@@ -41,28 +41,21 @@ int tfb_version(void);
 const char* tfb_last_error(void);
 /* Number of kernels this library has launched in the calling process. */
 int64_t tfb_launch_count(void);
-/* Device-side status of the tcgen05 kernels: 0, or the code of the first bounded wait that
- * expired (the kernels then return without doing work until the status is cleared).
- * Synchronises the device; meant for tests and post-mortems.  reset != 0 clears it.      */
+/* Device-side status word of the library on the calling thread's CURRENT device (one word per GPU,
+ * shared by every kernel of the library): 0, or the code of the first bounded wait that expired
+ * (0x2xxx attention backward, 0x5xxx attention forward, 0x1xxx / 0x3xxx GEMM, 0x7e00 the test probe)
+ * or 0x7100 for a token id outside the embedding table.  While it is non-zero the tcgen05 kernels
+ * (GEMM, attention) return at once without writing their outputs; the other kernels still run.
+ * Synchronises the device; call it where the host synchronises anyway (the loss read-back).
+ * reset != 0 clears the word; the caller must then also zero its GEMM workspaces, whose arrival
+ * counters an abandoned split product can leave non-zero.                                     */
 int tfb_device_status(int reset);
-/* Test and tuning switches.
- *   key 0: value 1 sends every GEMM to the generic-stride kernel.
- *   key 1: value 1 sends every attention call to the mma.sync kernels.
- *   key 2: attention: bit 0 skips the dQ accumulation, bit 1 turns the cycle counters on, bit 4 (16)
- *          selects the two-query-tiles-per-CTA forward kernel for head_dim 64.
- *   key 3: value 1 launches every kernel fully serialised (no programmatic dependent launch: a
- *          kernel's set-up no longer overlaps its predecessor's tail).
- *   key 4: GEMM: bit 0 whole tiles only (no sharing of a tile's contraction between SMs), bit 5 (32)
- *          no CTA-pair kernel, bit 6 (64) per-CTA timeline counters of the CTA-pair kernel.
- *   key 5: which counters tfb_debug_counters returns: -1 attention backward, -2 / -3 attention forward
- *          (head_dim 64, two-tile / one-tile kernel), n >= 0 the CTA-pair GEMM timeline of CTA n.
- *   key 6: how many SMs the persistent GEMM grids leave free (for a collective that runs beside
- *          them on another stream); 0 by default.                                */
-void tfb_debug_set(int key, int value);
-/* Timing counters of the attention backward kernel (16 cycle sums, filled while tfb_debug_set(2, 2)
- * is in effect); copies and clears them.  Synchronises the device.                        */
-int tfb_debug_counters(unsigned long long* out16);
 
+/* Which device an entry point works on: the calling thread's current device.  It must be the device
+ * that owns the stream and every buffer of the call (a launch on another device's stream fails with
+ * TFB_ERR_LAUNCH); per-device set-up (shared-memory limits, the fixed scratch of
+ * tfb_layernorm_bwd_static, the status word) is keyed by it.  Entry points are re-entrant; forward
+ * and backward may come from different host threads as long as each has that device current.      */
 /* ------------------------------------------------------------------ LayerNorm
  * Replaces layernorm_fwd + layernorm_fwd_kernel (tritonformer/kernels/layernorm.py:9-87).
  * y = alpha * (x - mean) * rstd + beta over the last dim; additionally stores the
@@ -108,9 +101,11 @@ int tfb_layernorm_bwd_acc(const void* dy, const void* x, const void* alpha,
  * fp32 partial sums live in a fixed array inside the library image (about 9.7 MB, held by every
  * GPU that loads the library) and the call allocates nothing.  Limit: d <= 4096; wider rows are
  * rejected with TFB_ERR_UNSUPPORTED.  The first call on a device looks up the array's device
- * address (with that device current); make that first call outside any stream capture.  All
- * calls share the one array: two calls whose kernels overlap on the GPU (different streams)
- * race on it, so keep them stream-ordered.                                                  */
+ * address (with that device current); make that first call outside any stream capture.  The
+ * address is remembered per device for the life of the process: after cudaDeviceReset() it is
+ * stale and the entry must not be used again in that process.  All calls share the one array:
+ * two calls whose kernels overlap on the GPU (different streams) race on it, so keep them
+ * stream-ordered.                                                                           */
 int tfb_layernorm_bwd_static(const void* dy, const void* x, const void* alpha,
                              const float* mean, const float* rstd, void* dx,
                              void* dalpha, void* dbeta,
@@ -158,16 +153,17 @@ int tfb_colsum(const void* x, void* out, float* partials, int64_t n_partials,
  * Replaces the two torch.nn.Embedding lookups and their sum at the head of
  * Transformer.forward (transformer.py:259-272, 311-321) and their gradients.
  *   out[b,t,:] = tok[ids[b,t],:] (+ pos[t,:] when pos is not NULL), summed in fp32.
- * ids is a contiguous (batch, seq) int64 array; tok is (vocab, d), pos (>= seq, d), out
- * (batch, seq, d), all contiguous.  A token id outside [0, vocab) gives a zero row and
- * the sticky code 0x7100 in tfb_device_status().                               */
+ * ids is a contiguous (batch, seq) int64 array; tok is (vocab, d), pos (pos_rows, d) with
+ * pos_rows >= seq (checked), out (batch, seq, d), all contiguous.  A token id outside
+ * [0, vocab) gives a zero row and the sticky code 0x7100 in tfb_device_status().  */
 int tfb_embedding_fwd(const int64_t* ids, const void* tok, const void* pos, void* out,
-                      int64_t batch, int64_t seq, int64_t d, int64_t vocab, int dtype,
-                      void* stream);
+                      int64_t batch, int64_t seq, int64_t d, int64_t vocab, int64_t pos_rows,
+                      int dtype, void* stream);
 /* Bytes of scratch tfb_embedding_bwd needs (two int32 tables over the vocabulary
  * plus one fp32 row per position).                                             */
 int64_t tfb_embedding_bwd_scratch_bytes(int64_t batch, int64_t seq, int64_t d, int64_t vocab);
-/* ADDS the gradients to what dtok (vocab, d) and dpos (>= seq, d; may be NULL) hold:
+/* ADDS the gradients to what dtok (vocab, d; NULL for a frozen table: nothing is indexed or
+ * written for it) and dpos (pos_rows >= seq, d; may be NULL) hold:
  *   dtok[v,:] += sum over positions holding v of dout[b,t,:],  dpos[t,:] += sum_b dout[b,t,:]
  * with fp32 sums and one rounding per touched row; untouched rows are not written.
  * Tokens held by several positions are summed with fp32 atomics, so the order of
@@ -175,7 +171,7 @@ int64_t tfb_embedding_bwd_scratch_bytes(int64_t batch, int64_t seq, int64_t d, i
  * initialisation and is 16-byte aligned.                                       */
 int tfb_embedding_bwd(const int64_t* ids, const void* dout, void* dtok, void* dpos,
                       void* scratch, int64_t scratch_bytes, int64_t batch, int64_t seq,
-                      int64_t d, int64_t vocab, int dtype, void* stream);
+                      int64_t d, int64_t vocab, int64_t pos_rows, int dtype, void* stream);
 
 /* ------------------------------------------------------------------------ GEMM
  * Replaces mm / gemm / bmm + torch.sum (tritonformer/kernels/gemm.py:81-616,

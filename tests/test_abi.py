@@ -9,15 +9,20 @@ import tritonformer_b200._lib as L
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _declared():
-    text = open(os.path.join(ROOT, "include", "tritonformer_b200.h")).read()
+def _declared(header):
+    text = open(os.path.join(ROOT, "include", header)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(tfb_\w+)\s*\(", text)))
 
 
 def test_every_declared_symbol_is_exported_and_bound():
-    names = _declared()
-    assert len(names) >= 19
+    operators = _declared("tritonformer_b200.h")
+    switches = _declared("tritonformer_b200_debug.h")
+    assert len(operators) >= 19
+    # the test and tuning switches live in a header of their own, outside the operator interface
+    assert switches and all(n.startswith("tfb_debug_") for n in switches)
+    assert not any(n.startswith("tfb_debug_") for n in operators)
+    names = sorted(operators + switches)
     raw = ctypes.CDLL(L.LIB_PATH)
     for n in names:
         assert hasattr(raw, n), n
@@ -51,8 +56,14 @@ def test_argument_checks_without_device():
     assert L.lib.tfb_colsum_partials(8192, 4096) > 0
     assert L.lib.tfb_attention_bwd_scratch_bytes(1, 2, 64, 64) == 2 * 64 * 4 + 2 * 64 * 64 * 4  # 512 is 256-aligned
     # embeddings: shape, position count and scratch are checked before anything is launched
-    assert L.lib.tfb_embedding_fwd(None, None, None, None, 2, 8, 0, 100, 0, None) == -1  # d = 0
-    assert L.lib.tfb_embedding_fwd(None, None, None, None, 0, 8, 64, 100, 0, None) == 0  # no positions: nothing to do
+    assert L.lib.tfb_embedding_fwd(None, None, None, None, 2, 8, 0, 100, 0, 0, None) == -1  # d = 0
+    assert L.lib.tfb_embedding_fwd(None, None, None, None, 0, 8, 64, 100, 0, 0, None) == 0  # no positions: nothing to do
+    one = ctypes.c_void_p(16)  # never dereferenced: the row-count check comes before any launch
+    rc = L.lib.tfb_embedding_fwd(None, None, one, None, 2, 8, 64, 100, 4, 0, None)
+    assert rc == -1 and b"position table" in L.lib.tfb_last_error()
+    rc = L.lib.tfb_embedding_bwd(None, None, None, one, None, 0, 2, 8, 64, 100, 4, 0, None)
+    assert rc == -1 and b"position table" in L.lib.tfb_last_error()
     assert L.lib.tfb_embedding_bwd_scratch_bytes(2, 8, 64, 100) == 2 * 100 * 4 + 2 * 8 * 64 * 4
-    rc = L.lib.tfb_embedding_bwd(None, None, None, None, None, 0, 2, 8, 64, 100, 0, None)
+    rc = L.lib.tfb_embedding_bwd(None, None, one, None, None, 0, 2, 8, 64, 100, 0, 0, None)
     assert rc == -1 and b"scratch" in L.lib.tfb_last_error()
+    assert L.lib.tfb_embedding_bwd(None, None, None, None, None, 0, 2, 8, 64, 100, 0, 0, None) == 0  # both tables frozen

@@ -16,6 +16,9 @@ DIMS = [(int(b), int(nh), int(sq), int(hd)) for b in rng.randint(1, 4, size=NUM_
         for nh in rng.randint(4, 32, size=NUM_TEST) for sq in 64 * rng.randint(1, 32, size=NUM_TEST)
         for hd in rng.choice([32, 64], size=NUM_TEST, replace=True)]
 DIMS += [(1, 2, 64, 128), (2, 4, 2048, 64), (1, 3, 1024, 128), (1, 2, 4096, 128), (1, 1, 64, 32), (2, 16, 512, 64)]
+# the attention shapes of the named configurations: the fused-op benchmark case and the 410M model (B4 H16 T2048
+# hd64), the 840M model (B1 H12 T4096 hd128) and the 1.4B model (B2 H16 T2048 hd128)
+NAMED = [(4, 16, 2048, 64), (1, 12, 4096, 128), (2, 16, 2048, 128)]
 
 
 def _make(dims, dtype, strided):
@@ -45,7 +48,9 @@ def _compare(q, k, v, dy, out, bias_f32, dtype):
         assert a.stride() == getattr(q if nm == "dq" else k if nm == "dk" else v, "stride")()
         assert norm_rel(a, b_) < 2.5 * rel, nm
         if dtype is torch.float16:
-            assert_close(a, b_, 2e-2, nm)
+            # the reference tests' own bound (atol 1e-2 against a torch fp16 product) plus one fp16 rounding of
+            # gradients whose magnitude is above 1 (sums over up to thousands of positions)
+            assert_close(a, b_, 1e-2, nm, rtol=2e-3)
 
 
 @pytest.mark.parametrize("dims", DIMS)
@@ -56,6 +61,29 @@ def test_causal_attention_fp16(dims, strided):
     out = CausalAttention.apply(q, k, v)
     assert out.stride() == q.stride()
     _compare(q, k, v, dy, out, None, torch.float16)
+
+
+@pytest.mark.parametrize("dims", NAMED)
+@pytest.mark.parametrize("alibi", [False, True])
+def test_attention_shapes_of_the_named_configurations(dims, alibi):
+    """fp16 without bias and with the ALiBi slopes 2^(-8(i+1)/H) of the benchmark case; the 1.4B shape in bf16
+    with the reference's (H, T, T) table."""
+    from tritonformer_b200 import attention as A
+    b, nh, sq, hd = dims
+    bf16_table = alibi and dims == (2, 16, 2048, 128)
+    dtype = torch.bfloat16 if bf16_table else torch.float16
+    q, k, v, dy = _make(dims, dtype, True)
+    if not alibi:
+        out, bias_ref = A.CausalAttention.apply(q, k, v), None
+    elif bf16_table:
+        table = ops.alibi_table(sq, nh, torch.float16, "cuda")
+        out, bias_ref = A.BiasedCausalAttention.apply(q, k, v, table), table.float()
+    else:
+        slopes = torch.tensor([2.0 ** (-8.0 * (i + 1) / nh) for i in range(nh)], device="cuda")
+        pos = torch.arange(sq, device="cuda")
+        bias_ref = -slopes[:, None, None] * (pos.view(sq, 1) - pos.view(1, sq)).clamp_min(0).float()
+        out = A.BiasedCausalAttention.apply(q, k, v, slopes)
+    _compare(q, k, v, dy, out, bias_ref, dtype)
 
 
 @pytest.mark.parametrize("dims", DIMS[-6:])
@@ -143,3 +171,21 @@ def test_both_generations_of_forward_kernels_agree(dims, alibi):
         assert norm_rel(out, ref) < 2e-3
     assert_close(out1, out2, 4e-3, "kernels")
     assert_close(lse1, lse2, 2e-3, "lse")
+
+
+def test_alibi_finding_is_tied_to_the_tensor_object():
+    """The "this table is ALiBi" finding lives on the tensor object: a different table that reuses the same
+    address is examined afresh, and an in-place write makes the finding stale."""
+    from tritonformer_b200 import attention as A
+    nh, sq = 4, 128
+    table = ops.alibi_table(sq, nh, torch.float16, "cuda")
+    assert A._resolve_bias(table, nh, sq, torch.float16).slopes is not None
+    addr = table.data_ptr()
+    del table
+    dense = torch.randn((nh, sq, sq), device="cuda").half()  # the caching allocator hands the block out again
+    res = A._resolve_bias(dense, nh, sq, torch.float16)
+    assert res.table is not None and res.slopes is None, (addr, dense.data_ptr())
+    table = ops.alibi_table(sq, nh, torch.float16, "cuda")
+    assert A._resolve_bias(table, nh, sq, torch.float16).slopes is not None
+    table[:, 5, 2] = 0.25  # no longer ALiBi; the write bumps the version counter
+    assert A._resolve_bias(table, nh, sq, torch.float16).table is not None

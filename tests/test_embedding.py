@@ -86,3 +86,39 @@ def test_embedding_empty_batch():
     assert out.shape == (0, 4, 16)
     out.sum().backward()
     assert tok.grad.eq(0).all() and pos.grad.eq(0).all()
+
+
+def test_embedding_frozen_token_table_gets_no_gradient_buffer():
+    """A token table that needs no gradient is neither indexed nor written; the position table still gets its sums."""
+    from tritonformer_b200.embedding import Embedding
+    torch.manual_seed(2)
+    ids = torch.randint(0, 50, (3, 24), device="cuda")
+    tok = torch.randn((50, 64), device="cuda").half()  # frozen
+    pos = torch.randn((32, 64), device="cuda").half().requires_grad_(True)
+    out = Embedding.apply(ids, tok, pos)
+    w = torch.randn_like(out)
+    out.backward(w)
+    assert tok.grad is None
+    want = torch.zeros((32, 64), device="cuda")
+    want[:24] = w.float().sum(0)
+    assert (pos.grad.float() - want).abs().max().item() < 1e-2
+
+
+def test_embedding_fp32_tables_under_autocast():
+    """A model kept in fp32 under autocast: the tables are cast like the inputs of the other Functions and the
+    gradients come back in fp32."""
+    from tritonformer_b200.embedding import Embedding
+    torch.manual_seed(3)
+    ids = torch.randint(0, 40, (2, 16), device="cuda")
+    tok = torch.randn((40, 32), device="cuda").requires_grad_(True)
+    pos = torch.randn((16, 32), device="cuda").requires_grad_(True)
+    with torch.autocast("cuda", dtype=torch.float16):
+        out = Embedding.apply(ids, tok, pos)
+    assert out.dtype is torch.float16
+    ref = ops.embedding(ids, tok.detach().half().float(), pos.detach().half().float())
+    assert torch.equal(out, ref.half())
+    out.float().sum().backward()
+    assert tok.grad.dtype is torch.float32 and pos.grad.dtype is torch.float32
+    counts = torch.bincount(ids.view(-1), minlength=40).float()
+    assert torch.equal(tok.grad, counts[:, None].expand(40, 32))
+    assert torch.equal(pos.grad, torch.full((16, 32), 2.0, device="cuda"))

@@ -10,6 +10,7 @@ import pytest
 import torch
 
 import tritonformer_b200._lib as L
+from oracle import ops
 from util import norm_rel
 
 pytestmark = pytest.mark.gpu
@@ -50,18 +51,30 @@ def _static(x, dy, alpha, stats):
     return dx, da, db
 
 
+# Calls in a row on the shared array: a large one on the vectorised kernel, a narrower one, then the widest the
+# array takes (all 296 partial rows at d = 4096, generic kernel), then a narrow one whose width is not a multiple
+# of 8 straight after it, so that stale wide rows are followed by a small call.
+SHAPES = [(8192, 1024), (777, 392), (5000, 4096), (300, 390)]
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_static_scratch_entry_matches_regular_entry_twice(dtype):
-    # two calls in a row: a large one that fills the whole built-in array, then a smaller, narrower one
-    for seed, (rows, d) in enumerate([(8192, 1024), (777, 392)]):
+    for seed, (rows, d) in enumerate(SHAPES):
         args = _inputs(rows, d, seed, dtype)
         want = _regular(*args)
         got = _static(*args)
         torch.cuda.synchronize()
-        # dx is computed row by row and must agree exactly; the column sums are folded from a different
-        # number of fp32 partial rows, so they agree to the tolerance the LayerNorm tests use (1e-3)
+        # dx is computed row by row and must agree exactly; the column sums are folded from the same number of
+        # fp32 partial rows by the same kernel, read from the built-in array instead of the caller's buffer
         assert torch.equal(got[0], want[0])
         assert norm_rel(got[1], want[1]) < 1e-3 and norm_rel(got[2], want[2]) < 1e-3
+        # and against the fp32 oracle (the tolerance the LayerNorm tests use for the parameter gradients)
+        x, dy, alpha, _ = args
+        xr, ar = x.float().requires_grad_(True), alpha.float().requires_grad_(True)
+        br = torch.zeros_like(ar).requires_grad_(True)
+        ops.layer_norm(xr, ar, br, 1e-5).backward(dy.float())
+        tol = 1e-3 if dtype is torch.float16 else 8e-3
+        assert norm_rel(got[1], ar.grad) < tol and norm_rel(got[2], br.grad) < tol
 
 
 def test_static_scratch_entry_rejects_rows_wider_than_its_array():

@@ -1,4 +1,5 @@
-"""ctypes binding of libtritonformer_b200.so (the C ABI declared in include/tritonformer_b200.h).
+"""ctypes binding of libtritonformer_b200.so (the C ABI declared in include/tritonformer_b200.h; the
+tfb_debug_* switches in include/tritonformer_b200_debug.h).
 
 The library is the only implementation: if it is missing the import fails loudly, there is
 no Python or CPU fallback for any operator.
@@ -26,6 +27,7 @@ _SIGNATURES = {
     "tfb_device_status": (_i32, [_i32]),
     "tfb_debug_set": (None, [_i32, _i32]),
     "tfb_debug_counters": (_i32, [_c.POINTER(_c.c_uint64)]),
+    "tfb_debug_wait_probe": (_i32, [_c.c_uint64, _vp, _vp]),
     "tfb_layernorm_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _f32, _i32, _vp]),
     "tfb_layernorm_bwd_partials": (_i64, [_i64, _i64]),
     "tfb_layernorm_bwd": (_i32, [_vp] * 9 + [_i64] * 6 + [_i32, _vp]),
@@ -39,9 +41,9 @@ _SIGNATURES = {
     "tfb_relu_bwd": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp]),
     "tfb_colsum_partials": (_i64, [_i64, _i64]),
     "tfb_colsum": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp]),
-    "tfb_embedding_fwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp]),
+    "tfb_embedding_fwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
     "tfb_embedding_bwd_scratch_bytes": (_i64, [_i64] * 4),
-    "tfb_embedding_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
+    "tfb_embedding_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
     "tfb_gemm": (_i32, [_vp, _vp, _vp, _vp] + [_i64] * 8 + [_i32, _i32, _i32, _vp, _pi32]),
     "tfb_gemm_workspace_bytes": (_i64, []),
     "tfb_gemm_fused": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64] + [_i64] * 8 + [_i32, _i32, _vp, _i64, _vp, _pi32]),
@@ -110,4 +112,24 @@ def launch_count() -> int:
 
 
 def device_status(reset: bool = False) -> int:
-    return int(lib.tfb_device_status(1 if reset else 0))
+    """The status word of the current device (synchronises it).  With `reset`, clears a non-zero word and
+    zeroes the GEMM workspaces, whose arrival counters an abandoned split product can leave non-zero."""
+    code = int(lib.tfb_device_status(1 if reset else 0))
+    if reset and code != 0:
+        from . import linear
+        linear.reset_workspaces()
+    return code
+
+
+_STATUS_TEXT = {0x7100: "a token id outside the embedding table", 0x7e00: "the wait probe of the test suite"}
+
+
+def check_status() -> None:
+    """Raises RuntimeError if a kernel of the library reported a failure on the current device (a bounded wait
+    that ran out, a token id outside the embedding table).  Synchronises the device: call it where the host
+    waits anyway, e.g. next to the read-back of the loss.  The status stays set until device_status(reset=True)."""
+    code = device_status()
+    if code != 0:
+        what = _STATUS_TEXT.get(code, "a bounded wait inside a kernel ran out")
+        raise RuntimeError("tritonformer_b200: device status 0x%x (%s); the tensor-core kernels skip their work "
+                           "until the status is cleared with device_status(reset=True)" % (code, what))

@@ -5,7 +5,8 @@ q, k, v are (B, H, T, head_dim) with any {b,h,t} strides (the model passes strid
 log-sum-exp per row.  `BiasedCausalAttention` takes either the reference's dense (H, T, T) bias
 table or a (H,) tensor of ALiBi slopes; a table that is exactly the ALiBi table of
 transformer.generate_alibi_mask is recognised once (per buffer) and computed in-kernel from its
-slopes with the same rounding, so the table is never read again.
+slopes with the same rounding, so the table is never read again (the finding is kept on the tensor
+object itself and is redone after an in-place write).
 """
 import ctypes
 
@@ -37,9 +38,6 @@ class _Bias:
         self.slopes, self.rounded, self.table = slopes, rounded, table
 
 
-_alibi_cache = {}
-
-
 def _resolve_bias(attn_bias, heads, seq, dtype):
     if attn_bias is None:
         return _Bias()
@@ -53,13 +51,14 @@ def _resolve_bias(attn_bias, heads, seq, dtype):
     assert attn_bias.shape[1] == attn_bias.shape[2], (
         f"Expected attention bias to be a square but got nr = {attn_bias.shape[1]} and nc = {attn_bias.shape[2]}")
     assert attn_bias.shape[1] >= seq, "attention bias is smaller than the sequence"
-    key = (attn_bias.data_ptr(), tuple(attn_bias.shape), attn_bias.dtype, attn_bias._version)
-    hit = _alibi_cache.get(key)
-    if hit is None:
-        hit = _detect_alibi(attn_bias)
-        if len(_alibi_cache) > 64:
-            _alibi_cache.clear()
-        _alibi_cache[key] = hit
+    # The verdict is remembered ON the tensor object (with the version counter it was taken at), so it dies
+    # with the tensor: another table that later lands at the same address is a different object and is
+    # examined afresh.  In-place writes bump the counter; writes through `.data` do not and are not seen.
+    memo = getattr(attn_bias, "_tfb_alibi", None)
+    if memo is None or memo[0] != attn_bias._version:
+        memo = (attn_bias._version, _detect_alibi(attn_bias))
+        attn_bias._tfb_alibi = memo
+    hit = memo[1]
     if hit is not False:
         return _Bias(slopes=hit, rounded=1 if attn_bias.dtype is torch.float16 else 2)
     table = attn_bias if attn_bias.dtype == dtype else attn_bias.to(dtype)

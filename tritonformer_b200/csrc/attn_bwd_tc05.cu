@@ -17,8 +17,9 @@
 // warps per lane quarter, each taking a quarter of the columns), warps 18-21 drain dQ_i.
 // At head_dim 64, Pᵀ goes into the 64 TMEM columns that are left instead of shared memory and is
 // the A operand of the dV product.
-// At head_dim 64 the scores of tile i+1 are issued before the gradient products of tile i, so the
-// compute warps work on tile i+1 while the tensor core finishes tile i.
+// At head_dim 64 the scores of tile i+1 are issued as soon as the compute warps hold the scores of tile i in
+// registers, ahead of the gradient products of tile i, so the compute warps find them ready and work on tile
+// i+1 while the tensor core finishes tile i.
 // TMEM columns: [0,128) Sᵀ; [128,256) dPᵀ; [256,256+hd) dV; then dK; then dQ_i (at head_dim 128
 // dQ_i reuses the Sᵀ columns).
 #include "attn.cuh"
@@ -38,19 +39,25 @@ constexpr int FB_COMPUTE = 256;     // threads in the compute warps
 template <int HD> struct FbCfg {
   static constexpr int PANELS = HD / 64;
   static constexpr int TILE_BYTES = PANELS * 16384;   // 128 rows x HD x 2 B
-  static constexpr int QSTAGES = (HD == 64) ? 2 : 1;  // query-side ring depth (smem bound at hd 128)
+  // Query-side ring depth.  head_dim 64 needs three stages: the gradient products of tile i-1 still read their
+  // Q / dO while the scores of tile i+1 are issued (with two, the load of tile i+1 could only start when tile
+  // i-1 had retired, and its latency showed up as a wait for scores on every tile).  Pᵀ lives in tensor memory
+  // there, so its shared-memory buffer is not allocated and the third stage takes its place.  One stage at
+  // head_dim 128 (shared memory).
+  static constexpr int QSTAGES = (HD == 64) ? 3 : 1;
   static constexpr int OFF_K = 0;
   static constexpr int OFF_V = TILE_BYTES;
   static constexpr int OFF_Q = 2 * TILE_BYTES;                       // [QSTAGES]
   static constexpr int OFF_DO = OFF_Q + QSTAGES * TILE_BYTES;        // [QSTAGES]
-  static constexpr int OFF_P = OFF_DO + QSTAGES * TILE_BYTES;        // Pᵀ  128 x 128 x 2 B
-  static constexpr int OFF_DS = OFF_P + 32768;                       // dSᵀ 128 x 128 x 2 B
-  static constexpr int OFF_STAT = OFF_DS + 32768;                    // 2 x (lse2[128], delta[128]) fp32
+  static constexpr int OFF_P = OFF_DO + QSTAGES * TILE_BYTES;        // Pᵀ  128 x 128 x 2 B (head_dim 128 only)
+  static constexpr int OFF_DS = OFF_P + ((256 + 3 * HD + 64 <= 512) ? 0 : 32768);  // dSᵀ 128 x 128 x 2 B
+  static constexpr int OFF_STAT = OFF_DS + 32768;                    // [2 parities][16 compute warps][lse2[32], delta[32]] fp32
   // dQ_i staging for the TMA reduction (head_dim 64 only: it does not fit next to 128-wide tiles)
   static constexpr bool DQ_TMA = (HD == 64);
-  static constexpr int OFF_DQ = OFF_STAT + 2048;                     // 4 drain warps x 2 boxes of 32 rows x 128 B
+  static constexpr int OFF_DQ = OFF_STAT + 8192;                     // 4 drain warps x 2 boxes of 32 rows x 128 B
   static constexpr int OFF_BAR = OFF_DQ + (DQ_TMA ? 32768 : 0);
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+  static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
   static constexpr int COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 256 + HD;
   // dQ_i has columns of its own when they fit (hd 64); otherwise it reuses the Sᵀ columns
   static constexpr bool DQ_ALIASED = (256 + 3 * HD > 512);
@@ -68,19 +75,17 @@ struct FbParams {
   void *dk, *dv;
   int64_t sdk_b, sdk_h, sdk_t, sdv_b, sdv_h, sdv_t;
   int H, T;
+  int BH, group;  // batch*heads; how many of them are walked together (their tiles share the L2)
   float scale;
   int bias_mode;
   const float* slopes;
   int debug;  // test switch: bit 0 skips the dQ accumulation (timing experiments only)
 };
 
-__device__ __forceinline__ float alibi_term_b(int mode, float slope, int dist) {
-  return alibi_table_value(mode, slope, dist);
-}
-
 // Cycle counters for the timing switch (debug bit 1): [0] CTA iterations, [1..5] compute warp 2:
 // wait scores, math, wait previous products, smem write, barrier+stats; [6..9] MMA thread: wait P/dS,
-// wait Q/dO, wait dQ drain, total; [10,11] drain warp: wait, drain; [12] CTA lifetime.
+// wait Q/dO, wait dQ drain, total; [10,11] drain warp: wait, drain; [12] / [15] MMA thread: time to issue the
+// score products / the gradient products of a tile.
 static __device__ unsigned long long g_prof[16];
 #define PROF_T(var) long long var = prof ? clock64() : 0
 #define PROF_ADD(idx, t0, t1) do { if (prof) atomicAdd(&g_prof[idx], (unsigned long long)((t1) - (t0))); } while (0)
@@ -97,9 +102,7 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-__device__ __forceinline__ void compute_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(32 * FB_CWARPS) : "memory"); }
-
-template <typename T, int HD, bool BIAS>
+template <typename T, int HD, int BIAS>
 __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __grid_constant__ CUtensorMap tmQ,
                                                                       const __grid_constant__ CUtensorMap tmK,
                                                                       const __grid_constant__ CUtensorMap tmV,
@@ -110,28 +113,40 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
   constexpr int QS = Cfg::QSTAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  float* s_stat = reinterpret_cast<float*>(smem + Cfg::OFF_STAT);  // [2 parities][lse2[128], delta[128]]
+  float* s_stat = reinterpret_cast<float*>(smem + Cfg::OFF_STAT);  // [2 parities][16 warps][lse2[32], delta[32]]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
   uint64_t* kv_full = bars + 0;
-  uint64_t* q_full = bars + 1;    // [2] Q_i and dO_i landed
-  uint64_t* q_empty = bars + 3;   // [2] products reading them retired
-  uint64_t* s_full = bars + 5;    // Sᵀ and dPᵀ in TMEM
-  uint64_t* pds_full = bars + 6;  // Pᵀ and dSᵀ in smem (and Sᵀ, dPᵀ consumed)
-  uint64_t* dq_full = bars + 7;   // dV, dK, dQ_i products retired
-  uint64_t* dq_free = bars + 8;   // dQ_i read out of TMEM
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* q_full = bars + 1;    // [3] Q_i and dO_i landed
+  uint64_t* q_empty = bars + 4;   // [3] products reading them retired
+  uint64_t* s_full = bars + 7;    // Sᵀ and dPᵀ in TMEM
+  uint64_t* pds_full = bars + 8;  // Pᵀ and dSᵀ in smem (and Sᵀ, dPᵀ consumed)
+  uint64_t* dq_full = bars + 9;   // dV, dK, dQ_i products retired
+  uint64_t* dq_free = bars + 10;  // dQ_i read out of TMEM
+  uint64_t* s_free = bars + 11;   // Sᵀ and dPᵀ read out of TMEM (head_dim 64: the next scores may overwrite them)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kt = blockIdx.x;  // key tile; tile 0 has the longest walk and starts first
-  const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
-  const int j0 = kt * FB_T;
+  // CTAs are dispatched in block order: within a group of batch*head slices the key tiles with the
+  // longest walk (tile 0) of EVERY slice come first, so the tail of the kernel is made of short CTAs
   const int nq = p.T / FB_T;
+  int kt, bh;
+  if (p.debug & 32) {  // per-slice order (test switch)
+    kt = blockIdx.x % nq;
+    bh = blockIdx.x / nq;
+  } else {
+    const int g = blockIdx.x / (nq * p.group), r = blockIdx.x % (nq * p.group);
+    const int gsz = min(p.group, p.BH - g * p.group);
+    kt = r / gsz;
+    bh = g * p.group + r % gsz;
+  }
+  const int b = bh / p.H, h = bh % p.H;
+  const int j0 = kt * FB_T;
   const int iters = nq - kt;
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < 3; ++i) {
       mbar_init(&q_full[i], 1);
       mbar_init(&q_empty[i], 1);
     }
@@ -139,6 +154,7 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
     mbar_init(pds_full, FB_CWARPS);
     mbar_init(dq_full, 1);
     mbar_init(dq_free, 4);
+    mbar_init(s_free, FB_CWARPS);
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -183,102 +199,126 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
     }
   } else if (warp == 1) {
     // ----------------------------------------------------------------------- MMA issuer
-    if (lane == 0 && !dead) {
+    // The whole warp runs this code and one elected lane issues each tcgen05 instruction.  With the loop in a
+    // single lane the operand descriptors live in ordinary registers and every instruction pays for moving
+    // them to the uniform registers the tensor core reads (measured: 63 cycles per M128 N64 K16 instruction
+    // against 49 with warp-uniform code, and 80-120 in this kernel, where it made the issue of a tile's 32
+    // instructions the longest item of the step).
+    // At head_dim 128 every instruction is 64 cycles of tensor work, the single lane keeps up, and the faster
+    // bursts only took tensor-memory bandwidth from the compute warps (373 against 349 us at T 4096): there the
+    // loop stays in lane 0.
+    constexpr bool WHOLE_WARP = (HD == 64);
+    if (!dead && (WHOLE_WARP || lane == 0)) {
       constexpr int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
       constexpr uint32_t idesc_s = instr_desc_f16(128, 128, fmt, 0, 0);   // Sᵀ, dPᵀ : both K-major
       constexpr uint32_t idesc_kv = instr_desc_f16(128, HD, fmt, 0, 1);   // dV, dK  : A K-major, B MN-major
       constexpr uint32_t idesc_q = instr_desc_f16(128, HD, fmt, 1, 1);    // dQ      : both MN-major
-      // operand descriptors of every buffer in both roles, built once; each MMA only advances the
-      // start address (K-major: lbo unused, 8-row groups 1024 B apart; MN-major: 64-element chunks
-      // one 16 KB panel apart, 8-row groups 1024 B apart)
-      const uint64_t dk_k = smem_desc_sw128(smem_u32(smem + Cfg::OFF_K), 16, 1024);
-      const uint64_t dk_mn = smem_desc_sw128(smem_u32(smem + Cfg::OFF_K), 16384, 1024);
-      const uint64_t dv_k = smem_desc_sw128(smem_u32(smem + Cfg::OFF_V), 16, 1024);
-      const uint64_t dp_k = smem_desc_sw128(smem_u32(smem + Cfg::OFF_P), 16, 1024);
-      const uint64_t dds_k = smem_desc_sw128(smem_u32(smem + Cfg::OFF_DS), 16, 1024);
-      const uint64_t dds_mn = smem_desc_sw128(smem_u32(smem + Cfg::OFF_DS), 16384, 1024);
-      uint64_t dq_k[QS], dq_mn[QS], ddo_k[QS], ddo_mn[QS];
-#pragma unroll
-      for (int i = 0; i < QS; ++i) {
-        dq_k[i] = smem_desc_sw128(smem_u32(smem + Cfg::OFF_Q + i * Cfg::TILE_BYTES), 16, 1024);
-        dq_mn[i] = smem_desc_sw128(smem_u32(smem + Cfg::OFF_Q + i * Cfg::TILE_BYTES), 16384, 1024);
-        ddo_k[i] = smem_desc_sw128(smem_u32(smem + Cfg::OFF_DO + i * Cfg::TILE_BYTES), 16, 1024);
-        ddo_mn[i] = smem_desc_sw128(smem_u32(smem + Cfg::OFF_DO + i * Cfg::TILE_BYTES), 16384, 1024);
-      }
-      const bool prof = (p.debug & 2) != 0;
+      // read from shared memory: tell the compiler it is uniform
+      const uint32_t tb = WHOLE_WARP ? __shfl_sync(0xffffffffu, tmem_base, 0) : tmem_base;
+      auto leader = [&]() -> bool { return WHOLE_WARP ? elect_one() : true; };
+      // operand descriptors of every buffer in both roles; each MMA only advances the start address
+      // (K-major: lbo unused, 8-row groups 1024 B apart; MN-major: 64-element chunks one 16 KB panel apart,
+      // 8-row groups 1024 B apart)
+      const uint32_t s0 = smem_u32(smem);
+      const uint64_t dk_k = smem_desc_sw128(s0 + Cfg::OFF_K, 16, 1024);
+      const uint64_t dk_mn = smem_desc_sw128(s0 + Cfg::OFF_K, 16384, 1024);
+      const uint64_t dv_k = smem_desc_sw128(s0 + Cfg::OFF_V, 16, 1024);
+      const uint64_t dp_k = smem_desc_sw128(s0 + Cfg::OFF_P, 16, 1024);
+      const uint64_t dds_k = smem_desc_sw128(s0 + Cfg::OFF_DS, 16, 1024);
+      const uint64_t dds_mn = smem_desc_sw128(s0 + Cfg::OFF_DS, 16384, 1024);
+      const bool prof = (p.debug & 2) && lane == 0;
       PROF_T(tm_start);
-      bool ok = mbar_wait(kv_full, 0, 0x2200, abort_flag);
+      // every lane waits; the verdict is made uniform so that the warp stays converged
+      auto wait = [&](uint64_t* bar, uint32_t parity, int code) -> bool {
+        const bool r = mbar_wait(bar, parity, code, abort_flag);
+        return WHOLE_WARP ? (__all_sync(0xffffffffu, r) != 0) : r;
+      };
+      bool ok = wait(kv_full, 0, 0x2200);
       // Sᵀ = K Q_iᵀ and dPᵀ = V dO_iᵀ of query tile `it`
       auto issue_scores = [&](int it) -> bool {
         const int st = it % QS;
         PROF_T(a0);
-        if (!mbar_wait(&q_full[st], (it / QS) & 1, 0x2300 | st, abort_flag)) return false;
+        if (!wait(&q_full[st], (it / QS) & 1, 0x2300 | st)) return false;
         PROF_T(a1);
         PROF_ADD(7, a0, a1);
         tc_fence_after();
-        const uint64_t q_k = dq_k[st], do_k = ddo_k[st];
+        PROF_T(i0_);
+        const uint64_t q_k = smem_desc_sw128(s0 + Cfg::OFF_Q + st * Cfg::TILE_BYTES, 16, 1024);
+        const uint64_t do_k = smem_desc_sw128(s0 + Cfg::OFF_DO + st * Cfg::TILE_BYTES, 16, 1024);
 #pragma unroll
         for (int s = 0; s < HD / 16; ++s) {
           const uint32_t off = (s / 4) * 16384 + (s % 4) * 32;
-          tc_mma_ss(tmem_base + Cfg::COL_S, desc_advance(dk_k, off), desc_advance(q_k, off), idesc_s, s ? 1u : 0u);
+          if (leader()) tc_mma_ss(tb + Cfg::COL_S, desc_advance(dk_k, off), desc_advance(q_k, off), idesc_s, s ? 1u : 0u);
         }
 #pragma unroll
         for (int s = 0; s < HD / 16; ++s) {
           const uint32_t off = (s / 4) * 16384 + (s % 4) * 32;
-          tc_mma_ss(tmem_base + Cfg::COL_DP, desc_advance(dv_k, off), desc_advance(do_k, off), idesc_s, s ? 1u : 0u);
+          if (leader()) tc_mma_ss(tb + Cfg::COL_DP, desc_advance(dv_k, off), desc_advance(do_k, off), idesc_s, s ? 1u : 0u);
         }
-        tc_commit(s_full);
+        if (leader()) tc_commit(s_full);
+        PROF_T(i1_);
+        PROF_ADD(12, i0_, i1_);
         return true;
       };
       // dV += Pᵀ dO_i, dK += dSᵀ Q_i, dQ_i = dS K
       auto issue_grads = [&](int it) -> bool {
         const int st = it % QS;
-        const uint64_t q_mn = dq_mn[st], do_mn = ddo_mn[st];
+        const uint64_t q_mn = smem_desc_sw128(s0 + Cfg::OFF_Q + st * Cfg::TILE_BYTES, 16384, 1024);
+        const uint64_t do_mn = smem_desc_sw128(s0 + Cfg::OFF_DO + st * Cfg::TILE_BYTES, 16384, 1024);
         // the dQ columns still hold the previous tile's dQ until the drain warps are done with it
         PROF_T(a0);
-        if (it > 0 && !mbar_wait(dq_free, (it - 1) & 1, 0x2400, abort_flag)) return false;
+        if (it > 0 && !wait(dq_free, (it - 1) & 1, 0x2400)) return false;
         PROF_T(a1);
         PROF_ADD(8, a0, a1);
         tc_fence_after();
+        PROF_T(i0_);
+        const uint32_t acc = it ? 1u : 0u;
 #pragma unroll
         for (int s = 0; s < FB_T / 16; ++s) {  // contraction over the 128 queries of this tile
           const uint32_t koff = (s / 4) * 16384 + (s % 4) * 32;  // K-major A: 16 queries = 32 B along the row
           const uint32_t moff = s * 2048;                         // MN-major B: 16 query rows of 128 B
-          if (Cfg::P_TMEM)
-            tc_mma_ts(tmem_base + Cfg::COL_DV, tmem_base + Cfg::COL_PT + s * 8, desc_advance(do_mn, moff), idesc_kv,
-                      (it | s) ? 1u : 0u);
-          else
-            tc_mma_ss(tmem_base + Cfg::COL_DV, desc_advance(dp_k, koff), desc_advance(do_mn, moff), idesc_kv,
-                      (it | s) ? 1u : 0u);
-          tc_mma_ss(tmem_base + Cfg::COL_DK, desc_advance(dds_k, koff), desc_advance(q_mn, moff), idesc_kv,
-                    (it | s) ? 1u : 0u);
+          if (leader()) {
+            if (Cfg::P_TMEM)
+              tc_mma_ts(tb + Cfg::COL_DV, tb + Cfg::COL_PT + s * 8, desc_advance(do_mn, moff), idesc_kv, s ? 1u : acc);
+            else
+              tc_mma_ss(tb + Cfg::COL_DV, desc_advance(dp_k, koff), desc_advance(do_mn, moff), idesc_kv, s ? 1u : acc);
+            tc_mma_ss(tb + Cfg::COL_DK, desc_advance(dds_k, koff), desc_advance(q_mn, moff), idesc_kv, s ? 1u : acc);
+          }
         }
 #pragma unroll
         for (int s = 0; s < FB_T / 16; ++s) {  // contraction over the 128 keys of this CTA
           const uint32_t moff = s * 2048;      // 16 key rows of 128 B in dSᵀ and in K
-          tc_mma_ss(tmem_base + Cfg::COL_DQ, desc_advance(dds_mn, moff), desc_advance(dk_mn, moff), idesc_q,
-                    s ? 1u : 0u);
+          if (leader()) tc_mma_ss(tb + Cfg::COL_DQ, desc_advance(dds_mn, moff), desc_advance(dk_mn, moff), idesc_q, s ? 1u : 0u);
         }
-        tc_commit(&q_empty[st]);
-        tc_commit(dq_full);
+        if (leader()) {
+          tc_commit(&q_empty[st]);
+          tc_commit(dq_full);
+        }
+        PROF_T(i1_);
+        PROF_ADD(15, i0_, i1_);
         return true;
       };
       if (ok) ok = issue_scores(0);
       for (int it = 0; it < iters && ok; ++it) {
+        if (!Cfg::DQ_ALIASED && it + 1 < iters) {
+          // The compute warps hand Sᵀ / dPᵀ back as soon as they hold them in registers, about half-way through
+          // their work on the tile: the next tile's scores are issued then and have landed when the warps come
+          // back for them.  (Issued only once Pᵀ / dSᵀ were ready, they cost a round trip of 1.5 k cycles per
+          // tile that nothing hid: the score buffers cannot be doubled, tensor memory is full.)
+          if (!wait(s_free, it & 1, 0x2550)) { ok = false; break; }
+          if (!issue_scores(it + 1)) { ok = false; break; }
+        }
         PROF_T(a0);
-        if (!mbar_wait(pds_full, it & 1, 0x2500, abort_flag)) { ok = false; break; }
+        if (!wait(pds_full, it & 1, 0x2500)) { ok = false; break; }
         PROF_T(a1);
         PROF_ADD(6, a0, a1);
         if (!Cfg::DQ_ALIASED) {
-          // Sᵀ/dPᵀ of this tile are consumed: the next tile's scores go first, so the compute warps
-          // can start on them while the three gradient products of this tile run
-          if (it + 1 < iters) ok = issue_scores(it + 1);
-          if (ok) ok = issue_grads(it);
+          ok = issue_grads(it);
         } else {
           // dQ_i reuses the Sᵀ columns: the next scores may only follow once dQ_i has been drained
           ok = issue_grads(it);
           if (ok && it + 1 < iters) {
-            ok = mbar_wait(dq_free, it & 1, 0x2450, abort_flag);
+            ok = wait(dq_free, it & 1, 0x2450);
             if (ok) ok = issue_scores(it + 1);
           }
         }
@@ -286,6 +326,7 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
       PROF_T(tm_end);
       PROF_ADD(9, tm_start, tm_end);
     }
+    __syncwarp();
   } else if (warp < 2 + FB_CWARPS) {
     // -------------------------------------------------------------------------- compute
     if (!dead) {
@@ -296,26 +337,35 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
       const int ct = threadIdx.x - 64;   // 0..255 within the compute group
       const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
       const float c2 = p.scale * kLog2eB;
-      const float slope = BIAS ? p.slopes[h] : 0.f;
+      const AlibiLog2<BIAS> alibi(BIAS ? p.slopes[h] : 0.f);
       const int j = j0 + r;              // this thread's key
       uint8_t* sp = smem + Cfg::OFF_P;
       uint8_t* sds = smem + Cfg::OFF_DS;
       bool ok = true;
       const bool prof = (p.debug & 2) && threadIdx.x == 64;
-      // Every compute thread runs every iteration up to the named barrier, also after a wait gave
-      // up (the remaining waits then return at once), so nobody is left alone at the barrier.
+      // Per-query statistics of the warp's 32 query columns: lane l carries lse and delta of
+      // column l, fetched one tile ahead (so the global-memory latency is not part of the tile) and handed to the
+      // other lanes through a slice of shared memory that belongs to this warp: no barrier across the warps.
+      auto load_stat = [&](int it, float& l2, float& dl) {
+        const int64_t at = (int64_t)bh * p.T + (kt + it) * FB_T + cq * 32 + lane;
+        l2 = p.lse[at];  // converted to log2 units where it is used: nothing here may wait for the load
+        dl = p.delta[at];
+      };
+      float lse_next, delta_next;
+      load_stat(0, lse_next, delta_next);
       for (int it = 0; it < iters; ++it) {
         const int i0 = (kt + it) * FB_T;
         const bool diag = (it == 0);
         PROF_T(t0);
-        // per-query statistics of this tile, double buffered by iteration parity: a thread that is
-        // already here may share the CTA with one still computing the previous tile
-        float* s_lse2 = s_stat + (it & 1) * 256;
-        float* s_delta = s_lse2 + FB_T;
-        if (ct < FB_T) s_lse2[ct] = p.lse[(int64_t)bh * p.T + i0 + ct] * kLog2eB;
-        else if (ct < 2 * FB_T) s_delta[ct - FB_T] = p.delta[(int64_t)bh * p.T + i0 + ct - FB_T];
-        compute_bar_sync();
+        // this tile's statistics, double buffered by iteration parity: a lane that is already here may share
+        // the warp with one that still reads the previous tile's slice
+        float* s_lse2 = s_stat + ((it & 1) * FB_CWARPS + cw) * 64;
+        float* s_delta = s_lse2 + 32;
+        s_lse2[lane] = lse_next * kLog2eB;
+        s_delta[lane] = delta_next;
+        __syncwarp();
         PROF_T(t1);
+        if (it + 1 < iters) load_stat(it + 1, lse_next, delta_next);  // after the warp barrier, which would wait for it
         if (ok) ok = mbar_wait(s_full, it & 1, 0x2600, abort_flag);
         PROF_T(t2);
         PROF_ADD(5, t0, t1);
@@ -323,23 +373,36 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
         if (prof) atomicAdd(&g_prof[0], 1ull);
         uint32_t pk[16], dk_[16];  // this thread's 32 columns of Pᵀ and dSᵀ, packed 16-bit pairs
         long long t3 = 0, t4 = 0;
-        if (ok) {
+        const bool quiet = (p.debug & 128) != 0;  // timing experiment: the compute warps only keep the barriers going
+        if (quiet) {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) pk[e] = dk_[e] = 0u;
+          if (!Cfg::DQ_ALIASED && lane == 0) mbar_arrive(s_free);
+          if (it > 0 && ok) ok = mbar_wait(dq_full, (it - 1) & 1, 0x2650, abort_flag);
+        }
+        if (ok && !quiet) {
           tc_fence_after();
           const bool plain = !BIAS && !diag;  // no bias and not the diagonal tile: scale, subtract, 2^x
 #pragma unroll
           for (int c = 0; c < 2; ++c) {         // 16-column steps keep the live register set small
             const int col0 = cq * 32 + c * 16;
+            const float d0 = (float)(i0 + col0 - j);  // distance of the chunk's first query to this thread's key
             uint32_t sv_[16], dv_[16];
             PROF_T(tl0);
             tmem_ld16(lane_addr + Cfg::COL_S + col0, sv_);
             tmem_ld16(lane_addr + Cfg::COL_DP + col0, dv_);
             tc_wait_ld();
+            if (c == 1 && !Cfg::DQ_ALIASED) {  // this warp's share of Sᵀ and dPᵀ is in registers
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(s_free);
+            }
             PROF_T(tl1);
             PROF_ADD(14, tl0, tl1);
 #pragma unroll
             for (int e4 = 0; e4 < 4; ++e4) {
-              const float4 l4 = *reinterpret_cast<const float4*>(s_lse2 + col0 + e4 * 4);
-              const float4 d4 = *reinterpret_cast<const float4*>(s_delta + col0 + e4 * 4);
+              const float4 l4 = *reinterpret_cast<const float4*>(s_lse2 + c * 16 + e4 * 4);
+              const float4 d4 = *reinterpret_cast<const float4*>(s_delta + c * 16 + e4 * 4);
               const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
               const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
               float pe[4], de[4];
@@ -351,7 +414,7 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
                   pe[k] = ex2_approx_b(x);
                 } else {
                   const int i = i0 + col0 + e;
-                  if (BIAS) x += alibi_term_b(p.bias_mode, slope, max(i - j, 0)) * kLog2eB;
+                  x = alibi.sub_from(x, d0 + (float)e);  // a key above the diagonal (negative distance) is masked below
                   pe[k] = (j > i) ? 0.f : ex2_approx_b(x);
                 }
                 de[k] = pe[k] * (__uint_as_float(dv_[e]) - dl[k]);
@@ -369,7 +432,12 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
           PROF_ADD(2, t2, t3);
           PROF_ADD(3, t3, t4);
         }
-        if (ok) {
+        if (ok && quiet) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(pds_full);
+        }
+        if (ok && !quiet) {
           if (Cfg::P_TMEM) tmem_st16(lane_addr + Cfg::COL_PT + cq * 16, pk);  // this thread's 32 queries of Pᵀ
 #pragma unroll
           for (int v4 = 0; v4 < 4; ++v4) {
@@ -435,7 +503,7 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
       PROF_T(a1);
       PROF_ADD(10, a0, a1);
       tc_fence_after();
-      if (Cfg::DQ_TMA) {
+      if (Cfg::DQ_TMA && !(p.debug & 64)) {
         uint32_t v0[32], v1[32];
         tmem_ld32(lane_addr + Cfg::COL_DQ, v0);
         tmem_ld32(lane_addr + Cfg::COL_DQ + 32, v1);
@@ -523,7 +591,6 @@ __global__ void __launch_bounds__(256) attn_dq_convert_kernel(const float* __res
 }
 
 // ------------------------------------------------------------------------------- host side
-int attn_bwd_tc05_status(int reset) { return read_dev_status(reset); }
 
 // Copies the timing counters to `out` (16 values) and clears them.  Synchronises the device.
 int attn_bwd_tc05_counters(unsigned long long* out) {
@@ -570,16 +637,23 @@ static int bwd_tc05_launch(const AttnArgs& a, int dtype, cudaStream_t st) {
   p.sdv_b = a.sdv.b; p.sdv_h = a.sdv.h; p.sdv_t = a.sdv.t;
   p.H = a.H; p.T = a.T; p.scale = a.scale; p.bias_mode = a.bias_mode; p.slopes = a.slopes;
   p.debug = g_attn_debug.load();
-  static std::atomic<uint64_t> done_plain{0}, done_bias{0};
-  if ((rc = ensure_dynamic_smem(attn_bwd_tc05_kernel<T, HD, false>, Cfg::SMEM_BYTES, done_plain, "attention_bwd(tcgen05)")))
-    return rc;
-  if ((rc = ensure_dynamic_smem(attn_bwd_tc05_kernel<T, HD, true>, Cfg::SMEM_BYTES, done_bias, "attention_bwd(tcgen05)")))
-    return rc;
-  dim3 grid(a.T / FB_T, a.B * a.H);
-  if (a.bias_mode)
-    launch_overlapped(attn_bwd_tc05_kernel<T, HD, true>, grid, dim3(FB_THREADS), Cfg::SMEM_BYTES, st, tq, tk, tv, tdo, tdq, p);
-  else
-    launch_overlapped(attn_bwd_tc05_kernel<T, HD, false>, grid, dim3(FB_THREADS), Cfg::SMEM_BYTES, st, tq, tk, tv, tdo, tdq, p);
+  p.BH = a.B * a.H;
+  p.group = attn_slices_per_group(a.B * a.H, a.T, HD);
+  dim3 grid((a.T / FB_T) * a.B * a.H);
+  static std::atomic<uint64_t> done[4] = {{0}, {0}, {0}, {0}};
+#define FB_LAUNCH(MODE, SLOT)                                                                                       \
+  {                                                                                                                 \
+    if ((rc = ensure_dynamic_smem(attn_bwd_tc05_kernel<T, HD, MODE>, Cfg::SMEM_BYTES, done[SLOT],                   \
+                                  "attention_bwd(tcgen05)")))                                                       \
+      return rc;                                                                                                    \
+    launch_overlapped(attn_bwd_tc05_kernel<T, HD, MODE>, grid, dim3(FB_THREADS), Cfg::SMEM_BYTES, st, tq, tk, tv, tdo, \
+                      tdq, p);                                                                                      \
+  }
+  if (a.bias_mode == 0) FB_LAUNCH(0, 0)
+  else if (a.bias_mode == 1) FB_LAUNCH(1, 1)
+  else if (a.bias_mode == 2) FB_LAUNCH(2, 2)
+  else FB_LAUNCH(4, 3)
+#undef FB_LAUNCH
   if ((rc = launched("attention_bwd(tcgen05)"))) return rc;
   const int64_t nvec = (int64_t)a.B * a.H * a.T * HD / 8;
   const unsigned blocks = (unsigned)(ceil_div(nvec, 256) < 148 * 8 ? ceil_div(nvec, 256) : 148 * 8);

@@ -483,7 +483,6 @@ __global__ void __launch_bounds__(F2_THREADS, 1) attn_fwd2_tc05_kernel(const __g
 }
 
 // ------------------------------------------------------------------------------- host side
-int attn_fwd2_tc05_status(int reset) { return read_dev_status(reset); }
 
 // Copies the 16 cycle counters to the host and clears them.
 int attn_fwd2_tc05_counters(unsigned long long* out) {

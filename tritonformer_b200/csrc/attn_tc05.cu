@@ -300,7 +300,6 @@ __global__ void __launch_bounds__(FA_THREADS, 1) attn_fwd_tc05_kernel(const __gr
 }
 
 // ------------------------------------------------------------------------------- host side
-int attn_tc05_status(int reset) { return read_dev_status(reset); }
 
 static int encode_qkv(CUtensorMap* m, const void* ptr, const AttnStrides& s, int B, int H, int T, int hd, int dtype) {
   const uint64_t dims[4] = {(uint64_t)hd, (uint64_t)T, (uint64_t)H, (uint64_t)B};

@@ -82,6 +82,17 @@ __device__ __forceinline__ void allow_dependents() { asm volatile("griddepcontro
     if (!(cond)) return ::tfb::fail(TFB_ERR_ARG, __VA_ARGS__); \
   } while (0)
 
+// SMs of the device the library first ran on (every GPU of a node is the same part).
+inline int sm_count() {
+  static int n = []() {
+    int dev = 0, v = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    return v > 0 ? v : 148;
+  }();
+  return n;
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 

@@ -10,7 +10,7 @@
 
 namespace tfb {
 
-static __device__ int g_embed_status = 0;
+extern __device__ int g_dev_status;  // the library's status word (status.cu)
 constexpr int kBadToken = 0x7100;       // a token id outside [0, vocab)
 constexpr int kTableFill = 0x7f7f7f7f;  // what a byte fill of 0x7f leaves in every int32
 constexpr int kTestLanes = 32;          // threads per row in the kernels that mostly test and skip rows
@@ -43,7 +43,7 @@ __global__ void __launch_bounds__(256) embed_fwd_kernel(const int64_t* __restric
   for (int64_t row = (int64_t)blockIdx.x * per + sub; row < n; row += (int64_t)gridDim.x * per) {
     const int64_t id = ids[row];
     const bool ok = id >= 0 && id < vocab;
-    if (!ok && l == 0) atomicCAS(&g_embed_status, 0, kBadToken);
+    if (!ok && l == 0) atomicCAS(&g_dev_status, 0, kBadToken);
     const T* prow = pos ? pos + (row % seq) * d : nullptr;
     for (int c = l; c < chunks; c += lanes) {
       float a[W];
@@ -74,7 +74,7 @@ __global__ void __launch_bounds__(256) embed_index_kernel(const int64_t* __restr
       atomicMin(table + id, (int)i);
       atomicAdd(table + vocab + id, 1);
     } else {
-      atomicCAS(&g_embed_status, 0, kBadToken);
+      atomicCAS(&g_dev_status, 0, kBadToken);
     }
   }
 }
@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(256) embed_bwd_scatter_kernel(const int64_t* _
           if (b0 + u < batch) {
             const int64_t row = (b0 + u) * seq + t;
             load_w<T, W>(dout + row * d + c * W, g[u]);
-            const int64_t v = ids[row];
+            const int64_t v = dtok ? ids[row] : -1;  // no token-table gradient wanted: position sums only
             if (v >= 0 && v < vocab) {
               id[u] = v;
               direct[u] = held(table, vocab, v) == 1u;
@@ -194,16 +194,6 @@ __global__ void __launch_bounds__(256) embed_bwd_fold_kernel(const int64_t* __re
   }
 }
 
-int embedding_status(int reset) {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_embed_status, sizeof(int)) != cudaSuccess) return -1;
-  if (reset && v != 0) {
-    const int z = 0;
-    cudaMemcpyToSymbol(g_embed_status, &z, sizeof(int));
-  }
-  return v;
-}
-
 // Threads per row: the smallest power of two that covers the row's chunks, at most 256.
 static int lanes_for(int64_t chunks) {
   int lanes = 1;
@@ -221,8 +211,10 @@ static unsigned grid_for(int64_t units, int per) {
 using namespace tfb;
 
 extern "C" int tfb_embedding_fwd(const int64_t* ids, const void* tok, const void* pos, void* out, int64_t batch,
-                                 int64_t seq, int64_t d, int64_t vocab, int dtype, void* stream) {
+                                 int64_t seq, int64_t d, int64_t vocab, int64_t pos_rows, int dtype, void* stream) {
   TFB_REQUIRE(batch >= 0 && seq >= 0 && d > 0 && d < (1 << 30) && vocab > 0, "embedding_fwd: bad shape");
+  TFB_REQUIRE(pos == nullptr || seq <= pos_rows, "embedding_fwd: sequence of %lld longer than the position table (%lld rows)",
+              (long long)seq, (long long)pos_rows);
   const int64_t n = batch * seq;
   if (n == 0) return TFB_OK;
   cudaStream_t st = (cudaStream_t)stream;
@@ -249,11 +241,13 @@ extern "C" int64_t tfb_embedding_bwd_scratch_bytes(int64_t batch, int64_t seq, i
 
 extern "C" int tfb_embedding_bwd(const int64_t* ids, const void* dout, void* dtok, void* dpos, void* scratch,
                                  int64_t scratch_bytes, int64_t batch, int64_t seq, int64_t d, int64_t vocab,
-                                 int dtype, void* stream) {
+                                 int64_t pos_rows, int dtype, void* stream) {
   TFB_REQUIRE(batch >= 0 && seq >= 0 && d > 0 && d < (1 << 30) && vocab > 0, "embedding_bwd: bad shape");
+  TFB_REQUIRE(dpos == nullptr || seq <= pos_rows, "embedding_bwd: sequence of %lld longer than the position table (%lld rows)",
+              (long long)seq, (long long)pos_rows);
   const int64_t n = batch * seq;
   TFB_REQUIRE(n < (1 << 30), "embedding_bwd: more than 2^30 positions");
-  if (n == 0) return TFB_OK;
+  if (n == 0 || (dtok == nullptr && dpos == nullptr)) return TFB_OK;
   TFB_REQUIRE(scratch != nullptr && aligned16(scratch) &&
                   scratch_bytes >= tfb_embedding_bwd_scratch_bytes(batch, seq, d, vocab),
               "embedding_bwd: scratch must hold tfb_embedding_bwd_scratch_bytes() bytes, 16-byte aligned");
@@ -261,11 +255,14 @@ extern "C" int tfb_embedding_bwd(const int64_t* ids, const void* dout, void* dto
   int* table = (int*)scratch;
   const int64_t table_bytes = ceil_div(2 * vocab * (int64_t)sizeof(int), 16) * 16;
   float* sums = (float*)((char*)scratch + table_bytes);
-  TFB_REQUIRE(cudaMemsetAsync(table, 0x7f, (size_t)table_bytes, st) == cudaSuccess, "embedding_bwd: table fill failed");
-  embed_index_kernel<<<grid_for(n, 256), 256, 0, st>>>(ids, table, n, vocab);
-  int rc = launched("embedding_bwd index");
-  if (rc) return rc;
-  {
+  int rc = TFB_OK;
+  if (dtok) {  // a frozen token table (dtok == NULL) needs neither the index nor the fp32 scratch rows
+    TFB_REQUIRE(cudaMemsetAsync(table, 0x7f, (size_t)table_bytes, st) == cudaSuccess, "embedding_bwd: table fill failed");
+    embed_index_kernel<<<grid_for(n, 256), 256, 0, st>>>(ids, table, n, vocab);
+    rc = launched("embedding_bwd index");
+    if (rc) return rc;
+  }
+  if (dtok) {
     // most rows are only tested (few tokens are held twice): a warp per row keeps eight tests in flight per CTA
     const int lanes = kTestLanes;
     launch_overlapped(embed_clear_kernel, dim3(grid_for(n, 256 / lanes)), dim3(256), 0, st, ids, (const int*)table, sums,
@@ -280,7 +277,7 @@ extern "C" int tfb_embedding_bwd(const int64_t* ids, const void* dout, void* dto
       launch_overlapped(embed_bwd_scatter_kernel<T, 8>, dim3(grid_for(seq, 256 / lanes)), dim3(256), 0, st, ids,
                         (const T*)dout, (T*)dtok, (T*)dpos, (const int*)table, sums, batch, seq, (int)d, vocab, lanes);
       rc = launched("embedding_bwd scatter");
-      if (rc) return rc;
+      if (rc || !dtok) return rc;
       launch_overlapped(embed_bwd_fold_kernel<T, 8>, dim3(grid_for(n, 256 / kTestLanes)), dim3(256), 0, st, ids,
                         (T*)dtok, (const int*)table, (const float*)sums, n, (int)d, vocab, kTestLanes);
     } else {
@@ -288,7 +285,7 @@ extern "C" int tfb_embedding_bwd(const int64_t* ids, const void* dout, void* dto
       launch_overlapped(embed_bwd_scatter_kernel<T, 1>, dim3(grid_for(seq, 256 / lanes)), dim3(256), 0, st, ids,
                         (const T*)dout, (T*)dtok, (T*)dpos, (const int*)table, sums, batch, seq, (int)d, vocab, lanes);
       rc = launched("embedding_bwd scatter");
-      if (rc) return rc;
+      if (rc || !dtok) return rc;
       launch_overlapped(embed_bwd_fold_kernel<T, 1>, dim3(grid_for(n, 256 / kTestLanes)), dim3(256), 0, st, ids,
                         (T*)dtok, (const int*)table, (const float*)sums, n, (int)d, vocab, kTestLanes);
     }

@@ -460,7 +460,6 @@ int gemm_pair_counters(int cta, unsigned long long* out) {
   return 0;
 }
 
-int gemm_pair_tc05_status(int reset) { return read_dev_status(reset); }
 
 int encode_tmap_sw128(CUtensorMap* out, const void* base, int dtype, int rank, const uint64_t* dims,
                       const uint64_t* strides_bytes, const uint32_t* box);

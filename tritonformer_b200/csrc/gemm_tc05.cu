@@ -416,17 +416,6 @@ int encode_tmap_sw128(CUtensorMap* out, const void* base, int dtype, int rank, c
   return TFB_OK;
 }
 
-int gemm_tc05_status(int reset) { return read_dev_status(reset); }
-
-static int sm_count() {
-  static int n = []() {
-    int dev = 0, v = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
-    return v > 0 ? v : 148;
-  }();
-  return n;
-}
 
 // Arrival counters plus one fp32 128 x 256 partial tile per SM.
 int64_t gemm_tc05_workspace_bytes() { return kFlagBytes + (int64_t)sm_count() * TB_M * 256 * (int64_t)sizeof(float); }

@@ -1,6 +1,7 @@
 // Library-wide state of the tritonformer_b200 C ABI: version, last error, launch counter,
 // test switches, and the GEMM entry point that picks between the two GEMM kernels.
 #include "common.cuh"
+#include "../../include/tritonformer_b200_debug.h"
 
 namespace tfb {
 thread_local char g_err[512] = {0};
@@ -22,14 +23,9 @@ int gemm_tc05(const void* a, const void* b, void* c, const void* bias, const voi
 bool gemm_tc05_eligible(const void* a, const void* b, const void* c, const void* bias, const void* addend,
                         int64_t ld_addend, const void* mask, int64_t ld_mask, int64_t M, int64_t N, int64_t K,
                         int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int64_t ldc);
-int gemm_tc05_status(int reset);
-int gemm_pair_tc05_status(int reset);
 int64_t gemm_tc05_workspace_bytes();
-int attn_tc05_status(int reset);
-int attn_bwd_tc05_status(int reset);
-int attn_fwd2_tc05_status(int reset);
-int attn_fwd1_tc05_status(int reset);
-int embedding_status(int reset);
+int read_dev_status(int reset);
+int launch_wait_probe(unsigned long long limit_ns, int* waited_ok, cudaStream_t st);
 int attn_bwd_tc05_counters(unsigned long long* out);
 int gemm_pair_counters(int cta, unsigned long long* out);
 int attn_fwd2_tc05_counters(unsigned long long* out);
@@ -45,14 +41,12 @@ extern "C" int64_t tfb_launch_count(void) { return g_launches.load(); }
 
 extern "C" int tfb_device_status(int reset) {
   cudaDeviceSynchronize();
-  const int a = gemm_tc05_status(reset);
-  const int b = attn_tc05_status(reset);
-  const int c = attn_bwd_tc05_status(reset);
-  const int d = attn_fwd2_tc05_status(reset);
-  const int e = gemm_pair_tc05_status(reset);
-  const int f = attn_fwd1_tc05_status(reset);
-  const int g = embedding_status(reset);
-  return a ? a : (b ? b : (c ? c : (d ? d : (e ? e : (f ? f : g)))));
+  return read_dev_status(reset);
+}
+
+extern "C" int tfb_debug_wait_probe(unsigned long long limit_ns, int* waited_ok, void* stream) {
+  TFB_REQUIRE(limit_ns <= 100000000ull, "wait_probe: limit above 100 ms");
+  return launch_wait_probe(limit_ns, waited_ok, (cudaStream_t)stream);
 }
 
 extern "C" int tfb_debug_counters(unsigned long long* out16) {

@@ -8,20 +8,11 @@
 
 namespace tfb {
 
-// Sticky status word, one per translation unit that includes this header: 0 = fine,
-// otherwise the code of the first wait that gave up.  Kernels of that unit do nothing while
-// it is non-zero; read_dev_status() fetches (and optionally clears) it from the host.
-static __device__ int g_dev_status = 0;
-
-static inline int read_dev_status(int reset) {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_dev_status, sizeof(int)) != cudaSuccess) return -1;
-  if (reset && v != 0) {
-    const int z = 0;
-    cudaMemcpyToSymbol(g_dev_status, &z, sizeof(int));
-  }
-  return v;
-}
+// Sticky status word of the library, one per GPU (defined in status.cu): 0 = fine, otherwise the code
+// of the first wait that gave up or of the first bad token id.  Every tcgen05 kernel returns at once
+// while it is non-zero; read_dev_status() fetches (and optionally clears) it for the current device.
+extern __device__ int g_dev_status;
+int read_dev_status(int reset);
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -77,13 +68,14 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s: three orders above any healthy kernel
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code, volatile int* abort_flag,
+                                          uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_ns();
   for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (global_ns() - t0 > kWaitLimitNs) break;
+    if (global_ns() - t0 > limit_ns) break;
   }
   *abort_flag = 1;
   atomicCAS(&g_dev_status, 0, code);

@@ -72,6 +72,13 @@ class GradBuckets:
         for b in self.buckets:
             b.zero_()
 
+    def accumulate(self):
+        """Context manager for the forward+backward of a step: the kernels that produce weight, LayerNorm and
+        embedding gradients add them straight into the bucket views (`linear.accumulate_into_grad`), so no
+        separate accumulation kernels run.  Clear the buckets with `zero()` at the start of a step."""
+        from . import linear
+        return linear.accumulate_into_grad()
+
     def check_views(self):
         """Autograd must have accumulated in place: every .grad still aliases its bucket."""
         for p, view in self._views:

@@ -38,7 +38,7 @@ class LayerNormFork(Function):
             return dres, None, None, None
         dres = dres.to(x.dtype) if dres is not None else None
         into = None
-        if L.ACCUMULATE_INTO_GRAD and ctx.needs_input_grad[1] and ctx.needs_input_grad[2]:
+        if L.accumulating() and ctx.needs_input_grad[1] and ctx.needs_input_grad[2]:
             ga, gb = alpha.grad, beta.grad
             if ga is not None and gb is not None and ga.is_contiguous() and gb.is_contiguous() \
                     and ga.dtype == x.dtype and gb.dtype == x.dtype and ga.shape == alpha.shape == gb.shape:
@@ -125,7 +125,7 @@ class QKVProjection(Function):
                 dx = L.input_grad(dy, w, x.shape) if need[0] else None
                 dws = [None, None, None]
                 pgrads = [p.grad for p in (wq, wk, wv)]
-                if L.ACCUMULATE_INTO_GRAD and all(need[1:4]) and all(g is not None for g in pgrads) \
+                if L.accumulating() and all(need[1:4]) and all(g is not None for g in pgrads) \
                         and pgrads[0].dtype == x.dtype and pgrads[0].shape == wq.shape \
                         and _adjacent_columns(pgrads, 3 * d):
                     # the three .grad are column blocks of one (in, 3 d) matrix (GradBuckets column_blocks):
@@ -140,7 +140,7 @@ class QKVProjection(Function):
                         if not need[1 + i]:
                             continue
                         part = dw[:, i * d:(i + 1) * d]
-                        if L.ACCUMULATE_INTO_GRAD and p.grad is not None and p.grad.dtype == part.dtype \
+                        if L.accumulating() and p.grad is not None and p.grad.dtype == part.dtype \
                                 and p.grad.shape == part.shape:
                             p.grad.add_(part)
                         else:

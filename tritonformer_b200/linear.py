@@ -6,6 +6,8 @@ operand strides; the weight gradient contracts over all B*T rows at once in fp32
 producing per-batch partials and summing them.  Bias and ReLU are applied in the GEMM epilogue.
 The incoming gradient is never modified (the reference masks it in place).
 """
+import collections
+import contextlib
 import ctypes
 
 import torch
@@ -54,14 +56,38 @@ def replay(calls, device):
              addend=addend, mask=mask)
 
 
-# When True, a weight gradient is added straight into an existing, contiguous `.grad` by the GEMM
-# epilogue (one rounding of accumulator + old value) and the Function reports no gradient for the
-# weight, so autograd launches no separate accumulation kernel.  Off by default because parameter
-# hooks do not fire for gradients delivered this way; the benchmark and the data-parallel buckets
-# turn it on.
-ACCUMULATE_INTO_GRAD = False
+# Inside `with accumulate_into_grad():` a weight gradient is added straight into an existing, contiguous
+# `.grad` by the GEMM epilogue (one rounding of accumulator + old value) and the Function reports no
+# gradient for the weight, so autograd launches no separate accumulation kernel.  Off outside the block,
+# because parameter hooks do not fire for gradients delivered this way; `dp.GradBuckets.accumulate()`
+# is the same block for a model whose gradients live in flat buckets.
+_accumulate_depth = 0
 
-_workspaces = {}
+
+def accumulating() -> bool:
+    return _accumulate_depth > 0
+
+
+@contextlib.contextmanager
+def accumulate_into_grad(enabled: bool = True):
+    """Weight, LayerNorm-parameter and embedding gradients produced inside the block are added into the
+    existing `.grad` buffers by the kernels that compute them."""
+    global _accumulate_depth
+    if not enabled:
+        yield
+        return
+    _accumulate_depth += 1
+    try:
+        yield
+    finally:
+        _accumulate_depth -= 1
+
+
+# GEMM scratch, newest last; at most _MAX_WORKSPACES are kept per process.  An entry that falls out is
+# returned to the caching allocator, which hands it out again only in the order of the stream it was
+# allocated on, so kernels still in flight on that stream keep their scratch.
+_workspaces = collections.OrderedDict()
+_MAX_WORKSPACES = 8
 
 
 def _gemm_workspace(device, stream):
@@ -73,7 +99,18 @@ def _gemm_workspace(device, stream):
     if ws is None:
         ws = torch.zeros(int(_lib.lib.tfb_gemm_workspace_bytes()), device=device, dtype=torch.uint8)
         _workspaces[key] = ws
+        while len(_workspaces) > _MAX_WORKSPACES:
+            _workspaces.popitem(last=False)
+    else:
+        _workspaces.move_to_end(key)
     return ws
+
+
+def reset_workspaces():
+    """Zeroes every cached GEMM workspace.  For use after the device status word was cleared: a split product
+    that gave up can leave arrival counters non-zero."""
+    for ws in _workspaces.values():
+        ws.zero_()
 
 
 def gemm(a, a_sm, a_sk, b, b_sk, b_sn, m, n, k, bias=None, relu=False, out=None, accumulate=False,
@@ -149,12 +186,12 @@ def input_grad(dy, w, x_shape, mask=None, addend=None, out=None):
 
 def weight_grad(x, dy, w):
     """dW = Xᵀ dY over every row of the flattened batch.  Returns None when the product was added
-    straight into `w.grad` (see ACCUMULATE_INTO_GRAD)."""
+    straight into `w.grad` (see accumulate_into_grad)."""
     x2, dy2 = _as_rows(x), _as_rows(dy)
     m, k = x2.shape
     n = dy2.shape[1]
     into = None
-    if ACCUMULATE_INTO_GRAD and w.grad is not None and w.grad.is_contiguous() and w.grad.dtype == x.dtype \
+    if accumulating() and w.grad is not None and w.grad.is_contiguous() and w.grad.dtype == x.dtype \
             and w.grad.shape == (k, n):
         into = w.grad
     # A(mm, kk) = X[kk, mm]
