@@ -28,6 +28,7 @@ sys.path.insert(0, ROOT)
 
 CONFIGS = {
     # name: (d_model, layers, heads, ffn, vocab, ctx, batch/GPU, dtype, linear bias, ALiBi)
+    "160m": (768, 12, 12, 3072, 50304, 1024, 2, "fp16", False, False),  # the CPU-runnable configuration
     "410m": (1024, 24, 16, 4096, 50304, 2048, 4, "fp16", False, False),
     "840m": (1536, 24, 12, 6144, 50304, 4096, 1, "fp16", False, False),
     "1.4b": (2048, 24, 16, 8192, 50304, 2048, 2, "bf16", True, True),
@@ -35,11 +36,14 @@ CONFIGS = {
 METRIC = "fwd+bwd tokens/s, 410M ctx2048 fp16 AMP"
 
 
-def make_config(name):
-    from tritonformer_b200.transformer import TransformerConfig
+def make_config(name, config_cls=None):
+    """`config_cls`: the class that carries the fields (the product's TransformerConfig by default; the CPU arm
+    passes the oracle's own, so that it never loads the product package)."""
+    if config_cls is None:
+        from tritonformer_b200.transformer import TransformerConfig as config_cls
     d, L, H, ffn, V, T, B, dt, lb, ab = CONFIGS[name]
-    cfg = TransformerConfig(vocab_size=V, hidden_size=d, max_position_embeddings=T, num_attention_heads=H,
-                            head_dim=d // H, ffn_dim=ffn, num_hidden_layers=L, use_linear_bias=lb, attn_bias=ab)
+    cfg = config_cls(vocab_size=V, hidden_size=d, max_position_embeddings=T, num_attention_heads=H,
+                     head_dim=d // H, ffn_dim=ffn, num_hidden_layers=L, use_linear_bias=lb, attn_bias=ab)
     return cfg, B, T, (torch.float16 if dt == "fp16" else torch.bfloat16)
 
 
@@ -113,41 +117,54 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------- CPU baseline
-def cpu_reference_step_time(config_name, steps, warmup, sample_batch=1, sample_seq=512):
-    """Seconds per fwd+bwd step of the fp32 oracle model on the host cores, on a bounded sample
-    (sample_batch x sample_seq tokens) of the configuration."""
-    from oracle.model import OracleTransformer, init_weights
-    cfg, _, _, _ = make_config(config_name)
+CPU_CONFIG = "160m"  # d768, 12 layers, 12 heads, ffn 3072, vocab 50304, ctx 1024, batch 2, fp32: the reference model's
+                     # CPU-runnable configuration; one step is 1.65 TFLOP by the count of algorithmic_flops()
+
+
+def cpu_reference_step_time(steps, warmup):
+    """Seconds per fwd+bwd step (median) of the fp32 restatement of the reference model on the host cores, on
+    the CPU-runnable configuration at its full batch and context.  Loads nothing of the product package."""
+    from oracle.model import OracleConfig, OracleTransformer, init_weights
+    cfg, batch, seq, _ = make_config(CPU_CONFIG, OracleConfig)
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     gen = torch.Generator().manual_seed(1234)
     model = OracleTransformer(cfg)
     init_weights(model, cfg.num_hidden_layers, lm_head_std=0.02, generator=gen)
-    ids = torch.randint(0, cfg.vocab_size, (sample_batch, sample_seq), generator=gen)
+    ids = torch.randint(0, cfg.vocab_size, (batch, seq), generator=gen)
     times = []
     for i in range(warmup + steps):
         t0 = time.perf_counter()
+        model.zero_grad(set_to_none=True)
         _, loss = model(ids, ids)
         loss.backward()
         if i >= warmup:
             times.append(time.perf_counter() - t0)
-    return statistics.median(times), cores, cfg, sample_batch, sample_seq
+    return statistics.median(times), cores, cfg, batch, seq
+
+
+def _cpu_sample_text(batch, seq, steps):
+    return (f"reference model restated in fp32 PyTorch (oracle/), {CPU_CONFIG} configuration (d768 L12 H12 ffn3072 "
+            f"V50304), {batch}x{seq} tokens per step, {steps} timed steps, all host cores")
 
 
 def run_reference_arm(args):
+    """The CPU arm: rank 0 times the restated reference model on the host cores; other ranks leave at once."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 6))
-    warmup = max(1, min(args.warmup, 2))
-    t, cores, cfg, sb, ss = cpu_reference_step_time(args.config, steps, warmup)
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
+    t, cores, cfg, sb, ss = cpu_reference_step_time(steps, warmup)
     tok_s = sb * ss / t
-    sample = f"{args.config} model, {sb}x{ss} tokens per step, {steps} timed steps (bounded sample of the workload)"
+    sample = _cpu_sample_text(sb, ss, steps)
     line = {
         "impl": "reference", "metric": METRIC, "value": tok_s, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": steps, "warmup": warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{args.config} fwd+bwd, CPU fp32 restatement of the reference model", "sample": sample},
+        "config": {"workload": f"{CPU_CONFIG} GPT fwd+bwd on the host cores: d{cfg.hidden_size} "
+                               f"L{cfg.num_hidden_layers} H{cfg.num_attention_heads} ffn{cfg.ffn_dim} V{cfg.vocab_size} "
+                               f"ctx{ss} batch{sb} (the 410M step of the GPU arm does not finish in minutes on a CPU)",
+                   "global_batch": sb, "seq_len": ss, "parallelism": "cpu"},
         "tflops": algorithmic_flops(cfg, sb, ss) / t / 1e12,
         "cpu_baseline": {"value": tok_s, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -205,6 +222,13 @@ def run_b200_arm(args):
     n_params = sum(p.numel() for p in model.parameters())
     buckets = GradBuckets(model.parameters(), column_blocks=model.projection_weight_groups())
     loss_scale = 4096.0 if dtype is torch.float16 else 1.0
+    optimizer = scaler = None
+    if args.optimizer:
+        # the step that follows forward+backward in a training loop: loss scale, inf/nan check, AdamW with fp32
+        # master weights on the reduced buckets, all on the device (captured in the graph with the rest)
+        from tritonformer_b200.optim import FusedAdamW, LossScaler
+        scaler = LossScaler(dev, init_scale=loss_scale)
+        optimizer = FusedAdamW(buckets, lr=1e-5, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, scaler=scaler)
 
     gen = torch.Generator().manual_seed(1234 + rank)
     host_tokens = [torch.randint(0, cfg.vocab_size, (B, T), generator=gen).pin_memory() for _ in range(4)]
@@ -223,7 +247,7 @@ def run_b200_arm(args):
 
     zero_stream = torch.cuda.Stream()
 
-    def step(ids):
+    def step(ids, marks=None):
         # the gradient buckets are cleared on a side stream while the forward pass runs (nothing reads them
         # before backward), then the weight-gradient GEMMs add into the bucket views themselves
         main = torch.cuda.current_stream()
@@ -234,9 +258,17 @@ def run_b200_arm(args):
             with torch.autocast("cuda", dtype=dtype):
                 _, loss = model(ids, ids)
             main.wait_stream(zero_stream)
-            (loss * loss_scale).backward()
+            (loss * (scaler.scale if scaler is not None else loss_scale)).backward()
+        if marks is not None:  # last backward kernel enqueued ...
+            marks.append(torch.cuda.Event(enable_timing=True))
+            marks[-1].record()
         if reducer is not None:
             reducer.finish()
+        if marks is not None:  # ... and the stream has joined the collectives
+            marks.append(torch.cuda.Event(enable_timing=True))
+            marks[-1].record()
+        if optimizer is not None and (reducer is not None or world == 1):
+            optimizer.step()
         return loss.detach()
 
     # eager warm-up (also fills every per-shape cache before graph capture)
@@ -269,6 +301,8 @@ def run_b200_arm(args):
             static_loss.copy_(step(static_ids))
         if reducer is None:
             buckets.all_reduce_mean()
+            if optimizer is not None and world > 1:
+                optimizer.step()
 
     def barrier():
         if world > 1:
@@ -308,54 +342,98 @@ def run_b200_arm(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_ms = t.tolist()
 
-    # dominant kernel family (the GEMMs), timed live on the launching stream: inside an eager step with CUDA
-    # events around every call (the reported figure), and recorded and replayed back to back (same shapes,
-    # strides and epilogues, scratch operands) inside a CUDA graph
-    roof = None
+    # N > 1: how much of the gradient all-reduce is NOT hidden behind backward: a few eager steps on every rank
+    # with an event after the last backward kernel and one after the stream has joined the collectives
+    exposed_ms = None
+    if reducer is not None:
+        gaps = []
+        for _ in range(5):
+            marks = []
+            step(static_ids, marks)
+            torch.cuda.synchronize()
+            gaps.append(marks[0].elapsed_time(marks[1]))
+        t = torch.tensor([statistics.median(gaps[1:])], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        exposed_ms = float(t.item())
+
+    # The two tensor-core kernel families, timed live on the launching stream inside eager steps: a CUDA event
+    # before and after every GEMM call and every attention call, on the step's own operands, with the SM clock
+    # sampled meanwhile.  Beside it, the GEMM calls recorded (shape, strides, epilogue) and replayed back to back
+    # on dense random operands inside a CUDA graph, under its own clock samples.
+    roof = roof_attn = None
     if rank == 0:
+        from tritonformer_b200 import attention as tattn
         peaks = measured_peaks()
         recs = []
         tlinear.PROFILE = recs
         if reducer is not None:
-            reducer.enabled = False  # this step runs on rank 0 only: no collectives
+            reducer.enabled = False  # these steps run on rank 0 only: no collectives
         step(static_ids)
-        if reducer is not None:
-            reducer.enabled = True
         tlinear.PROFILE = None
         torch.cuda.synchronize()
         gflop = sum(2.0 * r["m"] * r["n"] * r["k"] for r in recs)
-        # the same kernels inside the step itself, on the step's own operands: every GEMM call of an eager
-        # step bracketed by CUDA events on its stream (the second of two such steps counts)
-        in_step_s = None
-        for _ in range(2):
-            tlinear.TIMING = []
-            if reducer is not None:
-                reducer.enabled = False
+        smp = ClockSampler(local)
+        smp.start()
+        gemm_s, fwd_s, bwd_s, aflop = [], [], [], [0.0, 0.0]
+        for _ in range(12):
+            tlinear.TIMING, tattn.TIMING = [], []
             step(static_ids)
-            if reducer is not None:
-                reducer.enabled = True
-            marks, tlinear.TIMING = tlinear.TIMING, None
+            gm, am = tlinear.TIMING, tattn.TIMING
+            tlinear.TIMING = tattn.TIMING = None
             torch.cuda.synchronize()
-            in_step_s = sum(a.elapsed_time(b) for a, b, _ in marks) * 1e-3
-        g_s = _time_cuda(lambda: tlinear.replay(recs, dev), 3, 1)
+            gemm_s.append(sum(a.elapsed_time(b) for a, b, _ in gm) * 1e-3)
+            fwd_s.append(sum(a.elapsed_time(b) for a, b, k, _ in am if k == "fwd") * 1e-3)
+            bwd_s.append(sum(a.elapsed_time(b) for a, b, k, _ in am if k == "bwd") * 1e-3)
+            aflop = [sum(f for _, _, k, f in am if k == "fwd"), sum(f for _, _, k, f in am if k == "bwd")]
+            n_attn = len(am)
+        clk_step = smp.stop()
+        if reducer is not None:
+            reducer.enabled = True
+        in_step_s, fwd_t, bwd_t = (statistics.median(x[2:]) for x in (gemm_s, fwd_s, bwd_s))
+        smp = ClockSampler(local)
+        smp.start()
+        g_s = _time_cuda(lambda: tlinear.replay(recs, dev), 20, 2)
+        clk_replay = smp.stop()
         achieved = gflop / in_step_s / 1e12
+        mhz = lambda c: c.get("sm_mhz") if c else None
+        # one launch of the dominant kernel under ncu (profiles/ncu_gemm_tc05.md): the forward product of the first
+        # MLP linear, M8192 N4096 K1024 fp16.  DRAM read 25.29 MB = X (16.8 MB) + W (8.4 MB) once; 18.76 MB of the
+        # 67.1 MB output had been written back when the kernel ended (the rest was still in the L2).
+        traffic = {"launch": "gemm_pair_tc05_kernel, forward fc1 M8192 N4096 K1024 fp16 (profiles/ncu_gemm_tc05.md)",
+                   "dram_bytes_read": 25.29e6, "dram_bytes_written": 18.76e6,
+                   "algorithmic_bytes_read": 2.0 * (8192 * 1024 + 1024 * 4096),
+                   "algorithmic_bytes_written": 2.0 * 8192 * 4096}
         roof = {"bound": "tensor",
                 "kernel": "gemm_pair_tc05_kernel + gemm_tc05_kernel (all linear fwd/dX/dW products of one step)",
                 "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
-                "traffic": None, "launches": len(recs), "tcgen05_launches": sum(1 for r in recs if r["path"] == 1),
+                "traffic": traffic["dram_bytes_read"] + traffic["dram_bytes_written"], "traffic_detail": traffic,
+                "launches": len(recs), "tcgen05_launches": sum(1 for r in recs if r["path"] == 1),
                 "peak_source": peaks["source"] + " sustained bf16 cuBLAS", "gemm_ms_per_step": in_step_s * 1e3,
-                "flops_per_step": gflop,
-                "how": "CUDA events around every GEMM call of one eager step, on the step's own operands",
+                "flops_per_step": gflop, "sm_mhz": mhz(clk_step),
+                "ms_x_ghz": in_step_s * 1e3 * (mhz(clk_step) or 0) * 1e-3,
+                "how": "CUDA events around every GEMM call of eager steps (median of 10), on the step's own operands",
                 # the same calls back to back on dense random operands inside a CUDA graph: the kernels alone in
-                # the power-capped regime, where they run slower than between the other kernels of the step
+                # the power-capped regime; ms_x_ghz (time x median SM clock, i.e. giga-cycles) separates what the
+                # lower clock costs from what the operands cost
                 "replay": {"gemm_ms_per_step": g_s * 1e3, "achieved": gflop / g_s / 1e12,
-                           "frac": gflop / g_s / 1e12 / peaks["tflops"]}}
+                           "frac": gflop / g_s / 1e12 / peaks["tflops"], "sm_mhz": mhz(clk_replay),
+                           "ms_x_ghz": g_s * 1e3 * (mhz(clk_replay) or 0) * 1e-3}}
+        a_ach = (aflop[0] + aflop[1]) / (fwd_t + bwd_t) / 1e12
+        roof_attn = {"bound": "tensor",
+                     "kernel": "attn_fwd1_tc05_kernel + attn_bwd_tc05_kernel (+ delta pre-pass, dQ conversion)",
+                     "achieved": a_ach, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": a_ach / peaks["tflops"],
+                     "traffic": None, "calls": n_attn, "fwd_ms_per_step": fwd_t * 1e3, "bwd_ms_per_step": bwd_t * 1e3,
+                     "fwd_tflops": aflop[0] / fwd_t / 1e12, "bwd_tflops": aflop[1] / bwd_t / 1e12,
+                     "flops_per_step": aflop[0] + aflop[1], "sm_mhz": mhz(clk_step),
+                     "peak_source": peaks["source"] + " sustained bf16 cuBLAS",
+                     "how": "CUDA events around every attention call of eager steps (median of 10); causal FLOPs "
+                            "(2 products forward, 5 backward, half of the square)"}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        t_cpu, cores, _, sb, ss = cpu_reference_step_time(args.config, 2, 1)
+        t_cpu, cores, _, sb, ss = cpu_reference_step_time(3, 1)
         cpu = {"value": sb * ss / t_cpu, "unit": "tokens/s", "cores": cores, "kind": "port",
-               "sample": f"{args.config} model, {sb}x{ss} tokens per step, 2 timed steps, fp32 oracle on host cores"}
+               "sample": _cpu_sample_text(sb, ss, 3), "ms_per_step": t_cpu * 1e3}
 
     if rank == 0:
         flops = algorithmic_flops(cfg, B, T)
@@ -370,6 +448,8 @@ def run_b200_arm(args):
                                    f"H{cfg.num_attention_heads} ffn{cfg.ffn_dim} V{cfg.vocab_size} ctx{T} batch{B}/GPU",
                        "global_batch": world * B, "seq_len": T, "parallelism": f"dp{world}",
                        "cuda_graph": graph is not None, "loss_scale": loss_scale,
+                       "optimizer": ("fused AdamW, fp32 master weights, dynamic loss scale (in the timed step)"
+                                     if optimizer is not None else None),
                        "allreduce": ("overlapped with backward" if reducer is not None else "after backward")
                        if world > 1 else None,
                        "l2": "working set per step (>= 0.8 GB of weights plus activations) exceeds the 126 MB L2"},
@@ -385,6 +465,8 @@ def run_b200_arm(args):
             "gpu_launches": int(launches_per_step * args.steps),
             "launches_per_step": int(launches_per_step),
             "roofline": roof,
+            "roofline_attention": roof_attn,
+            "allreduce_exposed_ms": exposed_ms,
             "cpu_baseline": cpu,
             "device_status": L.device_status(),
         }
@@ -555,6 +637,21 @@ def run_kernel_bench(args):
             emit("embed_index + embed_clear + embed_bwd_scatter + embed_bwd_fold", case,
                  _time_cuda(lambda: EMB.embedding_backward(ids, dout, dtok, dpos), iters, warmup),
                  6.0 * bsz * t * d, "GB/s", "hbm")
+    if which in ("adam", "all"):
+        n = (64 if args.small else 256) * (1 << 20)  # elements: 28 B each across the five arrays, far beyond the L2
+        g = (torch.randn(n, device=dev) * 64.0).half()
+        p16 = torch.randn(n, device=dev).half()
+        w, m, v = p16.float(), torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+        state = torch.tensor([64.0, 1.0 / 64.0, 0.0, 0.0], device=dev)
+        found = torch.zeros(1, device=dev, dtype=torch.int32)
+        st = lambda: L.stream_ptr(dev)
+        chk = lambda: L.check(L.lib.tfb_grad_check(g.data_ptr(), n, 0, found.data_ptr(), st()))
+        emit("grad_check_kernel", f"{n} gradients fp16", _time_cuda(chk, iters, warmup), 2.0 * n, "GB/s", "hbm")
+        upd = lambda: L.check(L.lib.tfb_adamw_step(g.data_ptr(), p16.data_ptr(), w.data_ptr(), m.data_ptr(), v.data_ptr(), n,
+                                                   0, state[1:2].data_ptr(), found.data_ptr(), state[3:4].data_ptr(), 1e-4,
+                                                   0.9, 0.95, 1e-8, 0.1, st()))
+        emit("adamw_step_kernel", f"{n} parameters fp16 + fp32 master, m, v", _time_cuda(upd, iters, warmup), 28.0 * n,
+             "GB/s", "hbm")
     assert L.device_status() == 0
     return out
 
@@ -571,8 +668,10 @@ def main():
     ap.add_argument("--no-overlap", action="store_true",
                     help="N > 1: all-reduce the gradient buckets after the step instead of during backward")
     ap.add_argument("--kernel", default=None,
-                    choices=["all", "gemm", "attn", "layernorm", "crossentropy", "softmax", "relu", "embed"],
+                    choices=["all", "gemm", "attn", "layernorm", "crossentropy", "softmax", "relu", "embed", "adam"],
                     help="run the isolated-kernel micro-benchmarks instead of the model step")
+    ap.add_argument("--optimizer", action="store_true",
+                    help="add the fused AdamW step (fp32 master weights, dynamic loss scale) to the timed step")
     ap.add_argument("--small", action="store_true", help="with --kernel: one small case, one launch (for ncu captures)")
     args = ap.parse_args()
     if args.kernel:

@@ -250,6 +250,30 @@ int tfb_attention_bwd(const void* q, const void* k, const void* v, const void* o
                       void* scratch, int64_t scratch_bytes,
                       int dtype, void* stream, int* path);
 
+/* ------------------------------------------------------------------- optimizer step
+ * No counterpart in the reference, which ships no optimizer (its README trains with one, README.md:89-113):
+ * the step that follows forward+backward in a training loop, on the flat 16-bit gradient buckets the
+ * weight-gradient products write into.  Everything is decided on the device; nothing reads back to the host.
+ *
+ * tfb_grad_check: sets *found_inf to 1 if any of the n gradients is inf or nan (leaves it alone otherwise).   */
+int tfb_grad_check(const void* grad, int64_t n, int dtype, int* found_inf, void* stream);
+/* tfb_adamw_step: AdamW on n elements with fp32 master weights (torch.optim.AdamW's arithmetic, operation by
+ * operation): g = grad * *inv_scale; master *= 1 - lr*weight_decay; exp_avg, exp_avg_sq updated; master -=
+ * lr / (1 - beta1^t) * exp_avg / (sqrt(exp_avg_sq) / sqrt(1 - beta2^t) + eps) with t = *steps_taken + 1;
+ * param = master rounded to the 16-bit dtype.  Does nothing at all while *found_inf != 0 (step skipped).
+ * inv_scale, found_inf, steps_taken are device pointers and may be NULL (1, 0, 0).  beta1 > 0.5.  The
+ * hyper-parameters are doubles, like the Python floats of torch.optim.AdamW, and rounded to fp32 once.       */
+int tfb_adamw_step(const void* grad, void* param, float* master, float* exp_avg, float* exp_avg_sq,
+                   int64_t n, int dtype, const float* inv_scale, const int* found_inf,
+                   const float* steps_taken, double lr, double beta1, double beta2, double eps,
+                   double weight_decay, void* stream);
+/* tfb_loss_scale_update: after the step kernels of every bucket.  state4 (device) = {loss scale, 1 / scale,
+ * good steps since the scale last changed, optimizer steps taken}.  If *found_inf: scale *= backoff, the
+ * good-step count restarts; else the step counter advances and after `interval` good steps scale *= growth
+ * (torch.amp.GradScaler.update's rule).  Clears *found_inf.                                                 */
+int tfb_loss_scale_update(float* state4, int* found_inf, float growth, float backoff, int interval,
+                          void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -8,11 +8,27 @@ x @ W (tritonformer/nn.py:45-86).  Submodule and parameter names equal the refer
 state dicts are interchangeable.
 """
 import math
+from dataclasses import dataclass
 
 import torch
 import torch.nn as nn
 
 from . import ops
+
+
+@dataclass(frozen=True)
+class OracleConfig:
+    """The fields of the reference's TransformerConfig (transformer.py:24-34), for callers that must not load
+    the product package (the CPU baseline of the benchmark)."""
+    vocab_size: int
+    hidden_size: int
+    max_position_embeddings: int
+    num_attention_heads: int
+    head_dim: int
+    ffn_dim: int
+    num_hidden_layers: int
+    use_linear_bias: bool
+    attn_bias: bool
 
 
 class _Linear(nn.Module):

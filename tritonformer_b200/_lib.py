@@ -44,6 +44,9 @@ _SIGNATURES = {
     "tfb_embedding_fwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
     "tfb_embedding_bwd_scratch_bytes": (_i64, [_i64] * 4),
     "tfb_embedding_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
+    "tfb_grad_check": (_i32, [_vp, _i64, _i32, _vp, _vp]),
+    "tfb_adamw_step": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _vp, _vp, _vp] + [_c.c_double] * 5 + [_vp]),
+    "tfb_loss_scale_update": (_i32, [_vp, _vp, _f32, _f32, _i32, _vp]),
     "tfb_gemm": (_i32, [_vp, _vp, _vp, _vp] + [_i64] * 8 + [_i32, _i32, _i32, _vp, _pi32]),
     "tfb_gemm_workspace_bytes": (_i64, []),
     "tfb_gemm_fused": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64] + [_i64] * 8 + [_i32, _i32, _vp, _i64, _vp, _pi32]),

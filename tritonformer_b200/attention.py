@@ -17,6 +17,23 @@ from . import _lib
 from ._amp import amp_backward, amp_forward
 
 
+# When set to a list, every attention forward / backward call is bracketed by two CUDA events on its stream and
+# appends (start, end, "fwd" | "bwd", flops): the benchmark sums the elapsed times of an eager step.
+TIMING = None
+
+
+def _timed(kind, shape, call):
+    if TIMING is None:
+        return call()
+    b, h, t, hd = shape
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    out = call()
+    e1.record()
+    TIMING.append((e0, e1, kind, (2.0 if kind == "fwd" else 5.0) * b * h * t * t * hd))  # causal: half of 4 / 10
+    return out
+
+
 def _check_qkv(q, k, v):
     assert q.is_cuda and q.dim() == 4, "attention expects (B, H, T, head_dim) CUDA tensors"
     assert q.shape == k.shape == v.shape, "q, k, v must have the same shape"
@@ -91,13 +108,13 @@ def attention_forward(q, k, v, bias: _Bias):
     lse = torch.empty((b, h, t), device=q.device, dtype=torch.float32)
     path = ctypes.c_int(0)
     tab = bias.table
-    _lib.check(_lib.lib.tfb_attention_fwd(
+    _timed("fwd", q.shape, lambda: _lib.check(_lib.lib.tfb_attention_fwd(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), b, h, t, hd,
         _lib.strides3(q), _lib.strides3(k), _lib.strides3(v), _lib.strides3(out),
         bias.slopes.data_ptr() if bias.slopes is not None else None, int(bias.rounded),
         tab.data_ptr() if tab is not None else None,
         tab.stride(0) if tab is not None else 0, tab.stride(1) if tab is not None else 0,
-        _lib.dtype_code(q.dtype), _lib.stream_ptr(q.device), ctypes.byref(path)))
+        _lib.dtype_code(q.dtype), _lib.stream_ptr(q.device), ctypes.byref(path))))
     return out, lse, (q, k, v)
 
 
@@ -125,7 +142,7 @@ def attention_backward(d_out, out, q, k, v, lse, bias: _Bias):
     scratch = torch.empty((nbytes,), device=q.device, dtype=torch.uint8)
     path = ctypes.c_int(0)
     tab = bias.table
-    _lib.check(_lib.lib.tfb_attention_bwd(
+    _timed("bwd", q.shape, lambda: _lib.check(_lib.lib.tfb_attention_bwd(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), d_out.data_ptr(), lse.data_ptr(),
         dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), b, h, t, hd,
         _lib.strides3(q), _lib.strides3(k), _lib.strides3(v), _lib.strides3(out), _lib.strides3(d_out),
@@ -134,7 +151,7 @@ def attention_backward(d_out, out, q, k, v, lse, bias: _Bias):
         tab.data_ptr() if tab is not None else None,
         tab.stride(0) if tab is not None else 0, tab.stride(1) if tab is not None else 0,
         scratch.data_ptr(), nbytes, _lib.dtype_code(q.dtype), _lib.stream_ptr(q.device),
-        ctypes.byref(path)))
+        ctypes.byref(path))))
     return dq, dk, dv
 
 
