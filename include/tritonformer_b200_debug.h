@@ -13,14 +13,16 @@ extern "C" {
 /* Test and tuning switches.
  *   key 0: value 1 sends every GEMM to the generic-stride kernel.
  *   key 1: value 1 sends every attention call to the mma.sync kernels.
- *   key 2: attention: bit 0 skips the dQ accumulation, bit 1 turns the cycle counters on, bit 4 (16)
- *          selects the two-query-tiles-per-CTA forward kernel for head_dim 64.
+ *   key 2: attention: bit 0 skips the dQ accumulation, bit 1 turns the cycle counters on, bit 5 (32) walks the
+ *          (tile, batch*head) items slice by slice instead of longest first, bit 6 (64) adds dQ with vector
+ *          atomics instead of the TMA reduction, bit 7 (128) keeps only the barriers of the backward's compute
+ *          warps going (timing experiments: results are then meaningless).
  *   key 3: value 1 launches every kernel fully serialised (no programmatic dependent launch: a
  *          kernel's set-up no longer overlaps its predecessor's tail).
  *   key 4: GEMM: bit 0 whole tiles only (no sharing of a tile's contraction between SMs), bit 5 (32)
  *          no CTA-pair kernel, bit 6 (64) per-CTA timeline counters of the CTA-pair kernel.
- *   key 5: which counters tfb_debug_counters returns: -1 attention backward, -2 / -3 attention forward
- *          (head_dim 64, two-tile / one-tile kernel), n >= 0 the CTA-pair GEMM timeline of CTA n.
+ *   key 5: which counters tfb_debug_counters returns: -1 attention backward, -3 attention forward,
+ *          n >= 0 the CTA-pair GEMM timeline of CTA n.
  *   key 6: how many SMs the persistent GEMM grids leave free (for a collective that runs beside
  *          them on another stream); 0 by default.                                */
 void tfb_debug_set(int key, int value);

@@ -141,10 +141,10 @@ def test_reference_asserts_are_kept():
 
 @pytest.mark.parametrize("dims", [(2, 4, 2048, 64), (1, 5, 640, 64), (2, 16, 512, 64), (1, 3, 1024, 128)])
 @pytest.mark.parametrize("alibi", [False, True])
-def test_both_generations_of_forward_kernels_agree(dims, alibi):
-    """The tcgen05 forward has two generations of kernels: one query tile per CTA with doubled score buffers and
-    P in tensor memory (the default), and the earlier ones selected by a switch (two query tiles per CTA at
-    head_dim 64, P through shared memory at 128).  Both must match the oracle and each other."""
+def test_forward_is_independent_of_the_order_of_its_items(dims, alibi):
+    """The forward kernel's persistent CTAs walk (query tile, batch*head) items longest walk first; a switch makes
+    them walk slice by slice instead.  The arithmetic of an item does not depend on which CTA runs it or when, so
+    both orders give the same bits; output and log-sum-exp match the oracle."""
     from tritonformer_b200 import _lib
     from tritonformer_b200.attention import _Bias, attention_forward
     b, nh, sq, hd = dims
@@ -153,24 +153,28 @@ def test_both_generations_of_forward_kernels_agree(dims, alibi):
     slopes = torch.tensor([2.0 ** (-8.0 * (i + 1) / nh) for i in range(nh)], device="cuda") if alibi else None
     bias = _Bias(slopes=slopes)
     out1, lse1, _ = attention_forward(q, k, v, bias)
-    _lib.lib.tfb_debug_set(2, 16)
+    _lib.lib.tfb_debug_set(2, 32)
     try:
         out2, lse2, _ = attention_forward(q, k, v, bias)
     finally:
         _lib.lib.tfb_debug_set(2, 0)
     torch.cuda.synchronize()
     assert _lib.lib.tfb_device_status(0) == 0
+    assert torch.equal(out1, out2) and torch.equal(lse1, lse2)
     bias_f32 = None
     if alibi:
         pos = torch.arange(sq, device="cuda")
         dist = (pos.view(sq, 1) - pos.view(1, sq)).clamp(min=0).float()
         bias_f32 = -dist.view(1, sq, sq) * slopes.view(nh, 1, 1)
     ref = ops.attention(q.float(), k.float(), v.float(), bias_f32)
-    for out in (out1, out2):
-        assert_close(out, ref, 1e-2, "out")
-        assert norm_rel(out, ref) < 2e-3
-    assert_close(out1, out2, 4e-3, "kernels")
-    assert_close(lse1, lse2, 2e-3, "lse")
+    assert_close(out1, ref, 1e-2, "out")
+    assert norm_rel(out1, ref) < 2e-3
+    scores = torch.einsum("bhid,bhjd->bhij", q.float(), k.float()) / hd ** 0.5
+    if bias_f32 is not None:
+        scores = scores + bias_f32
+    causal = torch.ones((sq, sq), dtype=torch.bool, device="cuda").tril()
+    lse_ref = torch.logsumexp(scores.masked_fill(~causal, float("-inf")), dim=-1)
+    assert_close(lse1, lse_ref, 2e-3, "lse")
 
 
 def test_alibi_finding_is_tied_to_the_tensor_object():

@@ -5,8 +5,6 @@ namespace tfb {
 extern std::atomic<int> g_force_fallback_attn;
 extern std::atomic<int> g_attn_debug;
 bool attn_tc05_fwd_eligible(const AttnArgs& a, int hd);
-int attn_tc05_fwd(const AttnArgs& a, int hd, int dtype, cudaStream_t st);
-int attn_fwd2_tc05(const AttnArgs& a, int dtype, cudaStream_t st);
 int attn_fwd1_tc05(const AttnArgs& a, int hd, int dtype, cudaStream_t st);
 bool attn_tc05_bwd_eligible(const AttnArgs& a, int hd);
 int attn_tc05_bwd(const AttnArgs& a, int hd, int dtype, cudaStream_t st);
@@ -53,11 +51,7 @@ extern "C" int tfb_attention_fwd(const void* q, const void* k, const void* v, vo
   a.slopes = slopes; a.bias = bias; a.bias_sh = bias_sh; a.bias_si = bias_si;
   const bool fast = !g_force_fallback_attn.load() && attn_tc05_fwd_eligible(a, (int)hd);
   if (path) *path = fast ? 1 : 0;
-  if (fast && !(g_attn_debug.load() & 16))  // one query tile per CTA with doubled score buffers
-    return attn_fwd1_tc05(a, (int)hd, dtype, (cudaStream_t)stream);
-  // tfb_debug_set(2, 16): the earlier kernels (two query tiles per CTA at head_dim 64, P through shared memory at 128)
-  if (fast && hd == 64) return attn_fwd2_tc05(a, dtype, (cudaStream_t)stream);
-  if (fast) return attn_tc05_fwd(a, (int)hd, dtype, (cudaStream_t)stream);
+  if (fast) return attn_fwd1_tc05(a, (int)hd, dtype, (cudaStream_t)stream);
   return attn_generic_fwd(a, (int)hd, dtype, (cudaStream_t)stream);
 }
 

@@ -105,6 +105,40 @@ __device__ __forceinline__ float ex2_fma1(float x) {
   return __int_as_float(__float_as_int(q) + (__float_as_int(xr) << 23));
 }
 
+// Two fp32 values in one 64-bit register pair and the packed FMA that works on both (sm_100): half the
+// instructions for the scale-and-shift of the scores, the polynomial of the FMA-pipe exponentials and the row sums.
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+// 2^x for a pair on the FMA pipe (the polynomial of ex2_fma1, packed)
+__device__ __forceinline__ void ex2_fma2(uint64_t xp, float& r0, float& r1) {
+  float x0, x1;
+  f2_unpack(xp, x0, x1);
+  const uint64_t x = f2_pack(fmaxf(x0, -125.f), fmaxf(x1, -125.f));
+  const uint64_t one = f2_pack(1.f, 1.f);
+  const uint64_t xr = f2_fma(x, one, f2_pack(12582912.f, 12582912.f));
+  const uint64_t fr = f2_fma(xr, one, f2_pack(-12582912.f, -12582912.f));
+  const uint64_t f = f2_fma(fr, f2_pack(-1.f, -1.f), x);
+  uint64_t q = f2_fma(f, f2_pack(0.0551716685f, 0.0551716685f), f2_pack(0.2426111251f, 0.2426111251f));
+  q = f2_fma(q, f, f2_pack(0.6932609677f, 0.6932609677f));
+  q = f2_fma(q, f, f2_pack(0.9999280572f, 0.9999280572f));
+  float q0, q1, xr0, xr1;
+  f2_unpack(q, q0, q1);
+  f2_unpack(xr, xr0, xr1);
+  r0 = __int_as_float(__float_as_int(q0) + (__float_as_int(xr0) << 23));
+  r1 = __int_as_float(__float_as_int(q1) + (__float_as_int(xr1) << 23));
+}
+
 // The n-th item of this CTA: query tile and batch*head slice.  Items are numbered longest walk first across
 // the slices of a group (groups keep the K and V that are live at one time within the L2); round n of the
 // deal goes over the CTAs forwards when n is even and backwards when it is odd.  False past the last item
@@ -362,13 +396,51 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
     const bool prof = (p.debug & 2) && warp == 2 && lane == 0;
     if (prof) atomicAdd(&g_prof_f1[7], (unsigned long long)(clock64() - t_entry));
     int g0 = 0;  // steps of the CTA before this item
+    // Normalisation and store of a finished tile, run one step late: after the first (diagonal) step of the NEXT
+    // item, whose scores are already there, so that the wait for the tile's last P·V is hidden behind that step.
+    bool pend = false;
+    int pend_glast = 0, pend_buf = 0;
+    float pend_l = 1.f, pend_m = 0.f;
+    T* pend_row = nullptr;
+    float* pend_lse = nullptr;
+    auto finish_pending = [&]() {
+      if (!pend) return;
+      pend = false;
+      const long long f0 = clock64();
+      if (ok) ok = mbar_wait(&pv_done[pend_glast & 1], (pend_glast >> 1) & 1, 0x5900, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        const float inv = 1.f / pend_l;
+        const uint32_t o_addr = lane_addr + F1_COL_O + pend_buf * HD;
+        uint32_t v[F1_OW / 32][32];
+#pragma unroll
+        for (int cc = 0; cc < F1_OW / 32; ++cc) tmem_ld32(o_addr + ch * F1_OW + cc * 32, v[cc]);
+        tc_wait_ld();
+        // the accumulator has been read out: the first product of a later item may overwrite it
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&o_free[pend_buf]);
+#pragma unroll
+        for (int cc = 0; cc < F1_OW / 32; ++cc) {  // each warp of the row writes its share of the columns
+#pragma unroll
+          for (int v4 = 0; v4 < 4; ++v4) {
+            float o8[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o8[e] = __uint_as_float(v[cc][v4 * 8 + e]) * inv;
+            *reinterpret_cast<uint4*>(pend_row + cc * 32 + v4 * 8) = pack8<T>(o8);
+          }
+        }
+        if (ch == 0) *pend_lse = (pend_m + log2f(pend_l)) * kLn2_1;
+      }
+      if (prof) atomicAdd(&g_prof_f1[11], (unsigned long long)(clock64() - f0));
+    };
     for (int n = 0; ok; ++n) {
       int qt, bh;
       if (!f1_item(p, n, qt, bh)) break;
       const int b = bh / p.H, h = bh % p.H;
       const int jlast = qt;               // last key tile this query tile attends to
       const int i = qt * F1_TILE + r;     // query
-      const uint32_t o_addr = lane_addr + F1_COL_O + (n % NOBUF) * HD;
+      const uint32_t o_addr = lane_addr + F1_COL_O + (n % NOBUF) * HD;  // this item's accumulator (rescales)
       const AlibiLog2<BIAS> alibi(BIAS ? p.slopes[h] : 0.f);
       float m_run = -INFINITY;   // true running maximum of the row (both halves)
       float m_used = -INFINITY;  // maximum the accumulator and the running sums are expressed against
@@ -395,8 +467,9 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
           // at most this thread's partial row sum, so while that stays below 2^8 the 16-bit range holds;
           // otherwise (rare) the step is redone in two passes with a fresh maximum.  The two warps of a
           // row pair exchange the verdict.
-          float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+          uint64_t ls2[2] = {0ull, 0ull};  // four partial row sums in two register pairs
           const float neg_m = -m_used;
+          const uint64_t c2p = f2_pack(c2, c2), negmp = f2_pack(neg_m, neg_m), onep = f2_pack(1.f, 1.f);
           uint32_t buf[2][32];
           tmem_ld32(s_addr, buf[0]);
 #pragma unroll
@@ -405,24 +478,35 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
             if (c + 1 < F1_NC) tmem_ld32(s_addr + (c + 1) * 32, buf[(c + 1) & 1]);
             const uint32_t* v = buf[c & 1];
             const float d0 = (float)(i - (kbase + c * 32));  // distance of the chunk's first key
-            float e_[32];
-#pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              const float x = alibi.sub_from(fmaf(__uint_as_float(v[e]), c2, neg_m), d0 - (float)e);
-              e_[e] = (e & 3) == 3 ? ex2_fma1(x) : ex2_mufu(x);  // one exponential in four on the FMA pipe
-            }
-#pragma unroll
-            for (int e = 0; e < 32; ++e) ls4[e & 3] += e_[e];
             uint32_t pk[16];
 #pragma unroll
-            for (int e = 0; e < 16; ++e) {
-              const typename Num<T>::T2 h2 = Num<T>::from_f2(e_[2 * e], e_[2 * e + 1]);
-              pk[e] = *reinterpret_cast<const uint32_t*>(&h2);
+            for (int e2 = 0; e2 < 16; ++e2) {  // pairs of keys
+              uint64_t xp = f2_fma(f2_pack(__uint_as_float(v[2 * e2]), __uint_as_float(v[2 * e2 + 1])), c2p, negmp);
+              float p0, p1;
+              if (BIAS) {
+                float x0, x1;
+                f2_unpack(xp, x0, x1);
+                xp = f2_pack(alibi.sub_from(x0, d0 - (float)(2 * e2)), alibi.sub_from(x1, d0 - (float)(2 * e2 + 1)));
+              }
+              if ((e2 & 3) == 3) {  // one pair in four on the FMA pipe
+                ex2_fma2(xp, p0, p1);
+              } else {
+                float x0, x1;
+                f2_unpack(xp, x0, x1);
+                p0 = ex2_mufu(x0);
+                p1 = ex2_mufu(x1);
+              }
+              ls2[e2 & 1] = f2_fma(f2_pack(p0, p1), onep, ls2[e2 & 1]);
+              const typename Num<T>::T2 h2 = Num<T>::from_f2(p0, p1);
+              pk[e2] = *reinterpret_cast<const uint32_t*>(&h2);
             }
             // this P buffer is read by the P·V of two steps ago until that has retired (long ago, normally)
             if (c == 0 && g >= 2 && ok) ok = mbar_wait(&pv_done[bsel], ((g - 2) >> 1) & 1, 0x5a00 | bsel, abort_flag);
             tmem_st16(p_addr + c * 16, pk);
           }
+          float ls4[4];
+          f2_unpack(ls2[0], ls4[0], ls4[1]);
+          f2_unpack(ls2[1], ls4[2], ls4[3]);
           const float part = (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
           float bad = __any_sync(0xffffffffu, !(part <= kSinglePassLimit)) ? 1.f : 0.f;  // also true for inf / nan
           bad = exchange(bad, ok, false);
@@ -476,7 +560,13 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
           // every earlier P·V must have retired before O is rescaled or this P buffer rewritten (the
           // tensor core retires them in order, so the latest one covers the rest; at the first step of an
           // item that is the previous item's last product, which this warp has already waited for)
-          if (g > 0 && ok) ok = mbar_wait(&pv_done[(g - 1) & 1], ((g - 1) >> 1) & 1, 0x5800, abort_flag);
+          // (the first step of an item rescales nothing and only rewrites the P buffer, which the product of two
+          // steps ago read: it does not wait for the previous item's last product, whose tile is still pending)
+          if (t == 0) {
+            if (g >= 2 && ok) ok = mbar_wait(&pv_done[bsel], ((g - 2) >> 1) & 1, 0x5a80 | bsel, abort_flag);
+          } else if (ok) {
+            ok = mbar_wait(&pv_done[(g - 1) & 1], ((g - 1) >> 1) & 1, 0x5800, abort_flag);
+          }
           if (t == 0) {
             m_used = m_run;
           } else {
@@ -554,42 +644,20 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
           if (t == 0) atomicAdd(&g_prof_f1[8], (unsigned long long)(w3 - w0));
           if (t == 1) atomicAdd(&g_prof_f1[9], (unsigned long long)(w3 - w0));
         }
+        if (t == 0) finish_pending();  // the previous item's tile
       }
-      const long long t_loop = clock64();
-      const int glast = g0 + jlast;
+      // the row sum is the sum of the pair's partial sums; the tile itself is finished one step later
+      pend_l = exchange(l_run, ok, true);
+      pend_m = m_used;
+      pend_glast = g0 + jlast;
+      pend_buf = n % NOBUF;
+      pend_row = reinterpret_cast<T*>(p.out) + b * p.so_b + h * p.so_h + (int64_t)i * p.so_t + ch * F1_OW;
+      pend_lse = p.lse + (int64_t)bh * p.T + i;
+      pend = true;
       g0 += jlast + 1;
-      // the row sum is the sum of the pair's partial sums
-      const float l_tot = exchange(l_run, ok, true);
-      if (ok) ok = mbar_wait(&pv_done[glast & 1], (glast >> 1) & 1, 0x5900, abort_flag);
-      if (ok) {
-        tc_fence_after();
-        const float inv = 1.f / l_tot;
-        T* orow = reinterpret_cast<T*>(p.out) + b * p.so_b + h * p.so_h + (int64_t)i * p.so_t + ch * F1_OW;
-        uint32_t v[F1_OW / 32][32];
-#pragma unroll
-        for (int cc = 0; cc < F1_OW / 32; ++cc) tmem_ld32(o_addr + ch * F1_OW + cc * 32, v[cc]);
-        tc_wait_ld();
-        // the accumulator has been read out: the first product of a later item may overwrite it
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&o_free[n % NOBUF]);
-#pragma unroll
-        for (int cc = 0; cc < F1_OW / 32; ++cc) {  // each warp of the row writes its share of the columns
-#pragma unroll
-          for (int v4 = 0; v4 < 4; ++v4) {
-            float o8[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) o8[e] = __uint_as_float(v[cc][v4 * 8 + e]) * inv;
-            *reinterpret_cast<uint4*>(orow + cc * 32 + v4 * 8) = pack8<T>(o8);
-          }
-        }
-        if (ch == 0) p.lse[(int64_t)bh * p.T + i] = (m_used + log2f(l_tot)) * kLn2_1;
-      }
-      if (prof) {
-        atomicAdd(&g_prof_f1[5], 1ull);
-        atomicAdd(&g_prof_f1[11], (unsigned long long)(clock64() - t_loop));
-      }
+      if (prof) atomicAdd(&g_prof_f1[5], 1ull);
     }
+    finish_pending();  // the CTA's last tile
     if (prof) {
       atomicAdd(&g_prof_f1[6], (unsigned long long)(clock64() - t_entry));
       atomicAdd(&g_prof_f1[12], (unsigned long long)(global_ns() - ns_entry));
@@ -666,6 +734,11 @@ static int fwd1_launch(const AttnArgs& a, int dtype, cudaStream_t st) {
   else F1_LAUNCH(4, 3)
 #undef F1_LAUNCH
   return launched("attention_fwd(tcgen05, persistent)");
+}
+
+// The tcgen05 forward takes head_dim 64 / 128, whole 128-query tiles and no dense bias table.
+bool attn_tc05_fwd_eligible(const AttnArgs& a, int hd) {
+  return (hd == 64 || hd == 128) && a.T % 128 == 0 && a.bias_mode != 3;
 }
 
 int attn_fwd1_tc05(const AttnArgs& a, int hd, int dtype, cudaStream_t st) {

@@ -28,7 +28,6 @@ int read_dev_status(int reset);
 int launch_wait_probe(unsigned long long limit_ns, int* waited_ok, cudaStream_t st);
 int attn_bwd_tc05_counters(unsigned long long* out);
 int gemm_pair_counters(int cta, unsigned long long* out);
-int attn_fwd2_tc05_counters(unsigned long long* out);
 int attn_fwd1_tc05_counters(unsigned long long* out);
 std::atomic<int> g_counter_select{-1};
 }  // namespace tfb
@@ -51,7 +50,6 @@ extern "C" int tfb_debug_wait_probe(unsigned long long limit_ns, int* waited_ok,
 
 extern "C" int tfb_debug_counters(unsigned long long* out16) {
   const int sel = g_counter_select.load();
-  if (sel == -2) return attn_fwd2_tc05_counters(out16);
   if (sel == -3) return attn_fwd1_tc05_counters(out16);
   return sel >= 0 ? gemm_pair_counters(sel, out16) : attn_bwd_tc05_counters(out16);
 }

@@ -14,7 +14,7 @@ import torch.distributed as dist
 
 
 class GradBuckets:
-    def __init__(self, params, bucket_bytes: int = 256 << 20, column_blocks=()):
+    def __init__(self, params, bucket_bytes: int = 32 << 20, column_blocks=()):
         """`column_blocks`: tuples of 2-D parameters of one shape (in, d) whose gradients are laid out as the column
         blocks of ONE (in, len * d) matrix inside the bucket (the q/k/v projection weights: their gradients are then
         a single product that accumulates straight into the bucket)."""
@@ -114,7 +114,7 @@ class OverlappedReducer:
     captured in a CUDA graph together with the step.
     """
 
-    def __init__(self, buckets: GradBuckets, stages, group=None, on_collectives=None):
+    def __init__(self, buckets: GradBuckets, stages, group=None, on_collectives=None, high_priority=False):
         """`on_collectives(active)`: called with True when the first collective of a step is enqueued and with
         False from finish(), on the thread that enqueues the kernels; the benchmark uses it to size the GEMM
         grids for the SMs the collectives leave."""
@@ -141,7 +141,9 @@ class OverlappedReducer:
             self.ready_at.append(at)
         self.launched = [False] * len(buckets.buckets)
         self.enabled = True  # set False around a step that only some ranks run (no collectives then)
-        self.side = torch.cuda.Stream() if buckets.buckets and buckets.buckets[0].is_cuda else None
+        # `high_priority`: the collectives' CTAs are placed ahead of waiting compute CTAs whenever an SM frees up
+        self.side = (torch.cuda.Stream(priority=-1 if high_priority else 0)
+                     if buckets.buckets and buckets.buckets[0].is_cuda else None)
         self._handles = [m.register_forward_pre_hook(self._make_pre_hook(i)) for i, m in enumerate(stages)]
 
     def _make_pre_hook(self, i):
