@@ -383,33 +383,43 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
         if (ok && !quiet) {
           tc_fence_after();
           const bool plain = !BIAS && !diag;  // no bias and not the diagonal tile: scale, subtract, 2^x
+          // Four chunks of 8 query columns; the tensor-memory loads of a chunk are issued before the chunk ahead of
+          // it is worked on (two register sets of 8 + 8 values), so only the first load's latency is exposed.
+          // (Requesting a tile's first chunk at the end of the tile before it, ahead of the gradient products whose
+          // burst makes the load wait 850 cycles, was tried: the wait for the next scores at that point cost more
+          // than it saved, 230 against 210 us.)
+          uint32_t sv_[2][8], dv_[2][8];
+          PROF_T(tl0);
+          tmem_ld8(lane_addr + Cfg::COL_S + cq * 32, sv_[0]);
+          tmem_ld8(lane_addr + Cfg::COL_DP + cq * 32, dv_[0]);
 #pragma unroll
-          for (int c = 0; c < 2; ++c) {         // 16-column steps keep the live register set small
-            const int col0 = cq * 32 + c * 16;
+          for (int c = 0; c < 4; ++c) {
+            const int col0 = cq * 32 + c * 8;
             const float d0 = (float)(i0 + col0 - j);  // distance of the chunk's first query to this thread's key
-            uint32_t sv_[16], dv_[16];
-            PROF_T(tl0);
-            tmem_ld16(lane_addr + Cfg::COL_S + col0, sv_);
-            tmem_ld16(lane_addr + Cfg::COL_DP + col0, dv_);
             tc_wait_ld();
-            if (c == 1 && !Cfg::DQ_ALIASED) {  // this warp's share of Sᵀ and dPᵀ is in registers
+            if (c + 1 < 4) {
+              tmem_ld8(lane_addr + Cfg::COL_S + col0 + 8, sv_[(c + 1) & 1]);
+              tmem_ld8(lane_addr + Cfg::COL_DP + col0 + 8, dv_[(c + 1) & 1]);
+            } else if (!Cfg::DQ_ALIASED) {  // this warp's share of Sᵀ and dPᵀ is in registers
               tc_fence_before();
               __syncwarp();
               if (lane == 0) mbar_arrive(s_free);
             }
-            PROF_T(tl1);
-            PROF_ADD(14, tl0, tl1);
+            if (c == 0) {
+              PROF_T(tl1);
+              PROF_ADD(14, tl0, tl1);
+            }
 #pragma unroll
-            for (int e4 = 0; e4 < 4; ++e4) {
-              const float4 l4 = *reinterpret_cast<const float4*>(s_lse2 + c * 16 + e4 * 4);
-              const float4 d4 = *reinterpret_cast<const float4*>(s_delta + c * 16 + e4 * 4);
+            for (int e4 = 0; e4 < 2; ++e4) {
+              const float4 l4 = *reinterpret_cast<const float4*>(s_lse2 + c * 8 + e4 * 4);
+              const float4 d4 = *reinterpret_cast<const float4*>(s_delta + c * 8 + e4 * 4);
               const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
               const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
               float pe[4], de[4];
 #pragma unroll
               for (int k = 0; k < 4; ++k) {
                 const int e = e4 * 4 + k;
-                float x = fmaf(__uint_as_float(sv_[e]), c2, -lv[k]);
+                float x = fmaf(__uint_as_float(sv_[c & 1][e]), c2, -lv[k]);
                 if (plain) {
                   pe[k] = ex2_approx_b(x);
                 } else {
@@ -417,12 +427,12 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
                   x = alibi.sub_from(x, d0 + (float)e);  // a key above the diagonal (negative distance) is masked below
                   pe[k] = (j > i) ? 0.f : ex2_approx_b(x);
                 }
-                de[k] = pe[k] * (__uint_as_float(dv_[e]) - dl[k]);
+                de[k] = pe[k] * (__uint_as_float(dv_[c & 1][e]) - dl[k]);
               }
-              pk[c * 8 + e4 * 2] = pack2<T>(pe[0], pe[1]);
-              pk[c * 8 + e4 * 2 + 1] = pack2<T>(pe[2], pe[3]);
-              dk_[c * 8 + e4 * 2] = pack2<T>(de[0], de[1]);
-              dk_[c * 8 + e4 * 2 + 1] = pack2<T>(de[2], de[3]);
+              pk[c * 4 + e4 * 2] = pack2<T>(pe[0], pe[1]);
+              pk[c * 4 + e4 * 2 + 1] = pack2<T>(pe[2], pe[3]);
+              dk_[c * 4 + e4 * 2] = pack2<T>(de[0], de[1]);
+              dk_[c * 4 + e4 * 2 + 1] = pack2<T>(de[2], de[3]);
             }
           }
           // Pᵀ / dSᵀ of the previous tile are still being read by its gradient products

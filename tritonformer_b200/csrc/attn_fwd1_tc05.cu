@@ -56,7 +56,12 @@ template <int HD> struct F1Cfg {
   static constexpr int TILE_BYTES = PANELS * 16384;      // 128 rows x HD x 2 B
   static constexpr int STAGES = (HD == 64) ? 3 : 2;      // K / V ring depth (shared memory bound at 128)
   static constexpr int OW = HD / F1_NW;                  // accumulator columns per warp (rescale, output)
-  static constexpr int NOBUF = (HD == 64) ? 2 : 1;       // accumulators in tensor memory
+  // head_dim 64: the two softmax warps of a row each own an accumulator for THEIR 64 keys of every step (O_a at
+  // column 384, O_b at 448), with their own reference maximum and row sum, and the two are merged when the tile
+  // is stored; so the warps exchange a value once per item instead of once per step and drift apart freely.
+  // head_dim 128: one accumulator shared by both warps (tensor memory has no room for two).
+  static constexpr bool SPLIT = (HD == 64);
+  static constexpr int NOBUF = 1;                        // accumulator sets in tensor memory
   static constexpr int OFF_Q = 0;                                  // [2]
   static constexpr int OFF_K = 2 * TILE_BYTES;                     // [STAGES]
   static constexpr int OFF_V = OFF_K + STAGES * TILE_BYTES;        // [STAGES]
@@ -64,7 +69,7 @@ template <int HD> struct F1Cfg {
   static constexpr int OFF_BAR = OFF_X + 2 * F1_NW * 128 * 4;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
   static_assert(OW % 32 == 0, "a softmax warp handles whole 32-column chunks of the accumulator");
-  static_assert(F1_COL_O + NOBUF * HD <= 512, "tensor memory");
+  static_assert(F1_COL_O + (SPLIT ? 2 : 1) * HD <= 512, "tensor memory");
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
 };
 constexpr float kRescale1 = 8.0f;  // log2 units
@@ -175,6 +180,7 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
                                                                        const F1Params p) {
   using Cfg = F1Cfg<HD>;
   constexpr int F1_STAGES = Cfg::STAGES, F1_TILE_BYTES = Cfg::TILE_BYTES, F1_OW = Cfg::OW, NOBUF = Cfg::NOBUF;
+  constexpr bool SPLIT = Cfg::SPLIT;
   constexpr int F1_OFF_Q = Cfg::OFF_Q, F1_OFF_K = Cfg::OFF_K, F1_OFF_V = Cfg::OFF_V, F1_OFF_X = Cfg::OFF_X;
   constexpr int F1_OFF_BAR = Cfg::OFF_BAR;
   extern __shared__ uint8_t smem_raw[];
@@ -328,8 +334,12 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
           const uint32_t tp = tb + F1_COL_P + (pg & 1) * 64;
           const uint32_t to = tb + F1_COL_O + (pn % NOBUF) * HD;
 #pragma unroll
-          for (int s = 0; s < F1_TILE / 16; ++s)
-            if (elect_one()) tc_mma_ts(to, tp + s * 8, desc_advance(dv, s * 2048), idesc_o, (pj | s) ? 1u : 0u);
+          for (int s = 0; s < F1_TILE / 16; ++s) {
+            // split accumulators: keys 0-63 of the step (k-steps 0-3) go to O_a, keys 64-127 to O_b
+            const uint32_t acc = SPLIT ? to + (s / 4) * HD : to;
+            const uint32_t add = SPLIT ? ((pj | (s % 4)) ? 1u : 0u) : ((pj | s) ? 1u : 0u);
+            if (elect_one()) tc_mma_ts(acc, tp + s * 8, desc_advance(dv, s * 2048), idesc_o, add);
+          }
           if (elect_one()) {
             tc_commit(&pv_done[pg & 1]);
             tc_commit(&v_empty[vs]);
@@ -393,6 +403,18 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
       xw_total += clock64() - x0;
       return acc;
     };
+    // the same hand-shake, returning the partner's value as it is (two warps per row)
+    auto partner = [&](float mine, bool& fine) -> float {
+      float* slot = xch + xpar * (F1_NW * 128);
+      slot[ch * 128 + r] = mine;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&pair_bar[qd]);
+      if (fine) fine = mbar_wait(&pair_bar[qd], pair_phase, 0x5d00 | qd, abort_flag);
+      pair_phase ^= 1;
+      const float other = slot[(ch ^ 1) * 128 + r];
+      xpar ^= 1;
+      return other;
+    };
     const bool prof = (p.debug & 2) && warp == 2 && lane == 0;
     if (prof) atomicAdd(&g_prof_f1[7], (unsigned long long)(clock64() - t_entry));
     int g0 = 0;  // steps of the CTA before this item
@@ -400,7 +422,7 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
     // item, whose scores are already there, so that the wait for the tile's last P·V is hidden behind that step.
     bool pend = false;
     int pend_glast = 0, pend_buf = 0;
-    float pend_l = 1.f, pend_m = 0.f;
+    float pend_l = 1.f, pend_m = 0.f, pend_wa = 1.f, pend_wb = 1.f;  // (split accumulators: their weights)
     T* pend_row = nullptr;
     float* pend_lse = nullptr;
     auto finish_pending = [&]() {
@@ -413,9 +435,20 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
         const float inv = 1.f / pend_l;
         const uint32_t o_addr = lane_addr + F1_COL_O + pend_buf * HD;
         uint32_t v[F1_OW / 32][32];
+        if (SPLIT) {
+          // this warp's 32 output columns of both accumulators, each weighted back to the common maximum
+          uint32_t w[32];
+          tmem_ld32(o_addr + ch * F1_OW, v[0]);
+          tmem_ld32(o_addr + HD + ch * F1_OW, w);
+          tc_wait_ld();
 #pragma unroll
-        for (int cc = 0; cc < F1_OW / 32; ++cc) tmem_ld32(o_addr + ch * F1_OW + cc * 32, v[cc]);
-        tc_wait_ld();
+          for (int e = 0; e < 32; ++e)
+            v[0][e] = __float_as_uint(fmaf(__uint_as_float(v[0][e]), pend_wa, __uint_as_float(w[e]) * pend_wb));
+        } else {
+#pragma unroll
+          for (int cc = 0; cc < F1_OW / 32; ++cc) tmem_ld32(o_addr + ch * F1_OW + cc * 32, v[cc]);
+          tc_wait_ld();
+        }
         // the accumulator has been read out: the first product of a later item may overwrite it
         tc_fence_before();
         __syncwarp();
@@ -440,7 +473,9 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
       const int b = bh / p.H, h = bh % p.H;
       const int jlast = qt;               // last key tile this query tile attends to
       const int i = qt * F1_TILE + r;     // query
-      const uint32_t o_addr = lane_addr + F1_COL_O + (n % NOBUF) * HD;  // this item's accumulator (rescales)
+      // the accumulator this warp rescales: its own (split) or its share of the columns of the common one
+      const uint32_t o_addr = lane_addr + F1_COL_O + (n % NOBUF) * HD + (SPLIT ? ch * HD : ch * F1_OW);
+      constexpr int RESCALE_COLS = SPLIT ? HD : F1_OW;
       const AlibiLog2<BIAS> alibi(BIAS ? p.slopes[h] : 0.f);
       float m_run = -INFINITY;   // true running maximum of the row (both halves)
       float m_used = -INFINITY;  // maximum the accumulator and the running sums are expressed against
@@ -509,7 +544,7 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
           f2_unpack(ls2[1], ls4[2], ls4[3]);
           const float part = (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
           float bad = __any_sync(0xffffffffu, !(part <= kSinglePassLimit)) ? 1.f : 0.f;  // also true for inf / nan
-          bad = exchange(bad, ok, false);
+          if (!SPLIT) bad = exchange(bad, ok, false);  // a common accumulator: both warps of the row redo the step
           if (bad == 0.f) {
             l_run += part;
             done = true;
@@ -555,7 +590,10 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
             }
           }
           float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-          mx = exchange(mx, ok, false);  // finite: the diagonal tile holds key i of every row
+          // finite after the exchange: the diagonal tile holds key i of every row.  Split accumulators: only the
+          // diagonal step needs the partner (a warp whose share of the diagonal tile is masked has no maximum of
+          // its own yet); a redone step further out concerns this warp's accumulator alone.
+          if (!SPLIT || t == 0) mx = exchange(mx, ok, false);
           m_run = fmaxf(m_run, mx);
           // every earlier P·V must have retired before O is rescaled or this P buffer rewritten (the
           // tensor core retires them in order, so the latest one covers the rest; at the first step of an
@@ -577,13 +615,13 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
               const float f = grow ? ex2_mufu(m_used - m_run) : 1.f;
               // each warp of the row rescales its share of the accumulator columns
 #pragma unroll
-              for (int cc = 0; cc < F1_OW / 32; ++cc) {
+              for (int cc = 0; cc < RESCALE_COLS / 32; ++cc) {
                 uint32_t v[32];
-                tmem_ld32(o_addr + ch * F1_OW + cc * 32, v);
+                tmem_ld32(o_addr + cc * 32, v);
                 tc_wait_ld();
 #pragma unroll
                 for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * f);
-                tmem_st32(o_addr + ch * F1_OW + cc * 32, v);
+                tmem_st32(o_addr + cc * 32, v);
               }
               tc_wait_st();
               l_run *= f;
@@ -647,8 +685,19 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
         if (t == 0) finish_pending();  // the previous item's tile
       }
       // the row sum is the sum of the pair's partial sums; the tile itself is finished one step later
-      pend_l = exchange(l_run, ok, true);
-      pend_m = m_used;
+      if (SPLIT) {
+        // merge the two streams: common maximum, each stream's weight against it, common row sum
+        const float m_other = partner(m_used, ok), l_other = partner(l_run, ok);
+        const float m_all = fmaxf(m_used, m_other);
+        const float w_me = ex2_mufu(m_used - m_all), w_other = ex2_mufu(m_other - m_all);
+        pend_l = fmaf(l_run, w_me, l_other * w_other);
+        pend_m = m_all;
+        pend_wa = ch == 0 ? w_me : w_other;
+        pend_wb = ch == 0 ? w_other : w_me;
+      } else {
+        pend_l = exchange(l_run, ok, true);
+        pend_m = m_used;
+      }
       pend_glast = g0 + jlast;
       pend_buf = n % NOBUF;
       pend_row = reinterpret_cast<T*>(p.out) + b * p.so_b + h * p.so_h + (int64_t)i * p.so_t + ch * F1_OW;
