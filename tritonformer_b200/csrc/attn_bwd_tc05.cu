@@ -421,7 +421,7 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
                 const int e = e4 * 4 + k;
                 float x = fmaf(__uint_as_float(sv_[c & 1][e]), c2, -lv[k]);
                 if (plain) {
-                  pe[k] = ex2_approx_b(x);
+                  pe[k] = ex2_approx_b(x);  // (one exponential in four on the FMA pipe, as in the forward, changed nothing here)
                 } else {
                   const int i = i0 + col0 + e;
                   x = alibi.sub_from(x, d0 + (float)e);  // a key above the diagonal (negative distance) is masked below
