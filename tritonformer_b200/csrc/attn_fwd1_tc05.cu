@@ -110,21 +110,8 @@ __device__ __forceinline__ float ex2_fma1(float x) {
   return __int_as_float(__float_as_int(q) + (__float_as_int(xr) << 23));
 }
 
-// Two fp32 values in one 64-bit register pair and the packed FMA that works on both (sm_100): half the
-// instructions for the scale-and-shift of the scores, the polynomial of the FMA-pipe exponentials and the row sums.
-__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
+// (f2_pack / f2_unpack / f2_fma, the packed fp32 pair arithmetic, live in common.cuh: half the instructions for the
+// scale-and-shift of the scores, the polynomial of the FMA-pipe exponentials and the row sums.)
 // 2^x for a pair on the FMA pipe (the polynomial of ex2_fma1, packed)
 __device__ __forceinline__ void ex2_fma2(uint64_t xp, float& r0, float& r1) {
   float x0, x1;
