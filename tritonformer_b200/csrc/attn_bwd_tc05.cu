@@ -6,9 +6,9 @@
 //   Sᵀ  = K Q_iᵀ                 dPᵀ = V dO_iᵀ                      (tensor cores -> TMEM)
 //   Pᵀ  = 2^(Sᵀ·c + bias - lse)  dSᵀ = Pᵀ ∘ (dPᵀ - delta)            (compute warps -> smem, 16 bit)
 //   dV += Pᵀ dO_i     dK += dSᵀ Q_i     dQ_i = dS K                  (tensor cores -> TMEM)
-// dV and dK stay in TMEM for the whole walk; dQ_i is added to an fp32 global accumulator
-// (red.global.add.f32) because every key tile contributes to it; a small kernel scales and
-// rounds the accumulator afterwards.
+// dV and dK stay in TMEM for the whole walk; dQ_i is added to an fp32 global accumulator (TMA
+// reduce-add) because every key tile contributes to it; a small kernel scales and rounds the
+// accumulator afterwards.
 // A 128 x 64 swizzled panel of 16-bit values is at the same time a K-major operand with 128 rows
 // and an MN-major operand with 128 contraction rows, so each of K, V, Q_i, dO_i, dSᵀ sits in
 // shared memory once and serves two products.
@@ -52,10 +52,12 @@ template <int HD> struct FbCfg {
   static constexpr int OFF_P = OFF_DO + QSTAGES * TILE_BYTES;        // Pᵀ  128 x 128 x 2 B (head_dim 128 only)
   static constexpr int OFF_DS = OFF_P + ((256 + 3 * HD + 64 <= 512) ? 0 : 32768);  // dSᵀ 128 x 128 x 2 B
   static constexpr int OFF_STAT = OFF_DS + 32768;                    // [2 parities][16 compute warps][lse2[32], delta[32]] fp32
-  // dQ_i staging for the TMA reduction (head_dim 64 only: it does not fit next to 128-wide tiles)
-  static constexpr bool DQ_TMA = (HD == 64);
-  static constexpr int OFF_DQ = OFF_STAT + 8192;                     // 4 drain warps x 2 boxes of 32 rows x 128 B
-  static constexpr int OFF_BAR = OFF_DQ + (DQ_TMA ? 32768 : 0);
+  // dQ_i staging for the TMA reduction: per drain warp two boxes of 32 rows x 128 B at head_dim 64 (a tile's two
+  // column chunks), one at head_dim 128 (its four chunks go through it one after the other: shared memory)
+  static constexpr bool DQ_TMA = true;
+  static constexpr int DQ_BOXES = (HD == 64) ? 2 : 1;
+  static constexpr int OFF_DQ = OFF_STAT + 8192;
+  static constexpr int OFF_BAR = OFF_DQ + 4 * DQ_BOXES * 4096;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
   static constexpr int COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 256 + HD;
@@ -504,7 +506,7 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
     const int r = qd * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
     const bool prof = (p.debug & 2) && warp == 2 + FB_CWARPS && lane == 0;
-    uint8_t* stage = smem + Cfg::OFF_DQ + (warp - 2 - FB_CWARPS) * 8192;
+    uint8_t* stage = smem + Cfg::OFF_DQ + (warp - 2 - FB_CWARPS) * Cfg::DQ_BOXES * 4096;
     if (Cfg::DQ_TMA && lane == 0) tma_prefetch_desc(&tmDQ);
     for (int it = 0; it < iters; ++it) {
       const int i0 = (kt + it) * FB_T;
@@ -513,7 +515,39 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
       PROF_T(a1);
       PROF_ADD(10, a0, a1);
       tc_fence_after();
-      if (Cfg::DQ_TMA && !(p.debug & 64)) {
+      if (HD == 128 && !(p.debug & 64)) {
+        // Four chunks of 32 columns through one staging box: tensor memory -> registers -> swizzled box -> TMA
+        // reduce-add.  dQ reuses the score columns here, so the next scores wait for this drain.  (Vector atomics
+        // from registers took 4.9 k cycles per tile, by the four drain warps as well as by all sixteen compute
+        // warps, which idle meanwhile: the atomics' own throughput; this takes 3.7 k.)
+        const int row0 = (int)((int64_t)bh * p.T) + i0 + qd * 32;
+#pragma unroll 1
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld32(lane_addr + Cfg::COL_DQ + c * 32, v);
+          tc_wait_ld();
+          if (c + 1 == HD / 32) {  // TMEM is drained: the next scores may overwrite the columns
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(dq_free);
+          }
+          if (!(p.debug & 1)) {
+            if (lane == 0) tma_store_wait_read();  // the box has been read by the TMA unit
+            __syncwarp();
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const uint32_t off = lane * 128 + ((q ^ (lane & 7)) << 4);
+              *reinterpret_cast<uint4*>(stage + off) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_reduce_add_2d(&tmDQ, stage, c * 32, row0);
+              tma_store_commit();
+            }
+          }
+        }
+      } else if (HD == 64 && !(p.debug & 64)) {
         uint32_t v0[32], v1[32];
         tmem_ld32(lane_addr + Cfg::COL_DQ, v0);
         tmem_ld32(lane_addr + Cfg::COL_DQ + 32, v1);
