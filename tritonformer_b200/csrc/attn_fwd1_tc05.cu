@@ -1,25 +1,25 @@
 // Causal flash attention forward on tcgen05 / TMEM: persistent CTAs, one 128-query tile at a time with its
-// score and P buffers doubled and eight softmax warps (head_dim 64 or 128, T % 128 == 0).
+// score buffers doubled and eight softmax warps (head_dim 64 or 128, T % 128 == 0).
 //
 //   warp 0      TMA producer (Q of each tile into one of two buffers, K_j / V_j tiles of 128 keys through rings)
 //   warp 1      MMA issuer (one elected lane, an event loop over non-blocking barrier probes)
-//   warps 2-9   softmax: two warps per TMEM lane quarter, each taking 64 of the 128 keys of a step
-//               (F1_NW; four per quarter measured slower: the pass is bound by issue slots and the
-//               exponential unit of a scheduler, not by latency)
+//   warps 2-    softmax: NW warps per TMEM lane quarter (four at head_dim 64, two at 128), each taking 128 / NW
+//               of the 128 keys of a step
 // One CTA per SM walks a static list of (query tile, batch*head) items: the items are ordered longest walk
 // first over ALL slices and dealt to the CTAs in serpentine order, which balances the CTAs like a greedy
 // longest-first schedule.  Nothing is torn down between items: the producer runs ahead into the next item's
 // Q, K and V while the current item's last steps are computed, the MMA thread issues the next item's first
-// scores as soon as a score buffer is free, and at head_dim 64 the accumulator is doubled as well, so the
-// normalisation and store of one tile overlap the first products of the next.  (One CTA per tile, the
+// scores as soon as a score buffer is free, and a finished tile is normalised and stored one step late, behind
+// the first step of the next item.  (One CTA per tile, the
 // earlier form, paid 1.6 k cycles of set-up, 1.8 k of waiting for the first scores and the launch gap on
 // every tile: a third of the kernel at T 2048.)
 // The scores of step j+1 are computed into the other score buffer while the softmax warps work on
 // step j, so they go from step to step without waiting for the tensor core (with one buffer per tile
 // the round trip "probabilities ready -> next scores issued -> scores landed" is a fixed 1.5 k cycles
-// per step that nothing hides).  A thread owns 64 keys of one query row; the two warps of a row
-// exchange one value per step through shared memory (an mbarrier with one arrival per warp and lane
-// quarter, so the wait is bounded), keep separate partial row sums and add them at the end.
+// per step that nothing hides).  A thread owns 64 keys of one query row; the two warps of a row each keep
+// an accumulator, a reference maximum and a row sum for THEIR keys and meet only twice per item, through
+// shared memory (an mbarrier with one arrival per warp and lane quarter, so the wait is bounded): for the
+// row maximum of the diagonal step and when the accumulators are merged.
 // An item walks its key tiles from the diagonal outwards.  The diagonal tile takes two passes (row maximum,
 // then probabilities) with the causal mask applied per 32-key chunk, which for a whole warp is either
 // untouched, cut by the diagonal or fully masked (then nothing is computed).  Every later tile is a single
@@ -27,9 +27,9 @@
 // bounds P inside fp16/bf16 range; the accumulator row is rescaled only then), with one exponential in four
 // on the FMA pipe.  With ALiBi the penalty only grows along this walk, so the first maximum holds; walking
 // towards the diagonal instead, the maximum rose at every step and every step needed both passes.
-// P is stored 16-bit, two keys per 32-bit column, into tensor memory and is the A operand of P·V.
-// TMEM columns: [0,128) S0, [128,256) S1, [256,320) P0, [320,384) P1, [384,512) O (two accumulators at
-// head_dim 64, one at 128).
+// P is stored 16-bit, two keys per 32-bit column, into tensor memory, over the first half of the score columns
+// it was computed from, and is the A operand of P·V.
+// TMEM columns: [0,128) S0 / P0, [128,256) S1 / P1, [256, 256 + 2 head_dim) the two accumulators.
 // Barrier phases run on counters that continue across items: `g` counts the steps of the CTA (score and P
 // buffers alternate with g), `n` counts its items (Q buffers and accumulators alternate with n).
 #include "attn.cuh"
@@ -45,31 +45,31 @@ namespace {
 constexpr float kLog2e1 = 1.4426950408889634f;
 constexpr float kLn2_1 = 0.6931471805599453f;
 constexpr int F1_TILE = 128;
-constexpr int F1_NW = 2;                       // softmax warps per TMEM lane quarter (per query row)
-constexpr int F1_KW = F1_TILE / F1_NW;         // keys of a step per softmax warp
-constexpr int F1_NC = F1_KW / 32;              // 32-key chunks per warp and step
-constexpr int F1_THREADS = 64 + 128 * F1_NW;
-constexpr int F1_COL_S = 0, F1_COL_P = 256, F1_COL_O = 384;
+constexpr int F1_COL_S = 0;
 
 template <int HD> struct F1Cfg {
   static constexpr int PANELS = HD / 64;                 // 64-element (128-byte) panels along head_dim
   static constexpr int TILE_BYTES = PANELS * 16384;      // 128 rows x HD x 2 B
   static constexpr int STAGES = (HD == 64) ? 3 : 2;      // K / V ring depth (shared memory bound at 128)
-  static constexpr int OW = HD / F1_NW;                  // accumulator columns per warp (rescale, output)
-  // head_dim 64: the two softmax warps of a row each own an accumulator for THEIR 64 keys of every step (O_a at
-  // column 384, O_b at 448), with their own reference maximum and row sum, and the two are merged when the tile
-  // is stored; so the warps exchange a value once per item instead of once per step and drift apart freely.
-  // head_dim 128: one accumulator shared by both warps (tensor memory has no room for two).
-  static constexpr bool SPLIT = (HD == 64);
-  static constexpr int NOBUF = 1;                        // accumulator sets in tensor memory
+  // softmax warps per TMEM lane quarter, i.e. per query row: each takes KW of the 128 keys of a step
+  static constexpr int NW = 2;
+  static constexpr int KW = F1_TILE / NW;
+  static constexpr int NC = KW / 32;                     // 32-key chunks per warp and step
+  static constexpr int THREADS = 64 + 128 * NW;
+  static constexpr int OW = HD / NW;                     // output columns per warp when a tile is stored
+  // The NW softmax warps of a row each own an accumulator for THEIR keys of every step (column 256 + w * HD), with
+  // their own reference maximum and row sum; the accumulators are merged when the tile is stored, so the warps
+  // exchange values once per item instead of once per step and drift apart freely.  P (16-bit) is written over the
+  // first half of the score columns it was computed from, which is what leaves tensor memory for NW accumulators.
+  static constexpr int COL_O = 256;
   static constexpr int OFF_Q = 0;                                  // [2]
   static constexpr int OFF_K = 2 * TILE_BYTES;                     // [STAGES]
   static constexpr int OFF_V = OFF_K + STAGES * TILE_BYTES;        // [STAGES]
   static constexpr int OFF_X = OFF_V + STAGES * TILE_BYTES;        // row exchange: [2 parities][warps per row][128 rows] floats
-  static constexpr int OFF_BAR = OFF_X + 2 * F1_NW * 128 * 4;
+  static constexpr int OFF_BAR = OFF_X + 2 * NW * 128 * 4;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
-  static_assert(OW % 32 == 0, "a softmax warp handles whole 32-column chunks of the accumulator");
-  static_assert(F1_COL_O + (SPLIT ? 2 : 1) * HD <= 512, "tensor memory");
+  static_assert(OW % 16 == 0, "a softmax warp handles whole 16-column chunks of the accumulator");
+  static_assert(COL_O + NW * HD <= 512, "tensor memory");
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
 };
 constexpr float kRescale1 = 8.0f;  // log2 units
@@ -161,13 +161,14 @@ static __device__ unsigned long long g_prof_f1[16];
 #define F1_PROF(idx, t0, t1) do { if (prof) atomicAdd(&g_prof_f1[idx], (unsigned long long)((t1) - (t0))); } while (0)
 
 template <typename T, int HD, int BIAS>
-__global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __grid_constant__ CUtensorMap tmQ,
+__global__ void __launch_bounds__(F1Cfg<HD>::THREADS, 1) attn_fwd1_tc05_kernel(const __grid_constant__ CUtensorMap tmQ,
                                                                        const __grid_constant__ CUtensorMap tmK,
                                                                        const __grid_constant__ CUtensorMap tmV,
                                                                        const F1Params p) {
   using Cfg = F1Cfg<HD>;
-  constexpr int F1_STAGES = Cfg::STAGES, F1_TILE_BYTES = Cfg::TILE_BYTES, F1_OW = Cfg::OW, NOBUF = Cfg::NOBUF;
-  constexpr bool SPLIT = Cfg::SPLIT;
+  constexpr int F1_STAGES = Cfg::STAGES, F1_TILE_BYTES = Cfg::TILE_BYTES, F1_OW = Cfg::OW;
+  constexpr int F1_NW = Cfg::NW, F1_KW = Cfg::KW, F1_NC = Cfg::NC, F1_COL_O = Cfg::COL_O;
+  constexpr int KSTEPS = (F1_TILE / 16) / F1_NW;  // P.V instructions per softmax warp's share of the keys
   constexpr int F1_OFF_Q = Cfg::OFF_Q, F1_OFF_K = Cfg::OFF_K, F1_OFF_V = Cfg::OFF_V, F1_OFF_X = Cfg::OFF_X;
   constexpr int F1_OFF_BAR = Cfg::OFF_BAR;
   extern __shared__ uint8_t smem_raw[];
@@ -285,7 +286,10 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
       uint64_t t_idle = global_ns();
       while (ok && p_valid) {
         bool progress = false;
-        if (s_valid && (sg < 2 || ready(&p_full[sg & 1], ((sg - 2) >> 1) & 1)) && ready(&k_full[ks], kph) &&
+        // (P in the score columns: the product that reads P of two steps ago must be in the pipe before these
+        // scores, which overwrite it; the tensor core runs them in the order of issue)
+        if (s_valid && (sg < 2 || (pg > sg - 2 && ready(&p_full[sg & 1], ((sg - 2) >> 1) & 1))) &&
+            ready(&k_full[ks], kph) &&
             (sj > 0 || ready(&q_full[sn & 1], (sn >> 1) & 1))) {
           tc_fence_after();
           const uint64_t dq = smem_desc_sw128(s0 + F1_OFF_Q + (sn & 1) * F1_TILE_BYTES, 16, 1024);
@@ -313,19 +317,20 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
           progress = true;
         }
         if (ready(&p_full[pg & 1], (pg >> 1) & 1) && ready(&v_full[vs], vph) &&
-            (pj > 0 || pn < NOBUF || ready(&o_free[pn % NOBUF], ((pn - NOBUF) / NOBUF) & 1))) {
+            (pj > 0 || pn < 1 || ready(&o_free[0], (pn - 1) & 1))) {
           tc_fence_after();
           // A = P from tensor memory (a lane is a query row, a 32-bit column holds two consecutive
           // keys), B = V_j from shared memory
           const uint64_t dv = smem_desc_sw128(s0 + F1_OFF_V + vs * F1_TILE_BYTES, 16384, 1024);
-          const uint32_t tp = tb + F1_COL_P + (pg & 1) * 64;
-          const uint32_t to = tb + F1_COL_O + (pn % NOBUF) * HD;
+          const uint32_t tp = tb + F1_COL_S + (pg & 1) * 128;
+          const uint32_t to = tb + F1_COL_O;
 #pragma unroll
           for (int s = 0; s < F1_TILE / 16; ++s) {
-            // split accumulators: keys 0-63 of the step (k-steps 0-3) go to O_a, keys 64-127 to O_b
-            const uint32_t acc = SPLIT ? to + (s / 4) * HD : to;
-            const uint32_t add = SPLIT ? ((pj | (s % 4)) ? 1u : 0u) : ((pj | s) ? 1u : 0u);
-            if (elect_one()) tc_mma_ts(acc, tp + s * 8, desc_advance(dv, s * 2048), idesc_o, add);
+            // split accumulators: each softmax warp's share of the keys (KSTEPS instructions) has its own
+            const uint32_t acc = to + (s / KSTEPS) * HD;
+            const uint32_t add = (pj | (s % KSTEPS)) ? 1u : 0u;
+            const uint32_t pa = tp + (s / KSTEPS) * F1_KW + (s % KSTEPS) * 8;  // P sits at the head of its warp's score columns
+            if (elect_one()) tc_mma_ts(acc, pa, desc_advance(dv, s * 2048), idesc_o, add);
           }
           if (elect_one()) {
             tc_commit(&pv_done[pg & 1]);
@@ -390,26 +395,30 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
       xw_total += clock64() - x0;
       return acc;
     };
-    // the same hand-shake, returning the partner's value as it is (two warps per row)
-    auto partner = [&](float mine, bool& fine) -> float {
+    // the same hand-shake, returning the value of every warp of the row, in warp order
+    auto gather = [&](float mine, bool& fine, float (&all)[F1_NW]) {
       float* slot = xch + xpar * (F1_NW * 128);
       slot[ch * 128 + r] = mine;
       __syncwarp();
       if (lane == 0) mbar_arrive(&pair_bar[qd]);
       if (fine) fine = mbar_wait(&pair_bar[qd], pair_phase, 0x5d00 | qd, abort_flag);
       pair_phase ^= 1;
-      const float other = slot[(ch ^ 1) * 128 + r];
+#pragma unroll
+      for (int w = 0; w < F1_NW; ++w) all[w] = slot[w * 128 + r];
       xpar ^= 1;
-      return other;
     };
-    const bool prof = (p.debug & 2) && warp == 2 && lane == 0;
+    const bool prof = (p.debug & 2) && warp == 2 + ((p.debug >> 8) & 15) && lane == 0;  // bits 8-11: which softmax warp
     if (prof) atomicAdd(&g_prof_f1[7], (unsigned long long)(clock64() - t_entry));
     int g0 = 0;  // steps of the CTA before this item
+    long long last_w3 = clock64();
     // Normalisation and store of a finished tile, run one step late: after the first (diagonal) step of the NEXT
     // item, whose scores are already there, so that the wait for the tile's last P·V is hidden behind that step.
     bool pend = false;
-    int pend_glast = 0, pend_buf = 0;
-    float pend_l = 1.f, pend_m = 0.f, pend_wa = 1.f, pend_wb = 1.f;  // (split accumulators: their weights)
+    int pend_glast = 0;
+    float pend_l = 1.f, pend_m = 0.f;
+    float pend_w[F1_NW];  // (split accumulators: their weights)
+#pragma unroll
+    for (int w = 0; w < F1_NW; ++w) pend_w[w] = 1.f;
     T* pend_row = nullptr;
     float* pend_lse = nullptr;
     auto finish_pending = [&]() {
@@ -420,34 +429,31 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
       if (ok) {
         tc_fence_after();
         const float inv = 1.f / pend_l;
-        const uint32_t o_addr = lane_addr + F1_COL_O + pend_buf * HD;
-        uint32_t v[F1_OW / 32][32];
-        if (SPLIT) {
-          // this warp's 32 output columns of both accumulators, each weighted back to the common maximum
-          uint32_t w[32];
-          tmem_ld32(o_addr + ch * F1_OW, v[0]);
-          tmem_ld32(o_addr + HD + ch * F1_OW, w);
-          tc_wait_ld();
+        const uint32_t o_addr = lane_addr + F1_COL_O;
+        {
+          // this warp's OW output columns of every accumulator, each weighted back to the common maximum
+          float acc[F1_OW];
 #pragma unroll
-          for (int e = 0; e < 32; ++e)
-            v[0][e] = __float_as_uint(fmaf(__uint_as_float(v[0][e]), pend_wa, __uint_as_float(w[e]) * pend_wb));
-        } else {
+          for (int e = 0; e < F1_OW; ++e) acc[e] = 0.f;
 #pragma unroll
-          for (int cc = 0; cc < F1_OW / 32; ++cc) tmem_ld32(o_addr + ch * F1_OW + cc * 32, v[cc]);
-          tc_wait_ld();
-        }
-        // the accumulator has been read out: the first product of a later item may overwrite it
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&o_free[pend_buf]);
+          for (int w = 0; w < F1_NW; ++w) {
+            uint32_t v[F1_OW / 16][16];
 #pragma unroll
-        for (int cc = 0; cc < F1_OW / 32; ++cc) {  // each warp of the row writes its share of the columns
+            for (int cc = 0; cc < F1_OW / 16; ++cc) tmem_ld16(o_addr + w * HD + ch * F1_OW + cc * 16, v[cc]);
+            tc_wait_ld();
 #pragma unroll
-          for (int v4 = 0; v4 < 4; ++v4) {
+            for (int e = 0; e < F1_OW; ++e) acc[e] = fmaf(__uint_as_float(v[e / 16][e % 16]), pend_w[w], acc[e]);
+          }
+          // the accumulators have been read out: the first product of a later item may overwrite them
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&o_free[0]);
+#pragma unroll
+          for (int v8 = 0; v8 < F1_OW / 8; ++v8) {
             float o8[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) o8[e] = __uint_as_float(v[cc][v4 * 8 + e]) * inv;
-            *reinterpret_cast<uint4*>(pend_row + cc * 32 + v4 * 8) = pack8<T>(o8);
+            for (int e = 0; e < 8; ++e) o8[e] = acc[v8 * 8 + e] * inv;
+            *reinterpret_cast<uint4*>(pend_row + v8 * 8) = pack8<T>(o8);
           }
         }
         if (ch == 0) *pend_lse = (pend_m + log2f(pend_l)) * kLn2_1;
@@ -461,8 +467,8 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
       const int jlast = qt;               // last key tile this query tile attends to
       const int i = qt * F1_TILE + r;     // query
       // the accumulator this warp rescales: its own (split) or its share of the columns of the common one
-      const uint32_t o_addr = lane_addr + F1_COL_O + (n % NOBUF) * HD + (SPLIT ? ch * HD : ch * F1_OW);
-      constexpr int RESCALE_COLS = SPLIT ? HD : F1_OW;
+      const uint32_t o_addr = lane_addr + F1_COL_O + ch * HD;
+      constexpr int RESCALE_COLS = HD;
       const AlibiLog2<BIAS> alibi(BIAS ? p.slopes[h] : 0.f);
       float m_run = -INFINITY;   // true running maximum of the row (both halves)
       float m_used = -INFINITY;  // maximum the accumulator and the running sums are expressed against
@@ -474,8 +480,10 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
         const int kbase = j * F1_TILE + ch * F1_KW;  // first key of this thread's share
         const bool diag = (t == 0);
         const uint32_t s_addr = lane_addr + F1_COL_S + bsel * 128 + ch * F1_KW;
-        const uint32_t p_addr = lane_addr + F1_COL_P + bsel * 64 + ch * (F1_KW / 2);
+        // P of a 32-key chunk: 16 columns, at head_dim 64 the first 16 of this warp's own score columns
+        const uint32_t p_addr = s_addr;
         const long long w0 = clock64();
+        F1_PROF(14, last_w3, w0);
         if (ok) ok = mbar_wait(&s_full[bsel], (g >> 1) & 1, 0x5700 | bsel, abort_flag);
         const long long w1 = clock64();
         F1_PROF(1, w0, w1);
@@ -493,6 +501,7 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
           const float neg_m = -m_used;
           const uint64_t c2p = f2_pack(c2, c2), negmp = f2_pack(neg_m, neg_m), onep = f2_pack(1.f, 1.f);
           uint32_t buf[2][32];
+          uint32_t pk_all[F1_NC][16];  // P goes over the scores: stored once the pass is known to stand
           tmem_ld32(s_addr, buf[0]);
 #pragma unroll
           for (int c = 0; c < F1_NC; ++c) {
@@ -500,7 +509,7 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
             if (c + 1 < F1_NC) tmem_ld32(s_addr + (c + 1) * 32, buf[(c + 1) & 1]);
             const uint32_t* v = buf[c & 1];
             const float d0 = (float)(i - (kbase + c * 32));  // distance of the chunk's first key
-            uint32_t pk[16];
+            uint32_t (&pk)[16] = pk_all[c];
 #pragma unroll
             for (int e2 = 0; e2 < 16; ++e2) {  // pairs of keys
               uint64_t xp = f2_fma(f2_pack(__uint_as_float(v[2 * e2]), __uint_as_float(v[2 * e2 + 1])), c2p, negmp);
@@ -522,17 +531,15 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
               const typename Num<T>::T2 h2 = Num<T>::from_f2(p0, p1);
               pk[e2] = *reinterpret_cast<const uint32_t*>(&h2);
             }
-            // this P buffer is read by the P·V of two steps ago until that has retired (long ago, normally)
-            if (c == 0 && g >= 2 && ok) ok = mbar_wait(&pv_done[bsel], ((g - 2) >> 1) & 1, 0x5a00 | bsel, abort_flag);
-            tmem_st16(p_addr + c * 16, pk);
           }
           float ls4[4];
           f2_unpack(ls2[0], ls4[0], ls4[1]);
           f2_unpack(ls2[1], ls4[2], ls4[3]);
           const float part = (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
           float bad = __any_sync(0xffffffffu, !(part <= kSinglePassLimit)) ? 1.f : 0.f;  // also true for inf / nan
-          if (!SPLIT) bad = exchange(bad, ok, false);  // a common accumulator: both warps of the row redo the step
           if (bad == 0.f) {
+#pragma unroll
+            for (int c = 0; c < F1_NC; ++c) tmem_st16(p_addr + c * 16, pk_all[c]);
             l_run += part;
             done = true;
           } else if (prof) {
@@ -580,7 +587,7 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
           // finite after the exchange: the diagonal tile holds key i of every row.  Split accumulators: only the
           // diagonal step needs the partner (a warp whose share of the diagonal tile is masked has no maximum of
           // its own yet); a redone step further out concerns this warp's accumulator alone.
-          if (!SPLIT || t == 0) mx = exchange(mx, ok, false);
+          if (t == 0) mx = exchange(mx, ok, false);
           m_run = fmaxf(m_run, mx);
           // every earlier P·V must have retired before O is rescaled or this P buffer rewritten (the
           // tensor core retires them in order, so the latest one covers the rest; at the first step of an
@@ -664,6 +671,7 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
         F1_PROF(2, w1, w2);
         const long long w3 = clock64();
         F1_PROF(4, w2, w3);
+        last_w3 = w3;
         if (prof) {
           atomicAdd(&g_prof_f1[3], (unsigned long long)(xw_total - xw));
           if (t == 0) atomicAdd(&g_prof_f1[8], (unsigned long long)(w3 - w0));
@@ -672,21 +680,25 @@ __global__ void __launch_bounds__(F1_THREADS, 1) attn_fwd1_tc05_kernel(const __g
         if (t == 0) finish_pending();  // the previous item's tile
       }
       // the row sum is the sum of the pair's partial sums; the tile itself is finished one step later
-      if (SPLIT) {
+      {
         // merge the two streams: common maximum, each stream's weight against it, common row sum
-        const float m_other = partner(m_used, ok), l_other = partner(l_run, ok);
-        const float m_all = fmaxf(m_used, m_other);
-        const float w_me = ex2_mufu(m_used - m_all), w_other = ex2_mufu(m_other - m_all);
-        pend_l = fmaf(l_run, w_me, l_other * w_other);
+        float m_w[F1_NW], l_w[F1_NW];
+        const long long g0_ = clock64();
+        gather(m_used, ok, m_w);
+        gather(l_run, ok, l_w);
+        if (prof) atomicAdd(&g_prof_f1[13], (unsigned long long)(clock64() - g0_));
+        float m_all = m_w[0];
+#pragma unroll
+        for (int w = 1; w < F1_NW; ++w) m_all = fmaxf(m_all, m_w[w]);
+        pend_l = 0.f;
+#pragma unroll
+        for (int w = 0; w < F1_NW; ++w) {
+          pend_w[w] = ex2_mufu(m_w[w] - m_all);
+          pend_l = fmaf(l_w[w], pend_w[w], pend_l);
+        }
         pend_m = m_all;
-        pend_wa = ch == 0 ? w_me : w_other;
-        pend_wb = ch == 0 ? w_other : w_me;
-      } else {
-        pend_l = exchange(l_run, ok, true);
-        pend_m = m_used;
       }
       pend_glast = g0 + jlast;
-      pend_buf = n % NOBUF;
       pend_row = reinterpret_cast<T*>(p.out) + b * p.so_b + h * p.so_h + (int64_t)i * p.so_t + ch * F1_OW;
       pend_lse = p.lse + (int64_t)bh * p.T + i;
       pend = true;
@@ -762,7 +774,7 @@ static int fwd1_launch(const AttnArgs& a, int dtype, cudaStream_t st) {
     if ((rc = ensure_dynamic_smem(attn_fwd1_tc05_kernel<T, HD, MODE>, Cfg::SMEM_BYTES, done[SLOT],                   \
                                   "attention_fwd(tcgen05)")))                                                        \
       return rc;                                                                                                     \
-    launch_overlapped(attn_fwd1_tc05_kernel<T, HD, MODE>, grid, dim3(F1_THREADS), Cfg::SMEM_BYTES, st, tq, tk, tv, p); \
+    launch_overlapped(attn_fwd1_tc05_kernel<T, HD, MODE>, grid, dim3(Cfg::THREADS), Cfg::SMEM_BYTES, st, tq, tk, tv, p); \
   }
   if (a.bias_mode == 0) F1_LAUNCH(0, 0)
   else if (a.bias_mode == 1) F1_LAUNCH(1, 1)

@@ -185,14 +185,15 @@ static int softmax_bwd_launch(const void* dy, const void* y, void* dx, int64_t r
   constexpr int W = Vec16<T>::N;
   const unsigned grid = (unsigned)ceil_div(rows, 4);
   const bool vec = cols % W == 0 && dy_ld % W == 0 && y_ld % W == 0 && dx_ld % W == 0 &&
-                   aligned16(dy) && aligned16(y) && aligned16(dx) && cols <= 4 * 32 * W;
+                   aligned16(dy) && aligned16(y) && aligned16(dx) && cols <= 8 * 32 * W;
   const T *gp = (const T*)dy, *pp = (const T*)y;
   T* op = (T*)dx;
   const int nv = (int)ceil_div(cols, 32 * W);
   if (!vec) launch_overlapped(softmax_bwd_generic_kernel<T>, dim3(grid), dim3(128), 0, st, gp, pp, op, rows, (int)cols, dy_ld, y_ld, dx_ld);
   else if (nv <= 1) launch_overlapped(softmax_bwd_vec_kernel<T, 1>, dim3(grid), dim3(128), 0, st, gp, pp, op, rows, (int)cols, dy_ld, y_ld, dx_ld);
   else if (nv <= 2) launch_overlapped(softmax_bwd_vec_kernel<T, 2>, dim3(grid), dim3(128), 0, st, gp, pp, op, rows, (int)cols, dy_ld, y_ld, dx_ld);
-  else launch_overlapped(softmax_bwd_vec_kernel<T, 4>, dim3(grid), dim3(128), 0, st, gp, pp, op, rows, (int)cols, dy_ld, y_ld, dx_ld);
+  else if (nv <= 4) launch_overlapped(softmax_bwd_vec_kernel<T, 4>, dim3(grid), dim3(128), 0, st, gp, pp, op, rows, (int)cols, dy_ld, y_ld, dx_ld);
+  else launch_overlapped(softmax_bwd_vec_kernel<T, 8>, dim3(grid), dim3(128), 0, st, gp, pp, op, rows, (int)cols, dy_ld, y_ld, dx_ld);
   return launched("softmax_bwd");
 }
 
