@@ -52,10 +52,13 @@ template <int HD> struct FbCfg {
   static constexpr int OFF_P = OFF_DO + QSTAGES * TILE_BYTES;        // Pᵀ  128 x 128 x 2 B (head_dim 128 only)
   static constexpr int OFF_DS = OFF_P + ((256 + 3 * HD + 64 <= 512) ? 0 : 32768);  // dSᵀ 128 x 128 x 2 B
   static constexpr int OFF_STAT = OFF_DS + 32768;                    // [2 parities][16 compute warps][lse2[32], delta[32]] fp32
-  // dQ_i staging for the TMA reduction: per drain warp two boxes of 32 rows x 128 B at head_dim 64 (a tile's two
-  // column chunks), one at head_dim 128 (its four chunks go through it one after the other: shared memory)
+  // dQ_i staging for the TMA reduction: boxes of 32 rows x 128 B, one per drain warp and 32-column chunk.  At
+  // head_dim 64 they have shared memory of their own (two per warp).  At head_dim 128 there is none left, and the
+  // sixteen boxes are the Pᵀ / dSᵀ buffers themselves: between the last gradient product of a tile and the
+  // compute warps' next write nothing else uses them.
   static constexpr bool DQ_TMA = true;
-  static constexpr int DQ_BOXES = (HD == 64) ? 2 : 1;
+  static constexpr bool DQ_IN_PDS = (HD == 128);
+  static constexpr int DQ_BOXES = (HD == 64) ? 2 : 0;
   static constexpr int OFF_DQ = OFF_STAT + 8192;
   static constexpr int OFF_BAR = OFF_DQ + 4 * DQ_BOXES * 4096;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
@@ -125,7 +128,8 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
   uint64_t* dq_full = bars + 9;   // dV, dK, dQ_i products retired
   uint64_t* dq_free = bars + 10;  // dQ_i read out of TMEM
   uint64_t* s_free = bars + 11;   // Sᵀ and dPᵀ read out of TMEM (head_dim 64: the next scores may overwrite them)
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* stage_free = bars + 12;  // head_dim 128: the TMA unit has read dQ_i out of the Pᵀ / dSᵀ buffers
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -157,6 +161,7 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
     mbar_init(dq_full, 1);
     mbar_init(dq_free, 4);
     mbar_init(s_free, FB_CWARPS);
+    mbar_init(stage_free, 4);
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -440,6 +445,8 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
           // Pᵀ / dSᵀ of the previous tile are still being read by its gradient products
           if (prof) t3 = clock64();
           if (it > 0) ok = mbar_wait(dq_full, (it - 1) & 1, 0x2650, abort_flag);
+          // ... and, at head_dim 128, by the TMA reduction of its dQ, which was staged in them
+          if (Cfg::DQ_IN_PDS && it > 0 && ok) ok = mbar_wait(stage_free, (it - 1) & 1, 0x2660, abort_flag);
           if (prof) t4 = clock64();
           PROF_ADD(2, t2, t3);
           PROF_ADD(3, t3, t4);
@@ -516,36 +523,38 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
       PROF_ADD(10, a0, a1);
       tc_fence_after();
       if (HD == 128 && !(p.debug & 64)) {
-        // Four chunks of 32 columns through one staging box: tensor memory -> registers -> swizzled box -> TMA
-        // reduce-add.  dQ reuses the score columns here, so the next scores wait for this drain.  (Vector atomics
-        // from registers took 4.9 k cycles per tile, by the four drain warps as well as by all sixteen compute
-        // warps, which idle meanwhile: the atomics' own throughput; this takes 3.7 k.)
+        // The warp's four chunks of 32 columns go into four boxes inside the Pᵀ / dSᵀ buffers (idle until the
+        // compute warps write the next tile's Pᵀ / dSᵀ), so tensor memory is free after four loads and the next
+        // scores - dQ reuses their columns - start while the TMA unit adds the boxes to the accumulator.  (Through
+        // one box per warp with a wait between chunks the drain took 4.3 k cycles per tile, all of it ahead of the
+        // next scores; vector atomics from registers 4.9 k.)
         const int row0 = (int)((int64_t)bh * p.T) + i0 + qd * 32;
+        uint8_t* boxes = smem + Cfg::OFF_P + (warp - 2 - FB_CWARPS) * 4 * 4096;
 #pragma unroll 1
         for (int c = 0; c < HD / 32; ++c) {
           uint32_t v[32];
           tmem_ld32(lane_addr + Cfg::COL_DQ + c * 32, v);
           tc_wait_ld();
-          if (c + 1 == HD / 32) {  // TMEM is drained: the next scores may overwrite the columns
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(dq_free);
-          }
           if (!(p.debug & 1)) {
-            if (lane == 0) tma_store_wait_read();  // the box has been read by the TMA unit
-            __syncwarp();
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
               const uint32_t off = lane * 128 + ((q ^ (lane & 7)) << 4);
-              *reinterpret_cast<uint4*>(stage + off) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-            }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              tma_reduce_add_2d(&tmDQ, stage, c * 32, row0);
-              tma_store_commit();
+              *reinterpret_cast<uint4*>(boxes + c * 4096 + off) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
             }
           }
+        }
+        tc_fence_before();
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(dq_free);  // tensor memory is drained: the next scores may overwrite the columns
+          if (!(p.debug & 1)) {
+#pragma unroll
+            for (int c = 0; c < HD / 32; ++c) tma_reduce_add_2d(&tmDQ, boxes + c * 4096, c * 32, row0);
+            tma_store_commit();
+            tma_store_wait_read();  // the boxes have been read: Pᵀ / dSᵀ may be written again
+          }
+          mbar_arrive(stage_free);
         }
       } else if (HD == 64 && !(p.debug & 64)) {
         uint32_t v0[32], v1[32];

@@ -394,8 +394,8 @@ static EncodeFn get_encoder() {
   return fn;
 }
 
-int encode_tmap_sw128(CUtensorMap* out, const void* base, int dtype, int rank, const uint64_t* dims,
-                      const uint64_t* strides_bytes, const uint32_t* box) {
+static int encode_tmap(CUtensorMap* out, const void* base, int dtype, int rank, const uint64_t* dims,
+                       const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle) {
   EncodeFn enc = get_encoder();
   if (!enc) return fail(TFB_ERR_DRIVER, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t gdim[5], gstr[5];
@@ -410,10 +410,21 @@ int encode_tmap_sw128(CUtensorMap* out, const void* base, int dtype, int rank, c
                                  : dtype == TFB_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                                     : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUresult r = enc(out, dt, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, bx, es,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(TFB_ERR_DRIVER, "cuTensorMapEncodeTiled failed with code %d", (int)r);
   return TFB_OK;
+}
+
+// Boxes whose rows are 128 bytes in shared memory, 16-byte chunks swizzled over eight rows.
+int encode_tmap_sw128(CUtensorMap* out, const void* base, int dtype, int rank, const uint64_t* dims,
+                      const uint64_t* strides_bytes, const uint32_t* box) {
+  return encode_tmap(out, base, dtype, rank, dims, strides_bytes, box, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+// Boxes laid out row after row in shared memory, no swizzle.
+int encode_tmap_plain(CUtensorMap* out, const void* base, int dtype, int rank, const uint64_t* dims,
+                      const uint64_t* strides_bytes, const uint32_t* box) {
+  return encode_tmap(out, base, dtype, rank, dims, strides_bytes, box, CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
 
