@@ -288,22 +288,34 @@ __global__ void __launch_bounds__(256, 2) ln_bwd_split_kernel(
   int64_t row = (int64_t)blockIdx.x * RG + rg;
   uint4* mine = ring + (size_t)warp * LN_DEPTH * 2 * 3 * 32 + lane;
 
-  // one commit group per step, issued by every lane (empty groups keep the count uniform)
-  auto issue = [&](int64_t r0, int slot) {
-#pragma unroll
-    for (int k = 0; k < 2; ++k) {
-      const int64_t r = r0 + k * stride;
-      if (has && r < rows) {
-        uint4* dst = mine + ((slot * 2 + k) * 3) * 32;
-        cp_async16(dst, reinterpret_cast<const uint4*>(x + r * x_ld) + c);
-        cp_async16(dst + 32, reinterpret_cast<const uint4*>(dy + r * dy_ld) + c);
-        if (dres) cp_async16(dst + 64, reinterpret_cast<const uint4*>(dres + r * dres_ld) + c);
-      }
+  // One commit group per step, issued by every lane (empty groups keep the count uniform).  The source pointers
+  // of the step being issued walk down the tensors (one 64-bit add per tensor and step; the row strides are
+  // multiples of eight elements on this path); `ileft` counts the rows from the first row of that step to the end.
+  const uint4* ix = reinterpret_cast<const uint4*>(x + row * x_ld) + c;
+  const uint4* idy = reinterpret_cast<const uint4*>(dy + row * dy_ld) + c;
+  const uint4* idr = dres ? reinterpret_cast<const uint4*>(dres + row * dres_ld) + c : nullptr;
+  const int64_t x_k = stride * (x_ld >> 3), dy_k = stride * (dy_ld >> 3), dr_k = stride * (dres_ld >> 3);  // second row
+  int64_t ileft = rows - row;
+  auto issue = [&](int slot) {
+    uint4* dst = mine + (slot * 2 * 3) * 32;
+    if (has && ileft > 0) {
+      cp_async16(dst, ix);
+      cp_async16(dst + 32, idy);
+      if (dres) cp_async16(dst + 64, idr);
+    }
+    if (has && ileft > stride) {
+      cp_async16(dst + 96, ix + x_k);
+      cp_async16(dst + 128, idy + dy_k);
+      if (dres) cp_async16(dst + 160, idr + dr_k);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
+    ix += 2 * x_k;
+    idy += 2 * dy_k;
+    if (dres) idr += 2 * dr_k;
+    ileft -= step_rows;
   };
 #pragma unroll
-  for (int s = 0; s < LN_DEPTH - 1; ++s) issue(row + s * step_rows, s);
+  for (int s = 0; s < LN_DEPTH - 1; ++s) issue(s);
   // the row statistics travel one step ahead in registers (a dependent load per step otherwise)
   float mu_next[2], rs_next[2];
   auto fetch_stats = [&](int64_t r0) {
@@ -317,7 +329,7 @@ __global__ void __launch_bounds__(256, 2) ln_bwd_split_kernel(
   fetch_stats(row);
   int slot = 0, parity = 0;
   for (; row < rows; row += step_rows) {
-    issue(row + (LN_DEPTH - 1) * step_rows, (slot + LN_DEPTH - 1) % LN_DEPTH);
+    issue((slot + LN_DEPTH - 1) % LN_DEPTH);
     const float mu_cur[2] = {mu_next[0], mu_next[1]}, rs_cur[2] = {rs_next[0], rs_next[1]};
     fetch_stats(row + step_rows);
     asm volatile("cp.async.wait_group %0;" ::"n"(LN_DEPTH - 1) : "memory");  // this step's copies have landed
@@ -349,14 +361,29 @@ __global__ void __launch_bounds__(256, 2) ln_bwd_split_kernel(
         }
       }
     }
-#pragma unroll
-    for (int k = 0; k < 2; ++k) {
-      s1[k] = warp_sum(s1[k]);
-      s2[k] = warp_sum(s2[k]);
+    // The four sums of the step are reduced together: after the exchanges over 16 and over 8 lanes each lane
+    // carries ONE of them (which one: bits 4 and 3 of its lane number), so three more exchanges finish all four -
+    // six shuffles instead of twenty.  Lanes 0, 8, 16, 24 end up with s1[0], s2[0], s1[1], s2[1].
+    float red;
+    {
+      const bool hi = lane & 16, mid = lane & 8;
+      float k0 = hi ? s1[1] : s1[0], k1 = hi ? s2[1] : s2[0];
+      k0 += __shfl_xor_sync(0xffffffffu, hi ? s1[0] : s1[1], 16);
+      k1 += __shfl_xor_sync(0xffffffffu, hi ? s2[0] : s2[1], 16);
+      red = (mid ? k1 : k0) + __shfl_xor_sync(0xffffffffu, mid ? k0 : k1, 8);
+      red += __shfl_xor_sync(0xffffffffu, red, 4);
+      red += __shfl_xor_sync(0xffffffffu, red, 2);
+      red += __shfl_xor_sync(0xffffffffu, red, 1);
+    }
+    if (G == 1) {
+      s1[0] = __shfl_sync(0xffffffffu, red, 0);
+      s2[0] = __shfl_sync(0xffffffffu, red, 8);
+      s1[1] = __shfl_sync(0xffffffffu, red, 16);
+      s2[1] = __shfl_sync(0xffffffffu, red, 24);
     }
     if (G > 1) {
       // all G warps of the row group run the same number of steps, so the barrier counts match
-      if (lane == 0) xch[rg][parity][part] = make_float4(s1[0], s2[0], s1[1], s2[1]);
+      if ((lane & 7) == 0) reinterpret_cast<float*>(&xch[rg][parity][part])[lane >> 3] = red;
       asm volatile("bar.sync %0, %1;" ::"r"(1 + rg), "r"(32 * G) : "memory");
       float4 t = xch[rg][parity][0];
 #pragma unroll
