@@ -199,6 +199,44 @@ def test_gradients_accumulated_into_existing_grad_buffers(column_blocks):
         assert norm_rel(p.grad.float(), 2.0 * once[n]) < 2e-3, n
 
 
+@pytest.mark.parametrize("fused_qkv", [False, True])
+def test_overwritten_gradients_equal_accumulated_ones(fused_qkv):
+    """`GradBuckets.accumulate(overwrite=True)` writes the linear-weight and LayerNorm gradients instead of adding
+    them, and `zero(skip_written=True)` then clears only the rest of the buckets.  Two consecutive steps on
+    different tokens: nothing of the first step may survive in the second, and the gradients equal those of the
+    clear-everything / add path bit for bit (accumulator + 0 rounds like the accumulator alone)."""
+    from tritonformer_b200.dp import GradBuckets
+    from tritonformer_b200.transformer import Transformer
+    cfg = _cfg(vocab_size=1024, hidden_size=256, max_position_embeddings=128, num_attention_heads=4, head_dim=64,
+               ffn_dim=1024, num_hidden_layers=2, use_linear_bias=True, attn_bias=False)
+    torch.manual_seed(0)
+    model = Transformer(cfg, device="cuda")
+    with torch.no_grad():
+        model.logits_out.weight.normal_(0.0, 0.02)
+    if fused_qkv:
+        model.fuse_projection_weights()
+    tokens = [torch.randint(0, 1024, (2, 128), device="cuda") for _ in range(2)]
+    buckets = GradBuckets(model.parameters(), column_blocks=model.projection_weight_groups() if fused_qkv else ())
+
+    def step(ids, overwrite):
+        buckets.zero(skip_written=overwrite)
+        with buckets.accumulate(overwrite=overwrite):
+            with torch.autocast("cuda", dtype=torch.float16):
+                _, loss = model(ids, ids)
+            (loss * 1024.0).backward()
+        buckets.check_views()
+        return {n: p.grad.detach().clone() for n, p in model.named_parameters()}
+
+    want = step(tokens[1], False)
+    step(tokens[0], True)   # the first step in this mode still clears everything and learns what gets written
+    assert len(buckets._written) > 0
+    cleared = sum(hi - lo for ranges in buckets._ranges_to_clear() for lo, hi in ranges)
+    assert cleared < sum(b.numel() for b in buckets.buckets) // 2  # the weights are the bulk and are skipped
+    got = step(tokens[1], True)
+    for n in want:
+        assert torch.equal(got[n], want[n]), n
+
+
 @pytest.mark.parametrize("graph", [False, True])
 def test_overlapped_launches_match_serialised_launches(graph):
     """Kernels are launched so that their set-up may overlap the previous kernel's tail; every kernel waits

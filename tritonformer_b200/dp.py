@@ -22,6 +22,8 @@ class GradBuckets:
         self.buckets: List[torch.Tensor] = []
         self.members: List[list] = []  # parameters of each bucket
         self._views = []
+        self._blocks = []  # (bucket index, first element, elements, parameters) of every column-block matrix
+        self._written = set()  # data pointers of the .grad views that kernels overwrite (accumulate(overwrite=True))
         block_of = {}
         for blk in column_blocks:
             blk = tuple(blk)
@@ -58,6 +60,7 @@ class GradBuckets:
                         q.grad = view
                         self._views.append((q, view))
                         placed.add(id(q))
+                    self._blocks.append((len(self.buckets), off, len(blk) * p.numel(), tuple(blk)))
                     off += len(blk) * pad(p.numel())
                     continue
                 view = flat[off:off + p.numel()].view_as(p)
@@ -68,16 +71,58 @@ class GradBuckets:
             self.buckets.append(flat)
             self.members.append(list(group))
 
-    def zero(self):
-        for b in self.buckets:
-            b.zero_()
+    def zero(self, skip_written: bool = False):
+        """Clears the buckets.  `skip_written`: leaves out the gradients that the kernels overwrite anyway
+        (`accumulate(overwrite=True)`; known once one step has run that way) and clears only the rest - the
+        embedding tables, biases and the padding between views."""
+        if not skip_written:
+            for b in self.buckets:
+                b.zero_()
+            return
+        for b, ranges in zip(self.buckets, self._ranges_to_clear()):
+            for lo, hi in ranges:
+                b[lo:hi].zero_()
 
-    def accumulate(self):
+    def _ranges_to_clear(self):
+        written = self._written
+        if getattr(self, "_clear_key", None) == len(written):
+            return self._clear_ranges
+        es = {id(b): b.element_size() for b in self.buckets}
+        base = {id(b): b.data_ptr() for b in self.buckets}
+        out = []
+        for b, members in zip(self.buckets, self.members):
+            keep = []  # element ranges of this bucket that are overwritten
+            for p in members:
+                g = p.grad
+                if g is not None and g.data_ptr() in written and g.is_contiguous():
+                    lo = (g.data_ptr() - base[id(b)]) // es[id(b)]
+                    keep.append((lo, lo + g.numel()))
+            # column blocks of one matrix are not contiguous each, but written together: the matrix as a whole
+            for bi, lo, n, blk in self._blocks:
+                if self.buckets[bi] is b and all(q.grad is not None and q.grad.data_ptr() in written for q in blk):
+                    keep.append((lo, lo + n))
+            keep.sort()
+            ranges, at = [], 0
+            for lo, hi in keep:
+                if lo > at:
+                    ranges.append((at, lo))
+                at = max(at, hi)
+            if at < b.numel():
+                ranges.append((at, b.numel()))
+            out.append(ranges)
+        self._clear_key, self._clear_ranges = len(written), out
+        return out
+
+    def accumulate(self, overwrite: bool = False):
         """Context manager for the forward+backward of a step: the kernels that produce weight, LayerNorm and
         embedding gradients add them straight into the bucket views (`linear.accumulate_into_grad`), so no
-        separate accumulation kernels run.  Clear the buckets with `zero()` at the start of a step."""
+        separate accumulation kernels run.  Clear the buckets with `zero()` at the start of a step.
+
+        `overwrite`: linear-weight and LayerNorm gradients are written instead of added (one gradient per
+        parameter and step: no shared weights, one micro-batch); after a first step run this way,
+        `zero(skip_written=True)` clears only what is still added to."""
         from . import linear
-        return linear.accumulate_into_grad()
+        return linear.accumulate_into_grad(overwrite=overwrite, written=self._written)
 
     def check_views(self):
         """Autograd must have accumulated in place: every .grad still aliases its bucket."""

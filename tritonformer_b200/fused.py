@@ -43,7 +43,10 @@ class LayerNormFork(Function):
             if ga is not None and gb is not None and ga.is_contiguous() and gb.is_contiguous() \
                     and ga.dtype == x.dtype and gb.dtype == x.dtype and ga.shape == alpha.shape == gb.shape:
                 into = (ga, gb)  # the column sums are added to .grad by the kernel that folds them
-        dx, dalpha, dbeta = layernorm_backward(dy.to(x.dtype), x, alpha, stats, dres, into=into)
+        dx, dalpha, dbeta = layernorm_backward(dy.to(x.dtype), x, alpha, stats, dres, into=into,
+                                               overwrite=L.overwriting())
+        if into is not None and L.overwriting():
+            L.note_written(*into)
         if into is not None:
             return dx, None, None, None
         return dx, dalpha.view(alpha.shape), dbeta.view(alpha.shape), None
@@ -133,7 +136,9 @@ class QKVProjection(Function):
                     x2 = x.reshape(-1, x.shape[-1])
                     into = torch.as_strided(pgrads[0], (wq.shape[0], 3 * d), (3 * d, 1))
                     L.gemm(x2, x2.stride(1), x2.stride(0), dy, dy.stride(0), dy.stride(1), wq.shape[0], 3 * d, rows,
-                           out=into, accumulate=True)
+                           out=into, accumulate=not L.overwriting())
+                    if L.overwriting():
+                        L.note_written(*pgrads)
                 elif any(need[1:4]):
                     dw = L.weight_grad(x, dy, w)  # (in, 3 d); w is a temporary, so this is a fresh tensor
                     for i, p in enumerate((wq, wk, wv)):

@@ -31,9 +31,10 @@ def layernorm_forward(x, alpha, beta, eps):
     return y.view(x.shape), stats
 
 
-def layernorm_backward(dy, x, alpha, stats, dres=None, into=None):
+def layernorm_backward(dy, x, alpha, stats, dres=None, into=None, overwrite=False):
     """dx, dalpha, dbeta; `dres` (same shape as x) is added to dx inside the kernel.  `into` = (dalpha, dbeta)
-    buffers to ADD the parameter gradients to (then returned as None, None)."""
+    buffers to ADD the parameter gradients to, or with `overwrite` to write them to (then returned as None,
+    None)."""
     d = x.shape[-1]
     x2, dy2 = _rows(x), _rows(dy)
     r2 = _rows(dres) if dres is not None else None
@@ -53,7 +54,7 @@ def layernorm_backward(dy, x, alpha, stats, dres=None, into=None):
         dx.data_ptr(), dalpha.data_ptr(), dbeta.data_ptr(), partials.data_ptr(), n, rows, d,
         dy2.stride(0) if rows > 1 else d, x2.stride(0) if rows > 1 else d,
         (r2.stride(0) if rows > 1 else d) if r2 is not None else 0, d,
-        1 if into is not None else 0, _lib.dtype_code(x.dtype), _lib.stream_ptr(x.device)))
+        1 if (into is not None and not overwrite) else 0, _lib.dtype_code(x.dtype), _lib.stream_ptr(x.device)))
     if into is not None:
         return dx.view(x.shape), None, None
     return dx.view(x.shape), dalpha, dbeta

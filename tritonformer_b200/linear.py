@@ -62,25 +62,47 @@ def replay(calls, device):
 # because parameter hooks do not fire for gradients delivered this way; `dp.GradBuckets.accumulate()`
 # is the same block for a model whose gradients live in flat buckets.
 _accumulate_depth = 0
+_overwrite = False
+_written = None  # where the block in force records the .grad buffers that kernels WROTE (data pointers), or None
 
 
 def accumulating() -> bool:
     return _accumulate_depth > 0
 
 
+def overwriting() -> bool:
+    return _accumulate_depth > 0 and _overwrite
+
+
+def note_written(*grads):
+    """Called by the kernels' wrappers for every `.grad` buffer they overwrote."""
+    if _written is not None:
+        for g in grads:
+            _written.add(g.data_ptr())
+
+
 @contextlib.contextmanager
-def accumulate_into_grad(enabled: bool = True):
+def accumulate_into_grad(enabled: bool = True, overwrite: bool = False, written=None):
     """Weight, LayerNorm-parameter and embedding gradients produced inside the block are added into the
-    existing `.grad` buffers by the kernels that compute them."""
-    global _accumulate_depth
+    existing `.grad` buffers by the kernels that compute them.
+
+    `overwrite`: linear-weight and LayerNorm-parameter gradients are WRITTEN to `.grad` instead of added: the
+    buffers need not be cleared before the step and the product's epilogue does not read them.  Only valid when
+    each such parameter receives exactly one gradient per block (no weight shared between two layers, one
+    micro-batch per block); the data pointers of the buffers written are added to the set `written` when one is
+    given; everything else is still added and still needs a cleared buffer."""
+    global _accumulate_depth, _overwrite, _written
     if not enabled:
         yield
         return
+    previous = (_overwrite, _written)
     _accumulate_depth += 1
+    _overwrite, _written = bool(overwrite), (written if overwrite else None)
     try:
         yield
     finally:
         _accumulate_depth -= 1
+        _overwrite, _written = previous
 
 
 # GEMM scratch, newest last; at most _MAX_WORKSPACES are kept per process.  An entry that falls out is
@@ -196,7 +218,9 @@ def weight_grad(x, dy, w):
         into = w.grad
     # A(mm, kk) = X[kk, mm]
     dw = gemm(x2, x2.stride(1), x2.stride(0), dy2, dy2.stride(0), dy2.stride(1), k, n, m, out=into,
-              accumulate=into is not None)
+              accumulate=into is not None and not overwriting())
+    if into is not None and overwriting():
+        note_written(into)
     return None if into is not None else dw
 
 
