@@ -325,7 +325,10 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
           // dQ_i reuses the Sᵀ columns: the next scores may only follow once dQ_i has been drained
           ok = issue_grads(it);
           if (ok && it + 1 < iters) {
+            PROF_T(b0);
             ok = wait(dq_free, it & 1, 0x2450);
+            PROF_T(b1);
+            PROF_ADD(8, b0, b1);
             if (ok) ok = issue_scores(it + 1);
           }
         }
@@ -530,24 +533,35 @@ __global__ void __launch_bounds__(FB_THREADS, 1) attn_bwd_tc05_kernel(const __gr
         // next scores; vector atomics from registers 4.9 k.)
         const int row0 = (int)((int64_t)bh * p.T) + i0 + qd * 32;
         uint8_t* boxes = smem + Cfg::OFF_P + (warp - 2 - FB_CWARPS) * 4 * 4096;
-#pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld32(lane_addr + Cfg::COL_DQ + c * 32, v);
-          tc_wait_ld();
-          if (!(p.debug & 1)) {
+        // two loads in flight at a time; the columns are handed back as soon as the last load has landed, before
+        // the last stores and the proxy fence
+        auto store_box = [&](int c, const uint32_t (&v)[32]) {
+          if (p.debug & 1) return;
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              const uint32_t off = lane * 128 + ((q ^ (lane & 7)) << 4);
-              *reinterpret_cast<uint4*>(boxes + c * 4096 + off) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-            }
+          for (int q = 0; q < 8; ++q) {
+            const uint32_t off = lane * 128 + ((q ^ (lane & 7)) << 4);
+            *reinterpret_cast<uint4*>(boxes + c * 4096 + off) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
           }
+        };
+        {
+          uint32_t va[32], vb[32];
+          tmem_ld32(lane_addr + Cfg::COL_DQ, va);
+          tmem_ld32(lane_addr + Cfg::COL_DQ + 32, vb);
+          tc_wait_ld();
+          store_box(0, va);
+          store_box(1, vb);
+          tmem_ld32(lane_addr + Cfg::COL_DQ + 64, va);
+          tmem_ld32(lane_addr + Cfg::COL_DQ + 96, vb);
+          tc_wait_ld();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(dq_free);  // tensor memory is drained: the next scores may overwrite the columns
+          store_box(2, va);
+          store_box(3, vb);
         }
-        tc_fence_before();
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          mbar_arrive(dq_free);  // tensor memory is drained: the next scores may overwrite the columns
           if (!(p.debug & 1)) {
 #pragma unroll
             for (int c = 0; c < HD / 32; ++c) tma_reduce_add_2d(&tmDQ, boxes + c * 4096, c * 32, row0);
