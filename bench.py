@@ -272,13 +272,11 @@ def run_b200_arm(args):
             main.wait_stream(zero_stream)
             (loss * (scaler.scale if scaler is not None else loss_scale)).backward()
         if marks is not None:  # last backward kernel enqueued ...
-            marks.append(torch.cuda.Event(enable_timing=True))
-            marks[-1].record()
+            marks[0].record()
         if reducer is not None:
             reducer.finish()
         if marks is not None:  # ... and the stream has joined the collectives
-            marks.append(torch.cuda.Event(enable_timing=True))
-            marks[-1].record()
+            marks[1].record()
         if optimizer is not None and (reducer is not None or world == 1):
             optimizer.step()
         return loss.detach()
@@ -354,14 +352,24 @@ def run_b200_arm(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_ms = t.tolist()
 
-    # N > 1: how much of the gradient all-reduce is NOT hidden behind backward: a few eager steps on every rank
-    # with an event after the last backward kernel and one after the stream has joined the collectives
+    # N > 1: how much of the gradient all-reduce is NOT hidden behind backward: an event after the last backward
+    # kernel and one after the stream has joined the collectives, on every rank.  The step is captured a second time
+    # with the two events in it and replayed, so that the figure belongs to the step that was timed (launched
+    # eagerly, the host falls behind at 8 GPUs and the gap measures that instead); eager steps when not replaying.
     exposed_ms = None
     if reducer is not None:
         gaps = []
+        if graph is not None:
+            marks = [torch.cuda.Event(enable_timing=True, external=True) for _ in range(2)]
+            marked = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(marked):
+                static_loss.copy_(step(static_ids, marks))
         for _ in range(5):
-            marks = []
-            step(static_ids, marks)
+            if graph is not None:
+                marked.replay()
+            else:
+                marks = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+                step(static_ids, marks)
             torch.cuda.synchronize()
             gaps.append(marks[0].elapsed_time(marks[1]))
         t = torch.tensor([statistics.median(gaps[1:])], device=dev, dtype=torch.float64)
