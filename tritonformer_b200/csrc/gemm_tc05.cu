@@ -421,11 +421,6 @@ int encode_tmap_sw128(CUtensorMap* out, const void* base, int dtype, int rank, c
                       const uint64_t* strides_bytes, const uint32_t* box) {
   return encode_tmap(out, base, dtype, rank, dims, strides_bytes, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
-// Boxes laid out row after row in shared memory, no swizzle.
-int encode_tmap_plain(CUtensorMap* out, const void* base, int dtype, int rank, const uint64_t* dims,
-                      const uint64_t* strides_bytes, const uint32_t* box) {
-  return encode_tmap(out, base, dtype, rank, dims, strides_bytes, box, CU_TENSOR_MAP_SWIZZLE_NONE);
-}
 
 
 // Arrival counters plus one fp32 128 x 256 partial tile per SM.

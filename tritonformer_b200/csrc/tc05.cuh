@@ -256,7 +256,5 @@ __device__ __forceinline__ bool elect_one() {
 // dims[0] is the contiguous dimension; strides_bytes[i] is the byte stride of dims[i+1].
 int encode_tmap_sw128(CUtensorMap* out, const void* base, int dtype, int rank, const uint64_t* dims,
                       const uint64_t* strides_bytes, const uint32_t* box);
-int encode_tmap_plain(CUtensorMap* out, const void* base, int dtype, int rank, const uint64_t* dims,
-                      const uint64_t* strides_bytes, const uint32_t* box);  // the same without swizzle
 
 }  // namespace tfb
