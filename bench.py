@@ -442,7 +442,13 @@ def run_b200_arm(args):
         roof_attn = {"bound": "tensor",
                      "kernel": "attn_fwd1_tc05_kernel + attn_bwd_tc05_kernel (+ delta pre-pass, dQ conversion)",
                      "achieved": a_ach, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": a_ach / peaks["tflops"],
-                     "traffic": None, "calls": n_attn, "fwd_ms_per_step": fwd_t * 1e3, "bwd_ms_per_step": bwd_t * 1e3,
+                     # DRAM bytes of one forward + one backward launch, from the ncu captures of the B2 H16 T2048
+                     # hd64 case scaled by batch*heads (the traffic is q, k, v, dO read once: proportional);
+                     # only for the configuration the captures cover
+                     "traffic": (2 * (25.23e6 + 50.92e6 + 1.83e6) * (B * cfg.num_attention_heads) / 64.0
+                                 if (cfg.head_dim == 64 and T == 2048) else None),
+                     "traffic_detail": "profiles/ncu_attention_fwd.md, profiles/ncu_attention_bwd.md",
+                     "calls": n_attn, "fwd_ms_per_step": fwd_t * 1e3, "bwd_ms_per_step": bwd_t * 1e3,
                      "fwd_tflops": aflop[0] / fwd_t / 1e12, "bwd_tflops": aflop[1] / bwd_t / 1e12,
                      "flops_per_step": aflop[0] + aflop[1], "sm_mhz": mhz(clk_step),
                      "peak_source": peaks["source"] + " sustained bf16 cuBLAS",
