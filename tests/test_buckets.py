@@ -36,3 +36,42 @@ def test_groups_that_do_not_qualify_fall_back_to_flat_views():
     ps = _params()
     GradBuckets(ps, bucket_bytes=8 * 16 * 4, column_blocks=[(ps[0], ps[1], ps[2])])  # one parameter per bucket
     assert all(p.grad.is_contiguous() for p in ps)
+
+
+def test_partial_clear_skips_what_the_kernels_overwrite():
+    """`zero(skip_written=True)` leaves the gradients that were recorded as overwritten and clears the rest:
+    other parameters, and the padding between views.  A column-block matrix counts only when ALL of its blocks
+    are overwritten."""
+    from tritonformer_b200 import linear
+    ps = _params()
+    b = GradBuckets(ps, column_blocks=[(ps[0], ps[1], ps[2])])
+    for x in b.buckets:
+        x.fill_(7.0)
+    b.zero(skip_written=True)  # nothing recorded yet: everything is cleared
+    assert all(bool((x == 0).all()) for x in b.buckets)
+    # the block records what kernels would write: the three column blocks and one flat weight
+    with b.accumulate(overwrite=True):
+        assert linear.accumulating() and linear.overwriting()
+        linear.note_written(ps[0].grad, ps[1].grad, ps[2].grad, ps[3].grad)
+    assert not linear.accumulating() and not linear.overwriting()
+    with b.accumulate():  # the adding mode records nothing
+        assert not linear.overwriting()
+        linear.note_written(ps[4].grad)
+    for x in b.buckets:
+        x.fill_(7.0)
+    b.zero(skip_written=True)
+    for i in (0, 1, 2, 3):
+        assert bool((ps[i].grad == 7.0).all()), i      # left alone
+    for i in (4, 5):
+        assert bool((ps[i].grad == 0.0).all()), i      # cleared
+    kept = sum(ps[i].numel() for i in (0, 1, 2, 3))
+    assert sum(int((x == 7.0).sum()) for x in b.buckets) == kept  # the padding is cleared too
+    # only two of the three column blocks written: the matrix is cleared as a whole
+    ps = _params()
+    b = GradBuckets(ps, column_blocks=[(ps[0], ps[1], ps[2])])
+    with b.accumulate(overwrite=True):
+        linear.note_written(ps[0].grad, ps[1].grad)
+    for x in b.buckets:
+        x.fill_(7.0)
+    b.zero(skip_written=True)
+    assert all(bool((p.grad == 0.0).all()) for p in ps)
