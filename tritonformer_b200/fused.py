@@ -65,8 +65,7 @@ class LinearResidual(Function):
     def backward(ctx, dy):
         x, w = ctx.saved_tensors
         dy = dy.to(x.dtype)
-        dx = L.input_grad(dy, w, x.shape) if ctx.needs_input_grad[0] else None
-        dw = L.weight_grad(x, dy, w) if ctx.needs_input_grad[1] else None
+        dx, dw = L.linear_backward(dy, x, w, ctx.needs_input_grad[0], ctx.needs_input_grad[1])
         db = L.column_sum(dy) if ctx.has_bias and ctx.needs_input_grad[2] else None
         return dx, dw, db, dy
 
@@ -125,18 +124,23 @@ class QKVProjection(Function):
             if all(g is not None for g in grads) and _adjacent_columns(grads, 3 * d):
                 rows = x.numel() // x.shape[-1]
                 dy = torch.as_strided(grads[0], (rows, 3 * d), (3 * d, 1))
-                dx = L.input_grad(dy, w, x.shape) if need[0] else None
                 dws = [None, None, None]
                 pgrads = [p.grad for p in (wq, wk, wv)]
-                if L.accumulating() and all(need[1:4]) and all(g is not None for g in pgrads) \
-                        and pgrads[0].dtype == x.dtype and pgrads[0].shape == wq.shape \
-                        and _adjacent_columns(pgrads, 3 * d):
+                one_product = L.accumulating() and all(need[1:4]) and all(g is not None for g in pgrads) \
+                    and pgrads[0].dtype == x.dtype and pgrads[0].shape == wq.shape \
+                    and _adjacent_columns(pgrads, 3 * d)
+                fork = L._WeightGradFork(dy.device, need[0] and one_product)
+                mark = fork.mark()
+                dx = L.input_grad(dy, w, x.shape) if need[0] else None
+                if one_product:
                     # the three .grad are column blocks of one (in, 3 d) matrix (GradBuckets column_blocks):
-                    # one product that adds straight into it
+                    # one product that adds straight into it (on the side stream, beside the input gradient)
                     x2 = x.reshape(-1, x.shape[-1])
                     into = torch.as_strided(pgrads[0], (wq.shape[0], 3 * d), (3 * d, 1))
-                    L.gemm(x2, x2.stride(1), x2.stride(0), dy, dy.stride(0), dy.stride(1), wq.shape[0], 3 * d, rows,
-                           out=into, accumulate=not L.overwriting())
+                    fork.run(mark, lambda: L.gemm(x2, x2.stride(1), x2.stride(0), dy, dy.stride(0), dy.stride(1),
+                                                  wq.shape[0], 3 * d, rows, out=into,
+                                                  accumulate=not L.overwriting()))
+                    fork.join()
                     if L.overwriting():
                         L.note_written(*pgrads)
                 elif any(need[1:4]):
@@ -183,10 +187,16 @@ class MLPResidual(Function):
         x, w1, w2, act = ctx.saved_tensors
         dy = dy.to(x.dtype)
         need = ctx.needs_input_grad
+        # the two weight gradients run on the side stream beside the input-gradient products (see linear.py)
+        fork = L._WeightGradFork(dy.device, need[1] and need[3] and L._grad_goes_into_buffer(w1, x)
+                                 and L._grad_goes_into_buffer(w2, x))
+        m0 = fork.mark()
         dz = L.input_grad(dy, w2, act.shape, mask=act)  # hidden gradient with the ReLU mask applied
-        dw2 = L.weight_grad(act, dy, w2) if need[3] else None
+        m1 = fork.mark()
+        dw2 = fork.run(m0, lambda: L.weight_grad(act, dy, w2)) if need[3] else None
         db2 = L.column_sum(dy) if ctx.has_bias[1] and need[4] else None
         dx = L.input_grad(dz, w1, x.shape) if need[0] else None
-        dw1 = L.weight_grad(x, dz, w1) if need[1] else None
+        dw1 = fork.run(m1, lambda: L.weight_grad(x, dz, w1)) if need[1] else None
         db1 = L.column_sum(dz) if ctx.has_bias[0] and need[2] else None
+        fork.join()
         return dx, dw1, db1, dw2, db2, dy

@@ -7,6 +7,7 @@ producing per-batch partials and summing them.  Bias and ReLU are applied in the
 The incoming gradient is never modified (the reference masks it in place).
 """
 import collections
+import os
 import contextlib
 import ctypes
 
@@ -224,10 +225,59 @@ def weight_grad(x, dy, w):
     return None if into is not None else dw
 
 
+# The two products of a linear layer's backward are independent.  When the weight gradient goes straight into an
+# existing `.grad` buffer (so that nothing is allocated for it), it is launched on a side stream: both products are
+# persistent kernels that fill every SM, and on one stream the second can only start when the first has ended
+# completely, paying its start-up after the other's last epilogue; side by side, its CTAs take over the SMs one by
+# one as the first kernel's CTAs finish.  The compute stream joins the side stream before the backward function
+# returns, so the operands cannot be recycled under the side kernel.
+FORK_WEIGHT_GRAD = os.environ.get("TFB_FORK_DW", "1") == "1"
+_side_streams = {}
+
+
+class _WeightGradFork:
+    """`mark()` before the kernels that the side work does not depend on; `run(mark, fn)` launches fn on the side
+    stream after that point; `join()` makes the compute stream wait for it."""
+
+    def __init__(self, device, enabled=True):
+        self.on = bool(enabled) and FORK_WEIGHT_GRAD and accumulating() and device.type == "cuda"
+        self.used = False
+        if self.on:
+            self.main = torch.cuda.current_stream(device)
+            key = (device.index, self.main.cuda_stream)
+            side = _side_streams.get(key)
+            if side is None:
+                side = _side_streams[key] = torch.cuda.Stream(device)
+            self.side = side
+
+    def mark(self):
+        return self.main.record_event() if self.on else None
+
+    def run(self, mark, fn):
+        if not self.on:
+            return fn()
+        self.side.wait_event(mark)
+        with torch.cuda.stream(self.side):
+            out = fn()
+        self.used = True
+        return out
+
+    def join(self):
+        if self.on and self.used:
+            self.main.wait_stream(self.side)
+
+
+def _grad_goes_into_buffer(w, x):
+    return accumulating() and w.grad is not None and w.grad.is_contiguous() and w.grad.dtype == x.dtype
+
+
 def linear_backward(dy, x, w, need_dx=True, need_dw=True):
     """dX = dY Wᵀ, dW = Xᵀ dY (contraction over every row of the flattened batch)."""
+    fork = _WeightGradFork(dy.device, need_dx and need_dw and _grad_goes_into_buffer(w, x))
+    mark = fork.mark()
     dx = input_grad(dy, w, x.shape) if need_dx else None
-    dw = weight_grad(x, dy, w) if need_dw else None
+    dw = fork.run(mark, lambda: weight_grad(x, dy, w)) if need_dw else None
+    fork.join()
     return dx, dw
 
 
