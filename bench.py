@@ -258,6 +258,9 @@ def run_b200_arm(args):
     # added, so only the rest of the buckets (embedding tables, biases) is cleared (TFB_BENCH_OVERWRITE=0: clear
     # everything and add, the general path).
     overwrite = os.environ.get("TFB_BENCH_OVERWRITE", "1") == "1"
+    # the weight-gradient products float on their side stream until a bucket is reduced or the step ends (the fused
+    # blocks never write a gradient tensor in place; TFB_BENCH_DEFER=0: joined at the end of each backward function)
+    defer = os.environ.get("TFB_BENCH_DEFER", "1") == "1"
 
     def step(ids, marks=None):
         # the gradient buckets are cleared on a side stream while the forward pass runs (nothing reads them
@@ -266,7 +269,7 @@ def run_b200_arm(args):
         zero_stream.wait_stream(main)
         with torch.cuda.stream(zero_stream):
             buckets.zero(skip_written=overwrite)
-        with buckets.accumulate(overwrite=overwrite):
+        with buckets.accumulate(overwrite=overwrite, defer_weight_grads=defer):
             with torch.autocast("cuda", dtype=dtype):
                 _, loss = model(ids, ids)
             main.wait_stream(zero_stream)

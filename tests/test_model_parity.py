@@ -199,12 +199,15 @@ def test_gradients_accumulated_into_existing_grad_buffers(column_blocks):
         assert norm_rel(p.grad.float(), 2.0 * once[n]) < 2e-3, n
 
 
+@pytest.mark.parametrize("defer", [False, True])
 @pytest.mark.parametrize("fused_qkv", [False, True])
-def test_overwritten_gradients_equal_accumulated_ones(fused_qkv):
+def test_overwritten_gradients_equal_accumulated_ones(fused_qkv, defer):
     """`GradBuckets.accumulate(overwrite=True)` writes the linear-weight and LayerNorm gradients instead of adding
     them, and `zero(skip_written=True)` then clears only the rest of the buckets.  Two consecutive steps on
     different tokens: nothing of the first step may survive in the second, and the gradients equal those of the
-    clear-everything / add path bit for bit (accumulator + 0 rounds like the accumulator alone)."""
+    clear-everything / add path bit for bit (accumulator + 0 rounds like the accumulator alone).  `defer`: the
+    weight-gradient products stay on their side stream until the block ends instead of being joined at the end of
+    every backward function."""
     from tritonformer_b200.dp import GradBuckets
     from tritonformer_b200.transformer import Transformer
     cfg = _cfg(vocab_size=1024, hidden_size=256, max_position_embeddings=128, num_attention_heads=4, head_dim=64,
@@ -220,7 +223,7 @@ def test_overwritten_gradients_equal_accumulated_ones(fused_qkv):
 
     def step(ids, overwrite):
         buckets.zero(skip_written=overwrite)
-        with buckets.accumulate(overwrite=overwrite):
+        with buckets.accumulate(overwrite=overwrite, defer_weight_grads=defer and overwrite):
             with torch.autocast("cuda", dtype=torch.float16):
                 _, loss = model(ids, ids)
             (loss * 1024.0).backward()
@@ -233,6 +236,7 @@ def test_overwritten_gradients_equal_accumulated_ones(fused_qkv):
     cleared = sum(hi - lo for ranges in buckets._ranges_to_clear() for lo, hi in ranges)
     assert cleared < sum(b.numel() for b in buckets.buckets) // 2  # the weights are the bulk and are skipped
     got = step(tokens[1], True)
+    torch.cuda.synchronize()  # nothing of this test's side-stream work outlives it
     for n in want:
         assert torch.equal(got[n], want[n]), n
 

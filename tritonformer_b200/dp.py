@@ -113,16 +113,18 @@ class GradBuckets:
         self._clear_key, self._clear_ranges = len(written), out
         return out
 
-    def accumulate(self, overwrite: bool = False):
+    def accumulate(self, overwrite: bool = False, defer_weight_grads: bool = False):
         """Context manager for the forward+backward of a step: the kernels that produce weight, LayerNorm and
         embedding gradients add them straight into the bucket views (`linear.accumulate_into_grad`), so no
         separate accumulation kernels run.  Clear the buckets with `zero()` at the start of a step.
 
         `overwrite`: linear-weight and LayerNorm gradients are written instead of added (one gradient per
         parameter and step: no shared weights, one micro-batch); after a first step run this way,
-        `zero(skip_written=True)` clears only what is still added to."""
+        `zero(skip_written=True)` clears only what is still added to.  `defer_weight_grads`: see
+        `linear.accumulate_into_grad` (for graphs that never write a gradient tensor in place)."""
         from . import linear
-        return linear.accumulate_into_grad(overwrite=overwrite, written=self._written)
+        return linear.accumulate_into_grad(overwrite=overwrite, written=self._written,
+                                           defer_weight_grads=defer_weight_grads)
 
     def check_views(self):
         """Autograd must have accumulated in place: every .grad still aliases its bucket."""
@@ -208,6 +210,8 @@ class OverlappedReducer:
             self.on_collectives(True)
         self.launched[k] = True
         if self.side is not None:
+            from . import linear
+            linear.join_weight_grads()  # weight gradients still in flight on their side stream
             self.side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(self.side):
                 self.buckets.reduce_bucket(b, self.group)

@@ -135,11 +135,13 @@ class QKVProjection(Function):
                 if one_product:
                     # the three .grad are column blocks of one (in, 3 d) matrix (GradBuckets column_blocks):
                     # one product that adds straight into it (on the side stream, beside the input gradient)
-                    x2 = x.reshape(-1, x.shape[-1])
                     into = torch.as_strided(pgrads[0], (wq.shape[0], 3 * d), (3 * d, 1))
-                    fork.run(mark, lambda: L.gemm(x2, x2.stride(1), x2.stride(0), dy, dy.stride(0), dy.stride(1),
-                                                  wq.shape[0], 3 * d, rows, out=into,
-                                                  accumulate=not L.overwriting()))
+
+                    def product():
+                        x2 = x.reshape(-1, x.shape[-1])  # (a copy, if one is needed, belongs to the stream it is used on)
+                        L.gemm(x2, x2.stride(1), x2.stride(0), dy, dy.stride(0), dy.stride(1), wq.shape[0], 3 * d, rows,
+                               out=into, accumulate=not L.overwriting())
+                    fork.run(mark, product, (x, dy))
                     fork.join()
                     if L.overwriting():
                         L.note_written(*pgrads)
@@ -193,10 +195,10 @@ class MLPResidual(Function):
         m0 = fork.mark()
         dz = L.input_grad(dy, w2, act.shape, mask=act)  # hidden gradient with the ReLU mask applied
         m1 = fork.mark()
-        dw2 = fork.run(m0, lambda: L.weight_grad(act, dy, w2)) if need[3] else None
+        dw2 = fork.run(m0, lambda: L.weight_grad(act, dy, w2), (act, dy)) if need[3] else None
         db2 = L.column_sum(dy) if ctx.has_bias[1] and need[4] else None
         dx = L.input_grad(dz, w1, x.shape) if need[0] else None
-        dw1 = fork.run(m1, lambda: L.weight_grad(x, dz, w1)) if need[1] else None
+        dw1 = fork.run(m1, lambda: L.weight_grad(x, dz, w1), (x, dz)) if need[1] else None
         db1 = L.column_sum(dz) if ctx.has_bias[0] and need[2] else None
         fork.join()
         return dx, dw1, db1, dw2, db2, dy

@@ -83,7 +83,8 @@ def note_written(*grads):
 
 
 @contextlib.contextmanager
-def accumulate_into_grad(enabled: bool = True, overwrite: bool = False, written=None):
+def accumulate_into_grad(enabled: bool = True, overwrite: bool = False, written=None,
+                         defer_weight_grads: bool = False):
     """Weight, LayerNorm-parameter and embedding gradients produced inside the block are added into the
     existing `.grad` buffers by the kernels that compute them.
 
@@ -92,18 +93,20 @@ def accumulate_into_grad(enabled: bool = True, overwrite: bool = False, written=
     each such parameter receives exactly one gradient per block (no weight shared between two layers, one
     micro-batch per block); the data pointers of the buffers written are added to the set `written` when one is
     given; everything else is still added and still needs a cleared buffer."""
-    global _accumulate_depth, _overwrite, _written
+    global _accumulate_depth, _overwrite, _written, DEFER_WEIGHT_GRAD_JOIN
     if not enabled:
         yield
         return
-    previous = (_overwrite, _written)
+    previous = (_overwrite, _written, DEFER_WEIGHT_GRAD_JOIN)
     _accumulate_depth += 1
     _overwrite, _written = bool(overwrite), (written if overwrite else None)
+    DEFER_WEIGHT_GRAD_JOIN = bool(defer_weight_grads)
     try:
         yield
     finally:
         _accumulate_depth -= 1
-        _overwrite, _written = previous
+        _overwrite, _written, DEFER_WEIGHT_GRAD_JOIN = previous
+        join_weight_grads()
 
 
 # GEMM scratch, newest last; at most _MAX_WORKSPACES are kept per process.  An entry that falls out is
@@ -231,8 +234,25 @@ def weight_grad(x, dy, w):
 # completely, paying its start-up after the other's last epilogue; side by side, its CTAs take over the SMs one by
 # one as the first kernel's CTAs finish.  The compute stream joins the side stream before the backward function
 # returns, so the operands cannot be recycled under the side kernel.
-FORK_WEIGHT_GRAD = os.environ.get("TFB_FORK_DW", "1") == "1"
+# `accumulate_into_grad(defer_weight_grads=True)` goes one step further: the compute stream does not wait at the end
+# of each backward function but only where the gradients are needed - at the end of the block and before a bucket
+# is reduced (`join_weight_grads`) - so the weight-gradient products fill the gaps of the whole backward pass.  Their
+# operands are marked as in use by the side stream (`record_stream`), which keeps the allocator from recycling them
+# under the side kernels; what nothing guards against is a later IN-PLACE write to such an operand on the compute
+# stream (autograd adds a second gradient contribution into the first one's buffer when it can), so this is for
+# graphs whose gradient tensors are only read after they were handed to a linear layer's backward - the fused
+# blocks of `transformer.py` are such a graph (the residual sums happen inside kernels, into fresh tensors).
+FORK_WEIGHT_GRAD = os.environ.get("TFB_FORK_DW", "1") != "0"
+DEFER_WEIGHT_GRAD_JOIN = False  # set by the accumulate_into_grad block in force
 _side_streams = {}
+_unjoined = {}  # (device index, compute stream handle) -> (compute stream, side stream) with work not yet joined
+
+
+def join_weight_grads():
+    """Makes every compute stream wait for the weight-gradient products that still run on its side stream."""
+    for main, side in list(_unjoined.values()):
+        main.wait_stream(side)
+    _unjoined.clear()
 
 
 class _WeightGradFork:
@@ -253,18 +273,24 @@ class _WeightGradFork:
     def mark(self):
         return self.main.record_event() if self.on else None
 
-    def run(self, mark, fn):
+    def run(self, mark, fn, operands=()):
         if not self.on:
             return fn()
         self.side.wait_event(mark)
         with torch.cuda.stream(self.side):
             out = fn()
         self.used = True
+        if DEFER_WEIGHT_GRAD_JOIN:
+            for t in operands:
+                t.record_stream(self.side)
         return out
 
     def join(self):
         if self.on and self.used:
-            self.main.wait_stream(self.side)
+            if DEFER_WEIGHT_GRAD_JOIN:
+                _unjoined[(self.main.device.index, self.main.cuda_stream)] = (self.main, self.side)
+            else:
+                self.main.wait_stream(self.side)
 
 
 def _grad_goes_into_buffer(w, x):
@@ -276,7 +302,7 @@ def linear_backward(dy, x, w, need_dx=True, need_dw=True):
     fork = _WeightGradFork(dy.device, need_dx and need_dw and _grad_goes_into_buffer(w, x))
     mark = fork.mark()
     dx = input_grad(dy, w, x.shape) if need_dx else None
-    dw = fork.run(mark, lambda: weight_grad(x, dy, w)) if need_dw else None
+    dw = fork.run(mark, lambda: weight_grad(x, dy, w), (x, dy)) if need_dw else None
     fork.join()
     return dx, dw
 
