@@ -391,6 +391,9 @@ def run_b200_arm(args):
         tlinear.PROFILE = recs
         if reducer is not None:
             reducer.enabled = False  # these steps run on rank 0 only: no collectives
+        # every kernel is timed ALONE here: the weight-gradient products stay on the compute stream for these steps
+        # (side by side, as in the timed step, two kernels share the GPU and each one's elapsed time holds the other's)
+        fork_was, tlinear.FORK_WEIGHT_GRAD = tlinear.FORK_WEIGHT_GRAD, False
         step(static_ids)
         tlinear.PROFILE = None
         torch.cuda.synchronize()
@@ -410,6 +413,7 @@ def run_b200_arm(args):
             aflop = [sum(f for _, _, k, f in am if k == "fwd"), sum(f for _, _, k, f in am if k == "bwd")]
             n_attn = len(am)
         clk_step = smp.stop()
+        tlinear.FORK_WEIGHT_GRAD = fork_was
         if reducer is not None:
             reducer.enabled = True
         in_step_s, fwd_t, bwd_t = (statistics.median(x[2:]) for x in (gemm_s, fwd_s, bwd_s))
@@ -434,7 +438,9 @@ def run_b200_arm(args):
                 "peak_source": peaks["source"] + " sustained bf16 cuBLAS", "gemm_ms_per_step": in_step_s * 1e3,
                 "flops_per_step": gflop, "sm_mhz": mhz(clk_step),
                 "ms_x_ghz": in_step_s * 1e3 * (mhz(clk_step) or 0) * 1e-3,
-                "how": "CUDA events around every GEMM call of eager steps (median of 10), on the step's own operands",
+                "how": "CUDA events around every GEMM call of eager steps (median of 10), on the step's own operands, "
+                       "one kernel at a time (in the timed step the weight-gradient products run beside the others "
+                       "on a side stream)",
                 # the same calls back to back on dense random operands inside a CUDA graph: the kernels alone in
                 # the power-capped regime; ms_x_ghz (time x median SM clock, i.e. giga-cycles) separates what the
                 # lower clock costs from what the operands cost
