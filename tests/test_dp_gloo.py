@@ -21,7 +21,11 @@ def _free_port():
 def _worker(rank, world, port, mode, out):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     from datetime import timedelta
-    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=timedelta(seconds=20))
+    try:
+        dist.init_process_group("gloo", rank=rank, world_size=world, timeout=timedelta(seconds=20))
+    except Exception as e:  # noqa: BLE001  (the probed port was taken meanwhile, or the peer was slow to start)
+        out.put((rank, "init_error", repr(e)))
+        return
     try:
         torch.manual_seed(rank)  # replicas start different on purpose
         model = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.ReLU(), torch.nn.Linear(32, 4))
@@ -65,15 +69,18 @@ def _worker(rank, world, port, mode, out):
 
 def _run(mode):
     ctx = mp.get_context("spawn")
-    out = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, mode, out)) for r in range(2)]
-    for p in procs:
-        p.start()
-    res = [out.get(timeout=120) for _ in procs]
-    for p in procs:
-        p.join(timeout=60)
-    return {r: (s, v) for r, s, v in res}
+    for attempt in range(3):  # a rendezvous that did not come up is tried again on another port
+        out = ctx.Queue()
+        port = _free_port()
+        procs = [ctx.Process(target=_worker, args=(r, 2, port, mode, out)) for r in range(2)]
+        for p in procs:
+            p.start()
+        res = [out.get(timeout=120) for _ in procs]
+        for p in procs:
+            p.join(timeout=60)
+        if attempt < 2 and any(s == "init_error" for _, s, _ in res):
+            continue
+        return {r: (s, v) for r, s, v in res}
 
 
 def test_bucketed_allreduce_matches_single_process():
