@@ -205,7 +205,8 @@ def test_overwritten_gradients_equal_accumulated_ones(fused_qkv, defer):
     """`GradBuckets.accumulate(overwrite=True)` writes the linear-weight and LayerNorm gradients instead of adding
     them, and `zero(skip_written=True)` then clears only the rest of the buckets.  Two consecutive steps on
     different tokens: nothing of the first step may survive in the second, and the gradients equal those of the
-    clear-everything / add path bit for bit (accumulator + 0 rounds like the accumulator alone).  `defer`: the
+    clear-everything / add path bit for bit (accumulator + 0 rounds like the accumulator alone; the embedding tables,
+    whose rows are summed with atomics, to the last bit or so).  `defer`: the
     weight-gradient products stay on their side stream until the block ends instead of being joined at the end of
     every backward function."""
     from tritonformer_b200.dp import GradBuckets
@@ -238,7 +239,13 @@ def test_overwritten_gradients_equal_accumulated_ones(fused_qkv, defer):
     got = step(tokens[1], True)
     torch.cuda.synchronize()  # nothing of this test's side-stream work outlives it
     for n in want:
-        assert torch.equal(got[n], want[n]), n
+        if n.startswith("embed_"):
+            # rows of tokens that occur more than once are summed with fp32 atomics: the order, and with it the last
+            # bit, changes from run to run
+            diff = (got[n].float() - want[n].float()).abs().max().item()
+            assert diff <= 2e-3 * want[n].float().abs().max().item(), (n, diff)
+        else:
+            assert torch.equal(got[n], want[n]), n
 
 
 @pytest.mark.parametrize("graph", [False, True])

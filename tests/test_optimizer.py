@@ -43,8 +43,13 @@ def test_adamw_step_matches_torch_adamw(dtype, n):
         # the scaled 16-bit gradient times 1/1024 is exact (a power of two), so both sides see the same g
         um, uv, uw = (_ulps(a.cpu(), b).max().item() for a, b in ((m, st["exp_avg"]), (v, st["exp_avg_sq"]), (master, ref.detach())))
         print(f"step {it}: worst distance in units of the last place: exp_avg {um}, exp_avg_sq {uv}, master weight {uw}")
-        assert um <= 1 and uv <= 1
-        assert uw <= it + 2  # at most one unit per step on top of identical moments
+        import hashlib
+        sig = lambda t: hashlib.sha1(t.detach().cpu().contiguous().view(torch.uint8).numpy().tobytes()).hexdigest()[:10]
+        note = (f"step {it}: ulps m {um} v {uv} w {uw}; cpu w {sig(ref)} m {sig(st['exp_avg'])} v {sig(st['exp_avg_sq'])}; "
+                f"gpu w {sig(master)} m {sig(m)} v {sig(v)}; g {sig(g)}")
+        print(note)
+        assert um <= 1 and uv <= 1, note
+        assert uw <= it + 2, note  # at most one unit per step on top of identical moments
         assert torch.equal(param.float().cpu(), master.cpu().to(dtype).float())
 
 
