@@ -294,7 +294,10 @@ class _WeightGradFork:
 
 
 def _grad_goes_into_buffer(w, x):
-    return accumulating() and w.grad is not None and w.grad.is_contiguous() and w.grad.dtype == x.dtype
+    """The conditions under which weight_grad writes into `w.grad` and returns nothing (only then may it run on the
+    side stream: a tensor it allocated there would be used on the compute stream)."""
+    return accumulating() and w.grad is not None and w.grad.is_contiguous() and w.grad.dtype == x.dtype \
+        and w.grad.shape == w.shape and w.dim() == 2 and x.shape[-1] == w.shape[0]
 
 
 def linear_backward(dy, x, w, need_dx=True, need_dw=True):
