@@ -75,3 +75,24 @@ def test_partial_clear_skips_what_the_kernels_overwrite():
         x.fill_(7.0)
     b.zero(skip_written=True)
     assert all(bool((p.grad == 0.0).all()) for p in ps)
+
+
+def test_accumulate_blocks_restore_their_switches():
+    """The overwrite / deferred-join switches belong to the block that set them, nested or not, and are back to
+    their defaults afterwards (also when the block is left by an exception)."""
+    from tritonformer_b200 import linear
+    assert not linear.accumulating() and not linear.overwriting() and not linear.DEFER_WEIGHT_GRAD_JOIN
+    with linear.accumulate_into_grad(overwrite=True, defer_weight_grads=True):
+        assert linear.accumulating() and linear.overwriting() and linear.DEFER_WEIGHT_GRAD_JOIN
+        with linear.accumulate_into_grad():
+            assert linear.accumulating() and not linear.overwriting() and not linear.DEFER_WEIGHT_GRAD_JOIN
+        assert linear.overwriting() and linear.DEFER_WEIGHT_GRAD_JOIN
+        with linear.accumulate_into_grad(enabled=False):
+            assert linear.overwriting()  # a disabled block changes nothing
+    assert not linear.accumulating() and not linear.overwriting() and not linear.DEFER_WEIGHT_GRAD_JOIN
+    try:
+        with linear.accumulate_into_grad(overwrite=True):
+            raise ValueError("leave the block")
+    except ValueError:
+        pass
+    assert not linear.accumulating() and not linear.overwriting()
